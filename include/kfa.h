@@ -1,0 +1,94 @@
+/*
+ * kfa.h - C ABI of libkfa.so: flash-attention forward and backward for NVIDIA B200 (sm_100a).
+ *
+ * This is the boundary a host binds instead of the reference's Triton launchers
+ * (KohakuFA: src/kohakufa/sm100/fwd.py:1188-1232 attention_forward,
+ *            src/kohakufa/sm100/bwd.py:1413-1482 attention_backward).
+ *
+ * Conventions
+ *   - Every tensor is a [B, H, S, D] view described by KfaTensor4: element strides, last
+ *     dimension contiguous, every other stride a multiple of 8 elements (16 bytes), base
+ *     pointer 16-byte aligned (the reference's rule, src/kohakufa/sm100/op.py:53-55).
+ *   - 16-bit data is fp16 (KFA_F16) or bf16 (KFA_BF16). D is 64 or 128. H of q equals H of k / v.
+ *   - block = 0: dense. block = P > 0: key c is visible to query r iff c / P <= r / P
+ *     (top-left aligned; P = 1 is token-causal) (tests/reference.py:6-12).
+ *   - Calls enqueue work on `stream` (a cudaStream_t) of the CURRENT device and return without
+ *     synchronising. They allocate no device memory: outputs and scratch are the caller's.
+ *   - Return value: 0 on success, a negative KFA_ERR_* otherwise; kfa_last_error() then gives a
+ *     message (thread-local).
+ *   - `dev_status` points to one int32 in device memory, zero before the first call. A kernel
+ *     whose internal wait ran out of time writes a nonzero code there and finishes early
+ *     instead of hanging; later launches that see a nonzero word do nothing. The host reads
+ *     it whenever it wants to (tests do after every call).
+ */
+#ifndef KFA_H_
+#define KFA_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KFA_ABI_VERSION 1
+
+#define KFA_F16 0
+#define KFA_BF16 1
+
+#define KFA_OK 0
+#define KFA_ERR_ARG (-1)      /* shape / stride / alignment / dtype not supported */
+#define KFA_ERR_CUDA (-2)     /* a CUDA runtime or driver call failed */
+#define KFA_ERR_SELFTEST (-3) /* kfa_selftest: results differ from the host computation */
+
+typedef struct KfaTensor4 {
+  void* ptr;
+  int64_t shape[4];  /* B, H, S, D */
+  int64_t stride[4]; /* in elements */
+} KfaTensor4;
+
+int kfa_abi_version(void);
+const char* kfa_last_error(void);
+
+/* Bytes of the backward's per-row statistics scratch for (B, H, Sq): fp32
+ * [B*H, ceil(Sq/128), 3, 128] holding (m, log2 l, delta) per query row. */
+int64_t kfa_bwd_stats_bytes(int64_t B, int64_t H, int64_t Sq);
+
+/* Forward. out: [B, H, Sq, D]; lse: fp32 [B, H, 2, Sq] contiguous, plane 0 = row max m of the raw
+ * (unscaled) scores, plane 1 = log2(l), l = sum exp2((S - m) * scale * log2 e).
+ * Replaces attention_forward (fwd.py:1188-1232) + attention_fwd_kernel (fwd.py:1065-1136). */
+int kfa_fwd(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* out,
+            float* lse, float scale, int block, int dtype, int* dev_status, void* stream);
+
+/* Backward, step 1: delta = rowsum(dout * out) and the packed per-tile statistics.
+ * Replaces _prepare_kernel (bwd.py:1358-1388). */
+int kfa_bwd_prepare(const KfaTensor4* out, const KfaTensor4* dout, const float* lse, float* stats,
+                    int dtype, void* stream);
+
+/* Backward, step 2: dK and dV. Replaces the dK / dV half of attention_bwd_kernel (bwd.py:1248-1350). */
+int kfa_bwd_dkdv(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* dout,
+                 const float* stats, const KfaTensor4* dk, const KfaTensor4* dv, float scale, int block,
+                 int dtype, int* dev_status, void* stream);
+
+/* Backward, step 3: dQ. Replaces the dQ half of attention_bwd_kernel and _dq_convert_kernel
+ * (bwd.py:1135-1232, 1391-1410). */
+int kfa_bwd_dq(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* dout,
+               const float* stats, const KfaTensor4* dq, float scale, int block, int dtype,
+               int* dev_status, void* stream);
+
+/* Backward, all three steps in stream order. Replaces attention_backward (bwd.py:1413-1482).
+ * `stats` is scratch of kfa_bwd_stats_bytes(B, H, Sq) bytes. */
+int kfa_bwd(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* out,
+            const KfaTensor4* dout, const float* lse, float* stats, const KfaTensor4* dq,
+            const KfaTensor4* dk, const KfaTensor4* dv, float scale, int block, int dtype,
+            int* dev_status, void* stream);
+
+/* Hardware self-check of the building blocks (TMA tile load, MMA from shared memory, MMA with a
+ * tensor-memory operand, tensor-memory loads / stores) on small fixed matrices. Synchronises.
+ * `report` (may be NULL) receives `report_len` bytes of text. No counterpart in the reference. */
+int kfa_selftest(char* report, int report_len);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* KFA_H_ */

@@ -1,0 +1,142 @@
+"""ctypes binding of ``libkfa.so`` (declared in ``include/kfa.h``).
+
+The library is the only compute path of this package: there is no Python, Triton or CPU
+fallback. If it is missing, loading raises with the build command instead of degrading.
+"""
+
+import ctypes
+import threading
+from pathlib import Path
+
+import torch
+
+LIB_PATH = Path(__file__).resolve().parent / "libkfa.so"
+
+KFA_F16, KFA_BF16 = 0, 1
+ABI_VERSION = 1
+
+# Every entry point include/kfa.h declares (checked against the built library by the tests).
+SYMBOLS = (
+    "kfa_abi_version",
+    "kfa_last_error",
+    "kfa_bwd_stats_bytes",
+    "kfa_fwd",
+    "kfa_bwd_prepare",
+    "kfa_bwd_dkdv",
+    "kfa_bwd_dq",
+    "kfa_bwd",
+    "kfa_selftest",
+)
+
+
+class KfaTensor4(ctypes.Structure):
+    _fields_ = [
+        ("ptr", ctypes.c_void_p),
+        ("shape", ctypes.c_int64 * 4),
+        ("stride", ctypes.c_int64 * 4),
+    ]
+
+
+class KfaError(RuntimeError):
+    """A libkfa call returned a negative status."""
+
+
+_lock = threading.Lock()
+_lib = None
+_status = {}  # device index -> int32[1] status word
+
+
+def load() -> ctypes.CDLL:
+    """The loaded library; raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        if not LIB_PATH.exists():
+            raise KfaError(
+                f"{LIB_PATH} is missing: build it with `python -m kohakufa_b200.build` "
+                "(needs nvcc; there is no fallback path)"
+            )
+        lib = ctypes.CDLL(str(LIB_PATH))
+        T = ctypes.POINTER(KfaTensor4)
+        vp, fp, ip = ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p
+        lib.kfa_abi_version.restype = ctypes.c_int
+        lib.kfa_last_error.restype = ctypes.c_char_p
+        lib.kfa_bwd_stats_bytes.restype = ctypes.c_int64
+        lib.kfa_bwd_stats_bytes.argtypes = [ctypes.c_int64] * 3
+        lib.kfa_fwd.argtypes = [T, T, T, T, fp, ctypes.c_float, ctypes.c_int, ctypes.c_int, ip, vp]
+        lib.kfa_bwd_prepare.argtypes = [T, T, fp, fp, ctypes.c_int, vp]
+        lib.kfa_bwd_dkdv.argtypes = [T, T, T, T, fp, T, T, ctypes.c_float, ctypes.c_int, ctypes.c_int, ip, vp]
+        lib.kfa_bwd_dq.argtypes = [T, T, T, T, fp, T, ctypes.c_float, ctypes.c_int, ctypes.c_int, ip, vp]
+        lib.kfa_bwd.argtypes = [T, T, T, T, T, fp, fp, T, T, T, ctypes.c_float, ctypes.c_int, ctypes.c_int, ip, vp]
+        lib.kfa_selftest.argtypes = [ctypes.c_char_p, ctypes.c_int]
+        for name in ("kfa_fwd", "kfa_bwd_prepare", "kfa_bwd_dkdv", "kfa_bwd_dq", "kfa_bwd", "kfa_selftest"):
+            getattr(lib, name).restype = ctypes.c_int
+        if lib.kfa_abi_version() != ABI_VERSION:
+            raise KfaError(f"libkfa ABI {lib.kfa_abi_version()} != expected {ABI_VERSION}: rebuild")
+        _lib = lib
+    return _lib
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        raise KfaError(f"libkfa error {rc}: {load().kfa_last_error().decode()}")
+
+
+def tensor4(t: torch.Tensor) -> KfaTensor4:
+    """Descriptor of a [B, H, S, D] CUDA tensor (any strides; validated by the library)."""
+    assert t.dim() == 4 and t.is_cuda
+    d = KfaTensor4()
+    d.ptr = t.data_ptr()
+    for i in range(4):
+        d.shape[i] = t.shape[i]
+        d.stride[i] = t.stride(i)
+    return d
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float16:
+        return KFA_F16
+    if dtype == torch.bfloat16:
+        return KFA_BF16
+    raise TypeError(f"libkfa: dtype {dtype}: fp16 or bf16")
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """The per-device int32 word kernels report a timed-out wait in (0 = healthy)."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    word = _status.get(index)
+    if word is None:
+        with _lock:
+            word = _status.get(index)
+            if word is None:
+                word = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", index))
+                _status[index] = word
+    return word
+
+
+def device_status(device=None) -> int:
+    """Reads the status word back (synchronises). Nonzero: 100 + id of the wait that gave up."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    return int(status_word(device).item())
+
+
+def reset_device_status(device=None) -> None:
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    status_word(device).zero_()
+
+
+def stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def selftest() -> str:
+    """Runs the library's hardware self-check on the current device; returns its report."""
+    buf = ctypes.create_string_buffer(4096)
+    rc = load().kfa_selftest(buf, len(buf))
+    report = buf.value.decode()
+    if rc != 0:
+        raise KfaError(f"kfa_selftest failed ({rc}): {load().kfa_last_error().decode()}\n{report}")
+    return report

@@ -1,0 +1,332 @@
+// C ABI of libkfa.so (declared in include/kfa.h): argument checks, TMA tensor-map encoding and
+// kernel launches for the attention forward and backward. No device allocation, no host
+// synchronisation (except kfa_selftest), no global mutable state besides per-device "attribute
+// already set" flags.
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "../../include/kfa.h"
+#include "kfa_bwd.cuh"
+#include "kfa_fwd.cuh"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define KFA_CUDA(expr)                                                                    \
+  do {                                                                                    \
+    cudaError_t e_ = (expr);                                                              \
+    if (e_ != cudaSuccess) return fail(KFA_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(e_)); \
+  } while (0)
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static std::atomic<EncodeFn> cached{nullptr};
+  EncodeFn f = cached.load();
+  if (f) return f;
+  void* sym = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+      q != cudaDriverEntryPointSuccess || !sym)
+    return nullptr;
+  f = reinterpret_cast<EncodeFn>(sym);
+  cached.store(f);
+  return f;
+}
+
+int check_tensor(const KfaTensor4* t, const char* name) {
+  if (!t || !t->ptr) return fail(KFA_ERR_ARG, "%s: null tensor", name);
+  if (reinterpret_cast<uintptr_t>(t->ptr) % 16) return fail(KFA_ERR_ARG, "%s: base not 16-byte aligned", name);
+  if (t->stride[3] != 1) return fail(KFA_ERR_ARG, "%s: last dimension must be contiguous", name);
+  for (int i = 0; i < 3; ++i)
+    if (t->shape[i] > 1 && (t->stride[i] % 8 != 0 || t->stride[i] <= 0))
+      return fail(KFA_ERR_ARG, "%s: stride[%d]=%lld must be a positive multiple of 8 elements", name, i,
+                  static_cast<long long>(t->stride[i]));
+  for (int i = 0; i < 4; ++i)
+    if (t->shape[i] < 1 || t->shape[i] > 0x7fffffff) return fail(KFA_ERR_ARG, "%s: bad shape[%d]", name, i);
+  return KFA_OK;
+}
+
+// 4-D tiled map over a [B, H, S, D] view: dims (D, S, H, B), box (64, 128, 1, 1), 128-byte swizzle,
+// out-of-range rows read as zeros.
+int make_map(const KfaTensor4* t, int dtype, CUtensorMap* map, const char* name) {
+  EncodeFn enc = encode_fn();
+  if (!enc) return fail(KFA_ERR_CUDA, "cuTensorMapEncodeTiled not available from the driver");
+  const cuuint64_t D = t->shape[3], S = t->shape[2], H = t->shape[1], B = t->shape[0];
+  cuuint64_t dims[4] = {D, S, H, B};
+  // A dimension of extent 1 never advances: give it any legal stride.
+  auto st = [&](int i) -> cuuint64_t {
+    const int64_t s = (t->shape[i] > 1) ? t->stride[i] : static_cast<int64_t>(D);
+    return static_cast<cuuint64_t>(s) * 2;
+  };
+  cuuint64_t strides[3] = {st(2), st(1), st(0)};
+  cuuint32_t box[4] = {64, 128, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(map, dtype == KFA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                   t->ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(KFA_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", name, (int)r);
+  return KFA_OK;
+}
+
+int check_qkv(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, int dtype, int block) {
+  int rc;
+  if ((rc = check_tensor(q, "q")) || (rc = check_tensor(k, "k")) || (rc = check_tensor(v, "v"))) return rc;
+  if (dtype != KFA_F16 && dtype != KFA_BF16) return fail(KFA_ERR_ARG, "dtype %d: KFA_F16 or KFA_BF16", dtype);
+  const int64_t D = q->shape[3];
+  if (D != 64 && D != 128) return fail(KFA_ERR_ARG, "head_dim %lld: 64 or 128", (long long)D);
+  for (int i = 0; i < 4; ++i)
+    if (k->shape[i] != v->shape[i]) return fail(KFA_ERR_ARG, "k and v shapes differ");
+  if (k->shape[0] != q->shape[0] || k->shape[3] != D) return fail(KFA_ERR_ARG, "k / v batch or head_dim differ from q");
+  if (k->shape[1] != q->shape[1]) return fail(KFA_ERR_ARG, "q heads %lld != k / v heads %lld (grouped-query attention is not built)",
+                                               (long long)q->shape[1], (long long)k->shape[1]);
+  if (block < 0) return fail(KFA_ERR_ARG, "block %d < 0", block);
+  return KFA_OK;
+}
+
+int check_like(const KfaTensor4* t, const KfaTensor4* ref, const char* name) {
+  int rc = check_tensor(t, name);
+  if (rc) return rc;
+  for (int i = 0; i < 4; ++i)
+    if (t->shape[i] != ref->shape[i]) return fail(KFA_ERR_ARG, "%s: shape differs from its primal", name);
+  return KFA_OK;
+}
+
+template <typename K>
+int set_smem(K kernel, int bytes) {
+  KFA_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  return KFA_OK;
+}
+
+constexpr float LOG2E = 1.4426950408889634f;
+
+template <int D, bool BF16>
+int launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const kfa::FwdParams& p,
+               cudaStream_t s) {
+  auto kern = kfa::kfa_fwd_kernel<D, BF16>;
+  int rc = set_smem(kern, kfa::FwdCfg<D>::SMEM_BYTES);
+  if (rc) return rc;
+  const long long grid = static_cast<long long>(p.B) * p.H * p.n_q_tiles;
+  if (grid > 0x7fffffffll) return fail(KFA_ERR_ARG, "too many tiles");
+  kern<<<static_cast<unsigned>(grid), kfa::FWD_THREADS, kfa::FwdCfg<D>::SMEM_BYTES, s>>>(mq, mk, mv, p);
+  KFA_CUDA(cudaGetLastError());
+  return KFA_OK;
+}
+
+template <int D, bool BF16>
+int launch_prepare(const kfa::PrepParams& p, cudaStream_t s) {
+  dim3 grid(p.n_q128, p.B * p.H);
+  kfa::kfa_bwd_prepare_kernel<D, BF16><<<grid, 128, 0, s>>>(p);
+  KFA_CUDA(cudaGetLastError());
+  return KFA_OK;
+}
+
+template <int D, bool BF16>
+int launch_dkdv(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mdo,
+                const kfa::BwdParams& p, cudaStream_t s) {
+  auto kern = kfa::kfa_bwd_dkdv_kernel<D, BF16>;
+  int rc = set_smem(kern, kfa::BwdCfg<D>::KV_SMEM_BYTES);
+  if (rc) return rc;
+  const long long grid = static_cast<long long>(p.B) * p.H * p.n_k128;
+  if (grid > 0x7fffffffll) return fail(KFA_ERR_ARG, "too many tiles");
+  kern<<<static_cast<unsigned>(grid), kfa::BWD_THREADS, kfa::BwdCfg<D>::KV_SMEM_BYTES, s>>>(mq, mk, mv, mdo, p);
+  KFA_CUDA(cudaGetLastError());
+  return KFA_OK;
+}
+
+template <int D, bool BF16>
+int launch_dq(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mdo,
+              const kfa::BwdParams& p, cudaStream_t s) {
+  auto kern = kfa::kfa_bwd_dq_kernel<D, BF16>;
+  int rc = set_smem(kern, kfa::BwdCfg<D>::Q_SMEM_BYTES);
+  if (rc) return rc;
+  const long long grid = static_cast<long long>(p.B) * p.H * p.n_q128;
+  if (grid > 0x7fffffffll) return fail(KFA_ERR_ARG, "too many tiles");
+  kern<<<static_cast<unsigned>(grid), kfa::BWD_THREADS, kfa::BwdCfg<D>::Q_SMEM_BYTES, s>>>(mq, mk, mv, mdo, p);
+  KFA_CUDA(cudaGetLastError());
+  return KFA_OK;
+}
+
+#define KFA_DISPATCH(D_, dtype_, call)                     \
+  do {                                                     \
+    if ((D_) == 64 && (dtype_) == KFA_F16) {               \
+      constexpr int KD = 64;                               \
+      constexpr bool KB = false;                           \
+      return call;                                         \
+    } else if ((D_) == 64) {                               \
+      constexpr int KD = 64;                               \
+      constexpr bool KB = true;                            \
+      return call;                                         \
+    } else if ((dtype_) == KFA_F16) {                      \
+      constexpr int KD = 128;                              \
+      constexpr bool KB = false;                           \
+      return call;                                         \
+    } else {                                               \
+      constexpr int KD = 128;                              \
+      constexpr bool KB = true;                            \
+      return call;                                         \
+    }                                                      \
+  } while (0)
+
+void fill_bwd_params(kfa::BwdParams& p, const KfaTensor4* q, const KfaTensor4* k, const float* stats, float scale,
+                     int block, int* dev_status) {
+  std::memset(&p, 0, sizeof(p));
+  p.stats = stats;
+  p.B = static_cast<int>(q->shape[0]);
+  p.H = static_cast<int>(q->shape[1]);
+  p.Sq = static_cast<int>(q->shape[2]);
+  p.Skv = static_cast<int>(k->shape[2]);
+  p.P = block;
+  p.c = scale * LOG2E;
+  p.scale = scale;
+  p.n_q128 = (p.Sq + 127) / 128;
+  p.n_k128 = (p.Skv + 127) / 128;
+  p.status = dev_status;
+}
+
+}  // namespace
+
+extern "C" {
+
+int kfa_abi_version(void) { return KFA_ABI_VERSION; }
+
+const char* kfa_last_error(void) { return g_err; }
+
+int64_t kfa_bwd_stats_bytes(int64_t B, int64_t H, int64_t Sq) {
+  return B * H * ((Sq + 127) / 128) * 3 * 128 * 4;
+}
+
+int kfa_fwd(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* out, float* lse,
+            float scale, int block, int dtype, int* dev_status, void* stream) {
+  int rc;
+  if ((rc = check_qkv(q, k, v, dtype, block)) || (rc = check_like(out, q, "out"))) return rc;
+  if (!lse || !dev_status) return fail(KFA_ERR_ARG, "lse / dev_status: null pointer");
+  CUtensorMap mq, mk, mv;
+  if ((rc = make_map(q, dtype, &mq, "q")) || (rc = make_map(k, dtype, &mk, "k")) || (rc = make_map(v, dtype, &mv, "v")))
+    return rc;
+  kfa::FwdParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.o = out->ptr;
+  p.o_sb = out->stride[0];
+  p.o_sh = out->stride[1];
+  p.o_ss = out->stride[2];
+  p.lse = lse;
+  p.B = static_cast<int>(q->shape[0]);
+  p.H = static_cast<int>(q->shape[1]);
+  p.Sq = static_cast<int>(q->shape[2]);
+  p.Skv = static_cast<int>(k->shape[2]);
+  p.P = block;
+  p.c = scale * LOG2E;
+  p.n_q_tiles = (p.Sq + 255) / 256;
+  p.status = dev_status;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  KFA_DISPATCH(q->shape[3], dtype, (launch_fwd<KD, KB>(mq, mk, mv, p, s)));
+}
+
+int kfa_bwd_prepare(const KfaTensor4* out, const KfaTensor4* dout, const float* lse, float* stats, int dtype,
+                    void* stream) {
+  int rc;
+  if ((rc = check_tensor(out, "out")) || (rc = check_like(dout, out, "dout"))) return rc;
+  if (!lse || !stats) return fail(KFA_ERR_ARG, "lse / stats: null pointer");
+  if (dtype != KFA_F16 && dtype != KFA_BF16) return fail(KFA_ERR_ARG, "dtype %d", dtype);
+  const int64_t D = out->shape[3];
+  if (D != 64 && D != 128) return fail(KFA_ERR_ARG, "head_dim %lld: 64 or 128", (long long)D);
+  kfa::PrepParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.o = out->ptr;
+  p.o_sb = out->stride[0];
+  p.o_sh = out->stride[1];
+  p.o_ss = out->stride[2];
+  p.dout = dout->ptr;
+  p.do_sb = dout->stride[0];
+  p.do_sh = dout->stride[1];
+  p.do_ss = dout->stride[2];
+  p.lse = lse;
+  p.stats = stats;
+  p.B = static_cast<int>(out->shape[0]);
+  p.H = static_cast<int>(out->shape[1]);
+  p.Sq = static_cast<int>(out->shape[2]);
+  p.n_q128 = (p.Sq + 127) / 128;
+  if (static_cast<long long>(p.B) * p.H > 65535) return fail(KFA_ERR_ARG, "B * H > 65535");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  KFA_DISPATCH(D, dtype, (launch_prepare<KD, KB>(p, s)));
+}
+
+int kfa_bwd_dkdv(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* dout,
+                 const float* stats, const KfaTensor4* dk, const KfaTensor4* dv, float scale, int block, int dtype,
+                 int* dev_status, void* stream) {
+  int rc;
+  if ((rc = check_qkv(q, k, v, dtype, block)) || (rc = check_like(dout, q, "dout")) ||
+      (rc = check_like(dk, k, "dk")) || (rc = check_like(dv, v, "dv")))
+    return rc;
+  if (!stats || !dev_status) return fail(KFA_ERR_ARG, "stats / dev_status: null pointer");
+  CUtensorMap mq, mk, mv, mdo;
+  if ((rc = make_map(q, dtype, &mq, "q")) || (rc = make_map(k, dtype, &mk, "k")) ||
+      (rc = make_map(v, dtype, &mv, "v")) || (rc = make_map(dout, dtype, &mdo, "dout")))
+    return rc;
+  kfa::BwdParams p;
+  fill_bwd_params(p, q, k, stats, scale, block, dev_status);
+  p.dk = dk->ptr;
+  p.dk_sb = dk->stride[0];
+  p.dk_sh = dk->stride[1];
+  p.dk_ss = dk->stride[2];
+  p.dv = dv->ptr;
+  p.dv_sb = dv->stride[0];
+  p.dv_sh = dv->stride[1];
+  p.dv_ss = dv->stride[2];
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  KFA_DISPATCH(q->shape[3], dtype, (launch_dkdv<KD, KB>(mq, mk, mv, mdo, p, s)));
+}
+
+int kfa_bwd_dq(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* dout,
+               const float* stats, const KfaTensor4* dq, float scale, int block, int dtype, int* dev_status,
+               void* stream) {
+  int rc;
+  if ((rc = check_qkv(q, k, v, dtype, block)) || (rc = check_like(dout, q, "dout")) ||
+      (rc = check_like(dq, q, "dq")))
+    return rc;
+  if (!stats || !dev_status) return fail(KFA_ERR_ARG, "stats / dev_status: null pointer");
+  CUtensorMap mq, mk, mv, mdo;
+  if ((rc = make_map(q, dtype, &mq, "q")) || (rc = make_map(k, dtype, &mk, "k")) ||
+      (rc = make_map(v, dtype, &mv, "v")) || (rc = make_map(dout, dtype, &mdo, "dout")))
+    return rc;
+  kfa::BwdParams p;
+  fill_bwd_params(p, q, k, stats, scale, block, dev_status);
+  p.dq = dq->ptr;
+  p.dq_sb = dq->stride[0];
+  p.dq_sh = dq->stride[1];
+  p.dq_ss = dq->stride[2];
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  KFA_DISPATCH(q->shape[3], dtype, (launch_dq<KD, KB>(mq, mk, mv, mdo, p, s)));
+}
+
+int kfa_bwd(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* out,
+            const KfaTensor4* dout, const float* lse, float* stats, const KfaTensor4* dq, const KfaTensor4* dk,
+            const KfaTensor4* dv, float scale, int block, int dtype, int* dev_status, void* stream) {
+  int rc;
+  if ((rc = check_like(out, q, "out"))) return rc;
+  if ((rc = kfa_bwd_prepare(out, dout, lse, stats, dtype, stream))) return rc;
+  if ((rc = kfa_bwd_dkdv(q, k, v, dout, stats, dk, dv, scale, block, dtype, dev_status, stream))) return rc;
+  return kfa_bwd_dq(q, k, v, dout, stats, dq, scale, block, dtype, dev_status, stream);
+}
+
+}  // extern "C"
+
+#include "kfa_selftest.cuh"

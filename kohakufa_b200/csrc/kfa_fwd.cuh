@@ -1,0 +1,386 @@
+// Attention forward for sm_100a: O = softmax(scale * Q K^T + mask) V, plus the two per-row
+// statistics m (row max of the raw, unscaled scores) and log2(l), l = sum exp2((S - m) * c),
+// c = scale * log2(e).
+//
+// Replaces the reference's Gluon forward (src/kohakufa/sm100/fwd.py:1065-1136 kernel,
+// 578-1039 partitions, 76-418 tile scheduler) with a hand-written kernel:
+//
+//   CTA = 256 query rows of one (batch, head), as two 128-row halves; key tiles of 128.
+//   warps 0-3   softmax + correction + epilogue for half 0   (thread t <-> query row t)
+//   warps 4-7   the same for half 1
+//   warp  8     MMA issue (one thread): S_h = Q_h K_j^T, O_h += P_h V_j      (tcgen05, TMEM)
+//   warp  9     TMA producer (one thread): Q halves once, K_j / V_j through a ring
+//
+//   TMEM columns: S0 [0,128)  S1 [128,256)  O0 [256,256+D)  O1 [256+D,256+2D).
+//   P_h (16-bit) overwrites the first 64 columns of S_h and is the A operand of O_h += P V.
+//
+// Numerics kept from the reference (docs/precision.md:17-114; fwd.py:785-790, 905-924, 1029-1038):
+//   * the exponent is shift-then-scale, exp2((S - m) * c): the row's largest P is exactly 1;
+//   * m is the running max of the raw scores, with an exact rescale of O whenever it moves;
+//   * l sums the unrounded fp32 P; m and log2(l) are stored as two separate fp32 numbers.
+// Hidden key tiles of a causal / block-causal problem are never loaded: the key loop of a
+// half stops at its last visible tile (fwd.py:243, 265).
+#pragma once
+
+#include "kfa_ptx.cuh"
+
+namespace kfa {
+
+struct FwdParams {
+  void* o;  // [B, H, Sq, D] view; element strides; last dim contiguous
+  long long o_sb, o_sh, o_ss;
+  float* lse;  // [B, H, 2, Sq]: plane 0 = m, plane 1 = log2(l)
+  int B, H, Sq, Skv;
+  int P;    // 0 dense; P > 0: key c visible to query r iff c / P <= r / P
+  float c;  // scale * log2(e)
+  int n_q_tiles;
+  int* status;
+};
+
+constexpr int FWD_THREADS = 320;
+constexpr int TILE_BYTES_64 = 128 * 64 * 2;  // one 128-row x 64-column 16-bit box = 16 KB
+
+template <int D>
+struct FwdCfg {
+  static constexpr int CHUNKS = D / 64;
+  static constexpr int TILE_BYTES = CHUNKS * TILE_BYTES_64;
+  static constexpr int STAGES = (D == 128) ? 4 : 6;
+  static constexpr int SMEM_TILES = 2 * TILE_BYTES + STAGES * TILE_BYTES;
+  static constexpr int SMEM_BYTES = SMEM_TILES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr uint32_t TMEM_COLS = 512;
+  static constexpr uint32_t TM_S0 = 0, TM_S1 = 128, TM_O0 = 256, TM_O1 = 256 + D;
+};
+
+// Keys visible to query row r: [0, key_limit).
+__device__ __forceinline__ int key_limit(int r, int P, int Skv) {
+  if (P <= 0) return Skv;
+  long long lim = (static_cast<long long>(r / P) + 1) * P;
+  return lim < Skv ? static_cast<int>(lim) : Skv;
+}
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(FWD_THREADS, 1)
+kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+               const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
+  using Cfg = FwdCfg<D>;
+  constexpr int CH = Cfg::CHUNKS;
+  constexpr int NS = Cfg::STAGES;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t sQ = smem_base;                        // [half][chunk] 16 KB boxes
+  const uint32_t sKV = smem_base + 2 * Cfg::TILE_BYTES;  // [stage][chunk]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::SMEM_TILES);
+  // barrier indices
+  constexpr int B_QREADY = 0;             // 2
+  constexpr int B_KVREADY = 2;            // NS
+  constexpr int B_KVFREE = 2 + NS;        // NS
+  constexpr int B_SREADY = 2 + 2 * NS;    // 2
+  constexpr int B_PREADY = 4 + 2 * NS;    // 2
+  constexpr int B_OFINAL = 6 + 2 * NS;    // 2
+  constexpr int B_DRAIN = 8 + 2 * NS;     // 1
+  constexpr int N_BARS = 9 + 2 * NS;
+  static_assert(N_BARS * 8 + 16 <= 256, "barrier block too small");
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + N_BARS);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+  const uint32_t bar0 = smem_u32(bars);
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  // ---- tile decode: head-major, heaviest query tile of a head first when causal ----
+  const int bh = blockIdx.x / p.n_q_tiles;
+  const int t = blockIdx.x % p.n_q_tiles;
+  const int q_tile = (p.P > 0) ? (p.n_q_tiles - 1 - t) : t;
+  const int b = bh / p.H;
+  const int h = bh % p.H;
+  const int row0 = q_tile * 256;
+
+  int n_tiles[2], n_unmasked[2];
+#pragma unroll
+  for (int hf = 0; hf < 2; ++hf) {
+    const int first = row0 + 128 * hf;
+    if (first < p.Sq) {
+      const int last = min(first + 127, p.Sq - 1);
+      n_tiles[hf] = (key_limit(last, p.P, p.Skv) + 127) / 128;
+      n_unmasked[hf] = key_limit(first, p.P, p.Skv) / 128;
+    } else {
+      n_tiles[hf] = 0;
+      n_unmasked[hf] = 0;
+    }
+  }
+  const int n_max = max(n_tiles[0], n_tiles[1]);
+
+  // ---- setup ----
+  if (tid == 0) {
+    mbar_init(bar(B_QREADY + 0), 1);
+    mbar_init(bar(B_QREADY + 1), 1);
+    for (int i = 0; i < NS; ++i) {
+      mbar_init(bar(B_KVREADY + i), 1);
+      mbar_init(bar(B_KVFREE + i), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(B_SREADY + i), 1);
+      mbar_init(bar(B_PREADY + i), 128);
+      mbar_init(bar(B_OFINAL + i), 1);
+    }
+    mbar_init(bar(B_DRAIN), 1);
+    // An earlier failure (status word already set): allocate, skip the work, free.
+    *s_abort = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(s_tmem), Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *s_tmem;
+  const Ctl ctl{s_abort, p.status};
+  const bool dead = (*s_abort != 0);
+
+  if (dead) {
+    // nothing to do
+  } else if (warp == 9) {
+    // =========================== TMA producer ===========================
+    if (lane == 0) {
+      prefetch_tensormap(&tmQ);
+      prefetch_tensormap(&tmK);
+      prefetch_tensormap(&tmV);
+      for (int hf = 0; hf < 2; ++hf) {
+        if (n_tiles[hf] == 0) continue;
+        mbar_expect_tx(bar(B_QREADY + hf), Cfg::TILE_BYTES);
+        for (int ch = 0; ch < CH; ++ch)
+          tma_load_4d(sQ + (hf * CH + ch) * TILE_BYTES_64, &tmQ, bar(B_QREADY + hf), ch * 64,
+                      row0 + 128 * hf, h, b);
+      }
+      int armed[NS];  // last use index armed per stage (for the drain on abort)
+      for (int i = 0; i < NS; ++i) armed[i] = -1;
+      bool ok = true;
+      for (int idx = 0; idx < 2 * n_max && ok; ++idx) {
+        const int j = idx >> 1;
+        const int stage = idx % NS;
+        const int use = idx / NS;
+        if (use > 0) ok = mbar_wait(bar(B_KVFREE + stage), (use - 1) & 1, ctl, 1);
+        if (!ok) break;
+        mbar_expect_tx(bar(B_KVREADY + stage), Cfg::TILE_BYTES);
+        const CUtensorMap* map = (idx & 1) ? &tmV : &tmK;
+        for (int ch = 0; ch < CH; ++ch)
+          tma_load_4d(sKV + (stage * CH + ch) * TILE_BYTES_64, map, bar(B_KVREADY + stage), ch * 64,
+                      j * 128, h, b);
+        armed[stage] = use;
+      }
+      if (!ok) {
+        // Aborting: let the copies already in flight land before the CTA gives up its smem.
+        for (int i = 0; i < NS; ++i)
+          if (armed[i] >= 0) {
+            const long long t0 = clock64();
+            while (!mbar_try_wait(bar(B_KVREADY + i), armed[i] & 1) && clock64() - t0 < 2000000ll) {
+            }
+          }
+      }
+    }
+  } else if (warp == 8) {
+    // =========================== MMA issue ===========================
+    if (lane == 0) {
+      constexpr uint32_t IDESC_S = make_idesc(BF16, false, 128, 128);
+      constexpr uint32_t IDESC_O = make_idesc(BF16, true, 128, D);
+      const uint32_t tmS[2] = {tmem + Cfg::TM_S0, tmem + Cfg::TM_S1};
+      const uint32_t tmO[2] = {tmem + Cfg::TM_O0, tmem + Cfg::TM_O1};
+      bool ok = true;
+
+      auto issue_S = [&](int hf, int stage) {
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * TILE_BYTES_64 + (kk & 3) * 32;
+          const uint64_t a = make_sdesc(sQ + hf * Cfg::TILE_BYTES + off, 16, 1024);
+          const uint64_t bd = make_sdesc(sKV + stage * Cfg::TILE_BYTES + off, 16, 1024);
+          umma_ss(tmS[hf], a, bd, IDESC_S, kk > 0);
+        }
+      };
+      auto issue_PV = [&](int hf, int stage, bool acc) {
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint64_t bd =
+              make_sdesc(sKV + stage * Cfg::TILE_BYTES + kk * 2048, TILE_BYTES_64, 1024);
+          umma_ts(tmO[hf], tmS[hf] + kk * 8, bd, IDESC_O, (acc || kk > 0) ? 1u : 0u);
+        }
+      };
+      auto kv_wait = [&](int idx) {
+        return mbar_wait(bar(B_KVREADY + idx % NS), (idx / NS) & 1, ctl, 2);
+      };
+
+      // S(0) for both halves
+      ok = kv_wait(0);
+      for (int hf = 0; hf < 2 && ok; ++hf) {
+        if (n_tiles[hf] == 0) continue;
+        ok = mbar_wait(bar(B_QREADY + hf), 0, ctl, 3);
+        if (!ok) break;
+        tc_fence_after();
+        issue_S(hf, 0);
+        umma_commit(bar(B_SREADY + hf));
+      }
+      if (ok) umma_commit(bar(B_KVFREE + 0));
+
+      for (int j = 0; j < n_max && ok; ++j) {
+        const int iv = 2 * j + 1;  // V_j
+        const int ik = 2 * j + 2;  // K_{j+1}
+        const bool more = (j + 1 < n_max);
+        ok = kv_wait(iv);
+        if (!ok) break;
+        if (more) {
+          ok = kv_wait(ik);
+          if (!ok) break;
+        }
+        for (int hf = 0; hf < 2 && ok; ++hf) {
+          if (j < n_tiles[hf]) {
+            ok = mbar_wait(bar(B_PREADY + hf), j & 1, ctl, 4);
+            if (!ok) break;
+            tc_fence_after();
+            issue_PV(hf, iv % NS, j > 0);
+            if (j == n_tiles[hf] - 1) umma_commit(bar(B_OFINAL + hf));
+          }
+          if (hf == 1) umma_commit(bar(B_KVFREE + iv % NS));
+          if (more && j + 1 < n_tiles[hf]) {
+            issue_S(hf, ik % NS);
+            umma_commit(bar(B_SREADY + hf));
+          }
+          if (more && hf == 1) umma_commit(bar(B_KVFREE + ik % NS));
+        }
+      }
+      // Everything issued has to retire before TMEM is freed.
+      umma_commit(bar(B_DRAIN));
+      {
+        const long long t0 = clock64();
+        while (!mbar_try_wait(bar(B_DRAIN), 0) && clock64() - t0 < KFA_WAIT_CYCLES) {
+        }
+      }
+    }
+  } else {
+    // =========================== softmax / correction / epilogue ===========================
+    const int hf = warp >> 2;
+    const int r_in = tid & 127;
+    const int row = row0 + 128 * hf + r_in;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tS = tmem + (hf ? Cfg::TM_S1 : Cfg::TM_S0) + lane_base;
+    const uint32_t tO = tmem + (hf ? Cfg::TM_O1 : Cfg::TM_O0) + lane_base;
+    const int nt = n_tiles[hf];
+    const int nu = n_unmasked[hf];
+    const int my_limit = key_limit(min(row, p.Sq - 1), p.P, p.Skv);
+    const float c = p.c;
+
+    float m = -INFINITY;
+    float l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nt; ++j) {
+      ok = mbar_wait_warp(bar(B_SREADY + hf), j & 1, ctl, 5);
+      if (!ok) break;
+      tc_fence_after();
+      float s[128];
+      tmem_ld32(tS + 0, reinterpret_cast<uint32_t*>(s));
+      tmem_ld32(tS + 32, reinterpret_cast<uint32_t*>(s + 32));
+      tmem_ld32(tS + 64, reinterpret_cast<uint32_t*>(s + 64));
+      tmem_ld32(tS + 96, reinterpret_cast<uint32_t*>(s + 96));
+      tmem_wait_ld();
+      if (j >= nu) {
+        const int lim = my_limit - j * 128;
+#pragma unroll
+        for (int i = 0; i < 128; ++i)
+          if (i >= lim) s[i] = -INFINITY;
+      }
+      float mx0 = s[0], mx1 = s[1], mx2 = s[2], mx3 = s[3];
+#pragma unroll
+      for (int i = 4; i < 128; i += 4) {
+        mx0 = fmaxf(mx0, s[i]);
+        mx1 = fmaxf(mx1, s[i + 1]);
+        mx2 = fmaxf(mx2, s[i + 2]);
+        mx3 = fmaxf(mx3, s[i + 3]);
+      }
+      const float m_new = fmaxf(fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)), m);
+      // Shift first, then scale: the largest exponent of the row is exactly 0.
+      const float alpha = ex2(__fmul_rn(__fsub_rn(m, m_new), c));
+      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          const float p0 = ex2(__fmul_rn(__fsub_rn(s[g * 32 + i], m_new), c));
+          const float p1 = ex2(__fmul_rn(__fsub_rn(s[g * 32 + i + 1], m_new), c));
+          const float p2 = ex2(__fmul_rn(__fsub_rn(s[g * 32 + i + 2], m_new), c));
+          const float p3 = ex2(__fmul_rn(__fsub_rn(s[g * 32 + i + 3], m_new), c));
+          l0 += p0;
+          l1 += p1;
+          l2 += p2;
+          l3 += p3;
+          pk[i / 2] = pack16<BF16>(p0, p1);
+          pk[i / 2 + 1] = pack16<BF16>(p2, p3);
+        }
+        tmem_st16(tS + g * 16, pk);  // P over the S columns already read
+      }
+      l = l * alpha + ((l0 + l1) + (l2 + l3));
+      m = m_new;
+      // Exact rescale of O whenever any row of this warp moved its max. S_h(j) being ready
+      // implies O_h += P V of tile j-1 has retired (commits cover all earlier MMAs).
+      if (j > 0 && !__all_sync(0xffffffffu, alpha == 1.0f)) {
+#pragma unroll
+        for (int cc = 0; cc < D; cc += 32) {
+          float o[32];
+          tmem_ld32(tO + cc, reinterpret_cast<uint32_t*>(o));
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] *= alpha;
+          tmem_st32(tO + cc, reinterpret_cast<uint32_t*>(o));
+        }
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar(B_PREADY + hf));
+    }
+    // ---- epilogue ----
+    if (nt > 0) ok = mbar_wait_warp(bar(B_OFINAL + hf), 0, ctl, 6) && ok;
+    if (ok && nt > 0) {
+      tc_fence_after();
+      const float inv = 1.0f / l;
+      const bool valid = row < p.Sq;
+      uint8_t* orow = reinterpret_cast<uint8_t*>(p.o) +
+                      2 * (b * p.o_sb + h * p.o_sh + static_cast<long long>(row) * p.o_ss);
+#pragma unroll
+      for (int cc = 0; cc < D; cc += 32) {
+        float o[32];
+        tmem_ld32(tO + cc, reinterpret_cast<uint32_t*>(o));
+        tmem_wait_ld();
+        if (valid) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 w;
+            w.x = pack16<BF16>(o[i] * inv, o[i + 1] * inv);
+            w.y = pack16<BF16>(o[i + 2] * inv, o[i + 3] * inv);
+            w.z = pack16<BF16>(o[i + 4] * inv, o[i + 5] * inv);
+            w.w = pack16<BF16>(o[i + 6] * inv, o[i + 7] * inv);
+            *reinterpret_cast<uint4*>(orow + 2 * (cc + i)) = w;
+          }
+        }
+      }
+      if (valid) {
+        float* lse = p.lse + (static_cast<long long>(b) * p.H + h) * 2 * p.Sq;
+        lse[row] = m;
+        lse[p.Sq + row] = log2f(l);
+      }
+    }
+  }
+
+  // ---- teardown (every thread gets here, also after an abort) ----
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem, Cfg::TMEM_COLS);
+  }
+}
+
+}  // namespace kfa

@@ -1,0 +1,169 @@
+"""The sm_100a kernels as torch custom ops with autograd: ``attention(q, k, v, scale, block_causal)``.
+
+Mirrors the operator boundary of the reference (KohakuFA ``src/kohakufa/sm100/op.py:41-175``):
+
+    q [B, H, Sq, D], k / v [B, H, Skv, D], fp16 or bf16 (views of [B, S, H, D] projections are
+    fine: any strides with a contiguous last dim and 16-byte aligned strides), D = 64 or 128.
+    scale: softmax scale (None -> D ** -0.5). block_causal: frame size P (query i sees key j iff
+    j // P <= i // P), 0 for dense attention.
+    Returns out [B, H, Sq, D], a view of [B, Sq, H, D] storage.
+
+The ops live in their own namespace (``kohakufa_b200::sm100_forward`` / ``_backward``; the
+reference registers ``kohakufa::sm100_*``), so both packages can be imported side by side.
+Their bodies call ``libkfa.so`` through ctypes on the current stream: no host synchronisation,
+every buffer from the caching allocator, so ``torch.compile`` keeps them in the graph and CUDA
+graph capture works (after one eager call on the device, which creates the status word).
+
+Extra memory: forward statistics (row max and log2 sum, fp32 [B, H, 2, Sq]); backward
+(m, log2 l, delta) per query row (fp32, padded to 128 rows) while it runs.
+"""
+
+import ctypes
+
+import torch
+from torch import Tensor
+
+from kohakufa_b200 import _lib
+
+KERNEL_DIMS = (64, 128)  # head dims the kernels are built for; the API zero-pads up to one
+MAX_KERNEL_DIM = 128
+
+
+def _strides_ok(t: Tensor) -> bool:
+    if t.stride(-1) != 1 or (t.storage_offset() * 2) % 16:
+        return False
+    return all(s > 0 and (s * 2) % 16 == 0 for n, s in zip(t.shape[:-1], t.stride()[:-1]) if n > 1)
+
+
+def _check(q: Tensor, k: Tensor, v: Tensor) -> None:
+    """Same conditions and exception types as the reference's ``_check`` (op.py:41-55), with the
+    head dims and head counts this build supports."""
+    if q.dtype not in (torch.float16, torch.bfloat16) or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise TypeError("attention: q, k, v must be fp16 or bf16 (all the same)")
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+        raise ValueError("attention: q, k, v must be [B, H, S, D]")
+    dim = q.shape[-1]
+    if dim not in KERNEL_DIMS:
+        raise ValueError(f"attention: kernel head_dim {dim}: one of {KERNEL_DIMS}")
+    if k.shape != v.shape or k.shape[0] != q.shape[0] or k.shape[-1] != q.shape[-1]:
+        raise ValueError(f"attention: k {tuple(k.shape)} / v {tuple(v.shape)} vs q {tuple(q.shape)}")
+    if q.shape[1] % k.shape[1]:
+        raise ValueError("attention: query heads must be a multiple of K / V heads (GQA)")
+    if q.shape[1] != k.shape[1]:
+        raise NotImplementedError("attention: grouped-query attention (H != Hkv) is not built yet")
+    if not q.is_cuda:
+        raise ValueError("attention: CUDA tensors only (there is no CPU path)")
+    for t in (q, k, v):
+        if not _strides_ok(t):
+            raise ValueError("attention: inputs need a contiguous last dim and 16-byte strides")
+
+
+def _bshd_like(t: Tensor) -> Tensor:
+    batch, heads, seq, dim = t.shape
+    return t.new_empty(batch, seq, heads, dim).transpose(1, 2)
+
+
+@torch.library.custom_op("kohakufa_b200::sm100_forward", mutates_args=(), device_types="cuda")
+def attention_fwd_op(q: Tensor, k: Tensor, v: Tensor, scale: float, block: int) -> tuple[Tensor, Tensor]:
+    lib = _lib.load()
+    batch, heads, seq_q, _ = q.shape
+    out = _bshd_like(q)
+    lse = q.new_empty(batch, heads, 2, seq_q, dtype=torch.float32)
+    with torch.cuda.device(q.device):
+        rc = lib.kfa_fwd(
+            ctypes.byref(_lib.tensor4(q)),
+            ctypes.byref(_lib.tensor4(k)),
+            ctypes.byref(_lib.tensor4(v)),
+            ctypes.byref(_lib.tensor4(out)),
+            lse.data_ptr(),
+            float(scale),
+            int(block),
+            _lib.dtype_code(q.dtype),
+            _lib.status_word(q.device).data_ptr(),
+            _lib.stream_ptr(q.device),
+        )
+    _lib.check(rc)
+    return out, lse
+
+
+@attention_fwd_op.register_fake
+def _(q, k, v, scale, block):
+    batch, heads, seq_q, dim = q.shape
+    out = q.new_empty(batch, seq_q, heads, dim).transpose(1, 2)
+    lse = q.new_empty(batch, heads, 2, seq_q, dtype=torch.float32)
+    return out, lse
+
+
+@torch.library.custom_op("kohakufa_b200::sm100_backward", mutates_args=(), device_types="cuda")
+def attention_bwd_op(
+    q: Tensor, k: Tensor, v: Tensor, out: Tensor, dout: Tensor, lse: Tensor, scale: float, block: int
+) -> tuple[Tensor, Tensor, Tensor]:
+    lib = _lib.load()
+    batch, heads, seq_q, _ = q.shape
+    dq, dk, dv = _bshd_like(q), _bshd_like(k), _bshd_like(v)
+    stats = q.new_empty(lib.kfa_bwd_stats_bytes(batch, heads, seq_q) // 4, dtype=torch.float32)
+    with torch.cuda.device(q.device):
+        rc = lib.kfa_bwd(
+            ctypes.byref(_lib.tensor4(q)),
+            ctypes.byref(_lib.tensor4(k)),
+            ctypes.byref(_lib.tensor4(v)),
+            ctypes.byref(_lib.tensor4(out)),
+            ctypes.byref(_lib.tensor4(dout)),
+            lse.data_ptr(),
+            stats.data_ptr(),
+            ctypes.byref(_lib.tensor4(dq)),
+            ctypes.byref(_lib.tensor4(dk)),
+            ctypes.byref(_lib.tensor4(dv)),
+            float(scale),
+            int(block),
+            _lib.dtype_code(q.dtype),
+            _lib.status_word(q.device).data_ptr(),
+            _lib.stream_ptr(q.device),
+        )
+    _lib.check(rc)
+    return dq, dk, dv
+
+
+@attention_bwd_op.register_fake
+def _(q, k, v, out, dout, lse, scale, block):
+    return _bshd_like(q), _bshd_like(k), _bshd_like(v)
+
+
+def _setup_context(ctx, inputs, output):
+    q, k, v, scale, block = inputs
+    out, lse = output
+    ctx.save_for_backward(q, k, v, out, lse)
+    ctx.scale = scale
+    ctx.block = block
+    ctx.mark_non_differentiable(lse)
+
+
+def _backward(ctx, dout, dlse):
+    q, k, v, out, lse = ctx.saved_tensors
+    if not _strides_ok(dout):  # e.g. an expanded gradient: same rule as the reference (op.py:135-136)
+        dout = dout.contiguous()
+    dq, dk, dv = attention_bwd_op(q, k, v, out, dout, lse, ctx.scale, ctx.block)
+    return dq, dk, dv, None, None
+
+
+attention_fwd_op.register_autograd(_backward, setup_context=_setup_context)
+
+
+def attention(
+    q: Tensor,
+    k: Tensor,
+    v: Tensor,
+    scale: float | None = None,
+    block_causal: int = 0,
+    mask: Tensor | None = None,
+) -> Tensor:
+    """``softmax(scale q k^T) v`` over ``[B, H, S, D]``; ``block_causal > 0``: tokens of block ``i``
+    (``block_causal`` consecutive tokens) see blocks ``0..i`` only. ``mask`` (a boolean mask in the
+    reference, op.py:146-175) is not built."""
+    if mask is not None:
+        raise NotImplementedError("attention: boolean masks are not built yet")
+    _check(q, k, v)
+    if scale is None:
+        scale = q.shape[-1] ** -0.5
+    out, _ = attention_fwd_op(q, k, v, float(scale), int(block_causal))
+    return out

@@ -1,0 +1,30 @@
+"""pytest configuration: the ``gpu`` marker, and a guard that keeps GPU tests honest.
+
+``-m "not gpu"`` runs everywhere (oracle vs golden vectors, host logic, library symbols).
+``-m gpu`` needs a B200: those tests call the CUDA path through the C ABI and fail, not skip,
+if the library is missing.
+"""
+
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device of compute capability 10.x (B200)")
+
+
+def pytest_collection_modifyitems(config, items):
+    import torch
+
+    if torch.cuda.is_available():
+        return
+    skip = pytest.mark.skip(reason="no CUDA device")
+    for item in items:
+        if "gpu" in item.keywords:
+            item.add_marker(skip)

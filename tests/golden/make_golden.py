@@ -1,0 +1,102 @@
+"""Generates the golden fixtures that pin ``oracle/reference.py`` to the reference's own code.
+
+Run once where the reference checkout is available:
+
+    python tests/golden/make_golden.py /path/to/KohakuFA
+
+It imports the reference's ``tests/reference.py`` (fp64 attention + metrics) and
+``benchmarks/dinov3_backward.py`` (``emulated_grads``, the correct-kernel rounding floor and its
+bug variants), runs them on small seeded CPU inputs and stores inputs' recipe + outputs in
+``tests/golden/*.npz``. The fixtures travel with the repository; the reference does not.
+"""
+
+import importlib.util
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+
+# name -> (B, H, Sq, Skv, D, dtype, block, seed, input std)
+ATTENTION_CASES = {
+    "dense_f16": (2, 1, 40, 40, 64, "float16", 0, 11, 1.0),
+    "causal_f16": (1, 2, 77, 77, 64, "float16", 1, 12, 1.0),
+    "block7_f16": (1, 2, 50, 50, 32, "float16", 7, 13, 1.0),
+    "causal_sq_lt_skv": (1, 2, 33, 70, 64, "float16", 1, 14, 1.0),
+    "causal_sq_gt_skv": (1, 2, 70, 33, 64, "float16", 1, 15, 1.0),
+    "block24_bf16": (1, 1, 61, 61, 128, "bfloat16", 24, 16, 0.5),
+    "dense_cross_bf16": (1, 1, 19, 45, 128, "bfloat16", 0, 17, 1.0),
+}
+# name -> (B, H, S, D, dtype, seed, magnitude of q and k)
+FLOOR_CASES = {
+    "floor_f16": (1, 1, 40, 64, "float16", 21, 1.0),
+    "floor_bf16": (1, 1, 40, 64, "bfloat16", 22, 1.0),
+    "floor_large_f16": (1, 1, 40, 64, "float16", 23, 30.0),
+    "floor_large_bf16": (1, 1, 40, 64, "bfloat16", 24, 30.0),
+}
+BUG_SETS = {"floor": (), "scale_ds": ("scale*dS",), "single_lse": ("single lse",), "scale_shift": ("scale-shift",)}
+
+
+def make_attention_inputs(case):
+    b, h, sq, skv, d, dtype, block, seed, std = case
+    gen = torch.Generator().manual_seed(seed)
+    dt = getattr(torch, dtype)
+    q = (torch.randn(b, h, sq, d, generator=gen) * std).to(dt)
+    k = (torch.randn(b, h, skv, d, generator=gen) * std).to(dt)
+    v = (torch.randn(b, h, skv, d, generator=gen) * std).to(dt)
+    dout = (torch.randn(b, h, sq, d, generator=gen) * std).to(dt)
+    return q, k, v, dout
+
+
+def make_floor_inputs(case):
+    b, h, s, d, dtype, seed, mag = case
+    gen = torch.Generator().manual_seed(seed)
+    dt = getattr(torch, dtype)
+    q = (torch.randn(b, h, s, d, generator=gen) * mag).to(dt)
+    k = (torch.randn(b, h, s, d, generator=gen) * mag).to(dt)
+    v = torch.randn(b, h, s, d, generator=gen).to(dt)
+    dout = torch.randn(b, h, s, d, generator=gen).to(dt)
+    return q, k, v, dout
+
+
+def _load(path: Path, name: str):
+    spec = importlib.util.spec_from_file_location(name, path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def main(ref_root: str) -> None:
+    root = Path(ref_root)
+    ref = _load(root / "tests" / "reference.py", "kfa_ref_oracle")
+    out = {}
+    for name, case in ATTENTION_CASES.items():
+        q, k, v, dout = make_attention_inputs(case)
+        scale = case[4] ** -0.5
+        o, dq, dk, dv = ref.reference(q, k, v, dout, scale, block=case[6])
+        for key, val in zip(("out", "dq", "dk", "dv"), (o, dq, dk, dv)):
+            out[f"{name}/{key}"] = val.numpy()
+        # the reference's metrics() on a perturbed copy, to pin metrics too
+        noisy = o + 1e-3 * torch.randn(o.shape, generator=torch.Generator().manual_seed(5), dtype=torch.float64)
+        m = ref.metrics(noisy, o)
+        out[f"{name}/metrics"] = np.array([m["cos"], m["norm_ratio"], m["rel_err"], m["max_abs_err"], m["max_rel_err"]])
+    np.savez_compressed(HERE / "attention_fp64.npz", **out)
+
+    sys.path.insert(0, str(root / "benchmarks"))
+    emu = _load(root / "benchmarks" / "dinov3_backward.py", "kfa_ref_emulation")
+    out = {}
+    for name, case in FLOOR_CASES.items():
+        q, k, v, dout = make_floor_inputs(case)
+        inputs = {"q": q, "k": k, "v": v, "dout": dout, "scale": case[3] ** -0.5}
+        for tag, bugs in BUG_SETS.items():
+            dq, dk, dv = emu.emulated_grads(inputs, set(bugs))
+            for key, val in zip(("dq", "dk", "dv"), (dq, dk, dv)):
+                out[f"{name}/{tag}/{key}"] = val.numpy()
+    np.savez_compressed(HERE / "floor_emulation.npz", **out)
+    print("wrote", HERE / "attention_fp64.npz", HERE / "floor_emulation.npz")
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")

@@ -1,0 +1,346 @@
+"""GPU parity tests: ``kohakufa_b200.attention`` (CUDA kernels through the C ABI) against the fp64
+oracle on the same rounded inputs. Shapes and tolerances follow the reference's own test module
+(KohakuFA tests/test_attention.py: TOL / BF16_TOL lines 12, 166; CAUSAL / block / dense shape lists
+lines 50-85; bf16 combos 169-186; padded keys 129-141; huge logits 144-163; compile / CUDA graph
+88-116; fp32 inputs 119-126; head dims 363-379; center_keys 431-438)."""
+
+import pytest
+import torch
+
+from kohakufa_b200 import _lib, attention, workloads
+from oracle import reference as oracle
+
+pytestmark = pytest.mark.gpu
+
+TOL = 5e-3  # relative error (||got - fp64|| / ||fp64||) of out, dq, dk, dv in fp16
+BF16_TOL = 2e-2  # 8-bit mantissa
+
+
+def inputs(batch, heads, s_q, s_kv, dim=64, seed=0, dtype=torch.float16, std=1.0):
+    """q, k, v as [B, S, H, D] projections viewed as [B, H, S, D]; dout. Generated on the CPU."""
+    gen = torch.Generator().manual_seed(seed)
+
+    def projection(seq):
+        x = (torch.randn(batch, seq, heads, dim, generator=gen) * std).to(dtype)
+        return x.cuda().transpose(1, 2).requires_grad_()
+
+    dout = (torch.randn(batch, heads, s_q, dim, generator=gen) * std).to(dtype).cuda()
+    return projection(s_q), projection(s_kv), projection(s_kv), dout
+
+
+def run(q, k, v, dout, **kwargs):
+    for t in (q, k, v):
+        t.grad = None
+    out = attention(q, k, v, **kwargs)
+    out.backward(dout)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0, f"a kernel wait timed out: status {_lib.device_status()}"
+    return out, q.grad, k.grad, v.grad
+
+
+def check(got, want, tol=TOL):
+    for name, g, w in zip(("out", "dq", "dk", "dv"), got, want):
+        assert bool(torch.isfinite(g).all()), name
+        m = oracle.metrics(g, w)
+        if float(w.abs().max()) == 0.0:  # an exactly-zero gradient (e.g. one visible key)
+            assert m["max_abs_err"] < 1e-4, f"{name}: {m}"
+        else:
+            assert m["rel_err"] < tol, f"{name}: {m}"
+
+
+def want_for(q, k, v, dout, block=0, scale=None):
+    scale = q.shape[-1] ** -0.5 if scale is None else scale
+    return oracle.attention_fp64(q, k, v, dout, scale, block=block)
+
+
+def test_selftest():
+    report = _lib.selftest()
+    assert "exact" in report and "differ" not in report, report
+
+
+CAUSAL = [  # (batch, heads, s_q, s_kv)
+    (1, 1, 1, 1),
+    (1, 2, 127, 127),
+    (2, 2, 128, 128),
+    (1, 2, 129, 129),
+    (1, 1, 255, 255),
+    (2, 3, 256, 256),
+    (1, 2, 269, 269),
+    (1, 2, 1000, 1000),
+    (1, 2, 2048, 2048),
+    (1, 2, 300, 517),
+    (1, 2, 517, 300),
+    (2, 2, 257, 64),
+]
+
+
+@pytest.mark.parametrize("shape", CAUSAL)
+def test_causal(shape):
+    q, k, v, dout = inputs(*shape)
+    check(run(q, k, v, dout, causal=True), want_for(q, k, v, dout, block=1))
+
+
+@pytest.mark.parametrize("block", [1, 7, 24, 128, 129, 257])
+def test_block_causal(block):
+    q, k, v, dout = inputs(2, 3, 600, 600, seed=block)
+    check(run(q, k, v, dout, block_causal=block), want_for(q, k, v, dout, block=block))
+
+
+@pytest.mark.parametrize("block", [5, 128, 200])
+def test_block_causal_unseen_keys(block):
+    """Sq < Skv: keys of frames no query reaches get exactly-zero dK / dV."""
+    q, k, v, dout = inputs(1, 2, 130, 700, seed=3)
+    got = run(q, k, v, dout, block_causal=block)
+    want = want_for(q, k, v, dout, block=block)
+    check(got, want)
+    seen = min(((130 - 1) // block + 1) * block, 700)
+    assert float(got[2][:, :, seen:].abs().max() if seen < 700 else 0) == 0.0
+    assert float(got[3][:, :, seen:].abs().max() if seen < 700 else 0) == 0.0
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 5, 7), (1, 3, 269, 269), (2, 2, 131, 517), (2, 12, 1799, 1799)])
+def test_dense(shape):
+    q, k, v, dout = inputs(*shape, seed=1)
+    check(run(q, k, v, dout), want_for(q, k, v, dout))
+
+
+@pytest.mark.parametrize(
+    "shape,mode",
+    [
+        ((1, 2, 269, 269), {}),
+        ((2, 2, 600, 600), {"causal": True}),
+        ((1, 2, 600, 600), {"block_causal": 129}),
+        ((1, 2, 131, 517), {}),
+        ((1, 1, 1024, 1024), {"causal": True}),
+    ],
+)
+def test_bf16(shape, mode):
+    q, k, v, dout = inputs(*shape, seed=4, dtype=torch.bfloat16)
+    block = 1 if mode.get("causal") else mode.get("block_causal", 0)
+    check(run(q, k, v, dout, **mode), want_for(q, k, v, dout, block=block), tol=BF16_TOL)
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float16, TOL), (torch.bfloat16, BF16_TOL)])
+@pytest.mark.parametrize("mode", [{}, {"causal": True}, {"block_causal": 100}])
+def test_head_dim_128(dtype, tol, mode):
+    q, k, v, dout = inputs(2, 2, 389, 389, dim=128, seed=6, dtype=dtype, std=0.5)
+    block = 1 if mode.get("causal") else mode.get("block_causal", 0)
+    check(run(q, k, v, dout, **mode), want_for(q, k, v, dout, block=block), tol=tol)
+
+
+@pytest.mark.parametrize("dim", [8, 16, 40, 64, 72, 96, 128])
+@pytest.mark.parametrize("causal", [False, True])
+def test_head_dims(dim, causal):
+    q, k, v, dout = inputs(1, 2, 200, 200, dim=dim, seed=dim)
+    check(run(q, k, v, dout, causal=causal), want_for(q, k, v, dout, block=int(causal)))
+
+
+def test_config1_dense():
+    cfg = workloads.CONFIGS["C1"]
+    q, k, v, dout = (t.cuda() for t in workloads.make_inputs(cfg))
+    q, k, v = (t.requires_grad_() for t in (q, k, v))
+    check(run(q, k, v, dout), want_for(q, k, v, dout))
+
+
+def test_config4_partial_tiles_dense_4100():
+    """Dense at a length that is not a tile multiple (one batch x two heads of the C4 variant)."""
+    cfg = workloads.CONFIGS["C4-dense4100"]
+    q, k, v, dout = (t.cuda() for t in workloads.make_inputs(cfg, batch=1, heads=2))
+    q, k, v = (t.requires_grad_() for t in (q, k, v))
+    check(run(q, k, v, dout), want_for(q, k, v, dout))
+
+
+def test_config4_block_causal_slice():
+    cfg = workloads.CONFIGS["C4"]
+    q, k, v, dout = (t.cuda() for t in workloads.make_inputs(cfg, batch=1, heads=2))
+    q, k, v = (t.requires_grad_() for t in (q, k, v))
+    check(run(q, k, v, dout, block_causal=cfg.block), want_for(q, k, v, dout, block=cfg.block))
+
+
+def test_config3_causal_slice():
+    """One batch x one head of C3 (bf16, S=8192, D=128) against fp64 on the GPU."""
+    cfg = workloads.CONFIGS["C3"]
+    q, k, v, dout = (t.cuda() for t in workloads.make_inputs(cfg, batch=1, heads=1))
+    q, k, v = (t.requires_grad_() for t in (q, k, v))
+    check(run(q, k, v, dout, causal=True), want_for(q, k, v, dout, block=1), tol=BF16_TOL)
+
+
+def test_fp32_inputs_cast():
+    q, k, v, dout = inputs(1, 2, 269, 269, dtype=torch.float32)
+    out = attention(q, k, v, causal=True)
+    assert out.dtype == torch.float32
+    out.backward(dout)
+    want = want_for(*(t.half() for t in (q, k, v)), dout, block=1)
+    for name, g, w in zip(("out", "dq", "dk", "dv"), (out, q.grad, k.grad, v.grad), want):
+        assert oracle.metrics(g, w)["rel_err"] < 1e-2, name
+
+
+def test_padded_keys_with_all_negative_scores():
+    """Every score negative and Skv not a tile multiple: padded keys must not overflow in the
+    backward (dQ += dS K would be inf * 0)."""
+    gen = torch.Generator().manual_seed(1)
+    shape = (2, 269, 4, 64)
+    q = (4 * torch.randn(shape, generator=gen).abs()).half().cuda()
+    k = (-4 * torch.randn(shape, generator=gen).abs()).half().cuda()
+    v = torch.randn(shape, generator=gen).half().cuda()
+    q, k, v = (t.transpose(1, 2).requires_grad_() for t in (q, k, v))
+    dout = torch.randn(q.shape, generator=gen).half().cuda()
+    got = run(q, k, v, dout)
+    assert all(bool(torch.isfinite(g).all()) for g in got)
+    check(got, want_for(q, k, v, dout))
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("dim,mag", [(64, 400.0), (128, 300.0)])
+def test_huge_logits(causal, dim, mag):
+    """Near-one-hot rows with |scores| ~ 1e7: the backward's P must match the forward's (row max and
+    log2 l kept apart, shift before scale), so dV is exact and dK close. dQ is not checked: with
+    clustered keys it cancels to far below its terms for any 16-bit kernel."""
+    gen = torch.Generator().manual_seed(2)
+    centers = torch.randn(1, 2, 8, dim, generator=gen)
+    pick = torch.randint(0, 8, (1, 2, 269), generator=gen)
+    base = torch.gather(centers, 2, pick[..., None].expand(-1, -1, -1, dim))
+    q = mag * (base + 1e-3 * torch.randn(base.shape, generator=gen))
+    k = mag * (base + 1e-3 * torch.randn(base.shape, generator=gen))
+    v = torch.randn(base.shape, generator=gen)
+    q, k, v = (t.half().cuda().requires_grad_() for t in (q, k, v))
+    dout = torch.randn(base.shape, generator=gen).half().cuda()
+    got = run(q, k, v, dout, causal=causal)
+    want = want_for(q, k, v, dout, block=int(causal))
+    for name, g, w, bound in zip(("dk", "dv"), got[2:], want[2:], (0.995, 0.9999)):
+        assert oracle.metrics(g, w)["cos"] > bound, name
+
+
+@pytest.mark.parametrize("name", ["C2", "C2-bf16"])
+def test_config2_large_logit_floor(name):
+    """C2: dK and dV within 1.1x the correct-kernel rounding floor, fp16 and bf16. dQ is reported by
+    the bench but not gated here: with the magnitude on K it cancels catastrophically and the floor
+    itself is far above 1 (the reference's own huge-logit test skips dQ for the same reason)."""
+    cfg = workloads.CONFIGS[name]
+    q, k, v, dout = (t.cuda() for t in workloads.make_inputs(cfg, batch=4, heads=cfg.heads))
+    q, k, v = (t.requires_grad_() for t in (q, k, v))
+    got = run(q, k, v, dout)
+    want = want_for(q, k, v, dout)
+    floor = oracle.floor_grads(q, k, v, dout, cfg.scale)
+    out_tol = TOL if cfg.dtype == torch.float16 else BF16_TOL
+    assert oracle.metrics(got[0], want[0])["rel_err"] < out_tol
+    for idx, key in ((2, "dk"), (3, "dv")):
+        err = oracle.rel_l2(got[idx], want[idx])
+        base = oracle.rel_l2(floor[idx - 1], want[idx])
+        assert err <= 1.1 * base, f"{key}: kernel {err:.3e} vs floor {base:.3e} ({err / base:.3f}x)"
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_balanced_large_logits(dtype):
+    """The reference's own large-logit generator (magnitude split between q and k): all three
+    gradients near the floor."""
+    q, k, v, dout = (t.cuda() for t in workloads.balanced_large_logit_inputs(1, 4, 512, 64, dtype))
+    q, k, v = (t.requires_grad_() for t in (q, k, v))
+    got = run(q, k, v, dout)
+    want = want_for(q, k, v, dout)
+    floor = oracle.floor_grads(q, k, v, dout, 64**-0.5)
+    for idx, key in ((1, "dq"), (2, "dk"), (3, "dv")):
+        err = oracle.rel_l2(got[idx], want[idx])
+        base = oracle.rel_l2(floor[idx - 1], want[idx])
+        assert err <= 1.25 * base + 1e-6, f"{key}: kernel {err:.3e} vs floor {base:.3e}"
+
+
+def test_largest_p_is_exactly_one():
+    """Shift-then-scale: log2(l) of a row whose other keys are far below the max is exactly 0, and
+    m is the raw (unscaled) row max."""
+    from kohakufa_b200.op import attention_fwd_op
+
+    q, k, v, _ = inputs(1, 1, 128, 128, seed=9)
+    with torch.no_grad():
+        big = 300.0 * torch.nn.functional.normalize(q.float(), dim=-1)
+        q = big.half().contiguous()
+        k = big.half().contiguous()
+        out, lse = attention_fwd_op(q, k, v.detach().contiguous(), 0.125, 0)
+    torch.cuda.synchronize()
+    s = q.double() @ k.double().transpose(-1, -2)
+    assert torch.allclose(lse[0, 0, 0].double(), s.amax(-1)[0, 0], rtol=1e-6)
+    sep = (s.amax(-1, keepdim=True) - s).masked_fill(s == s.amax(-1, keepdim=True), 1e9).amin(-1) * 0.125
+    rows = sep[0, 0] > 200  # every other key underflows to exactly 0
+    assert bool(rows.any())
+    assert bool((lse[0, 0, 1][rows] == 0).all())
+
+
+def test_deterministic():
+    q, k, v, dout = inputs(2, 2, 700, 700, seed=8)
+    a = run(q, k, v, dout, causal=True)
+    b = run(q, k, v, dout, causal=True)
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
+
+
+def test_output_layout_and_strides():
+    q, k, v, dout = inputs(2, 3, 130, 130)
+    out = attention(q, k, v)
+    assert out.shape == (2, 3, 130, 64)
+    assert out.transpose(1, 2).is_contiguous()
+    out.backward(dout)
+    for t in (q, k, v):
+        assert t.grad.shape == t.shape
+
+
+def test_expanded_gradient():
+    """A broadcast (stride-0) upstream gradient is made contiguous first."""
+    q, k, v, _ = inputs(1, 2, 140, 140)
+    attention(q, k, v, causal=True).sum().backward()
+    torch.cuda.synchronize()
+    dout = torch.ones(1, 2, 140, 64, dtype=torch.float16, device="cuda")
+    want = want_for(q, k, v, dout, block=1)
+    for g, w in zip((q.grad, k.grad, v.grad), want[1:]):
+        assert oracle.metrics(g, w)["rel_err"] < TOL
+
+
+def test_center_keys():
+    q, k, v, dout = inputs(1, 2, 269, 269, seed=5)
+    with torch.no_grad():
+        k += 3.0
+    got = run(q, k, v, dout, center_keys=True)
+    check(got, want_for(q, k, v, dout))
+
+
+def test_causal_cuda_graph():
+    q, k, v, dout = inputs(1, 2, 269, 269)
+    run(q, k, v, dout, causal=True)  # warm-up: creates the status word outside the capture
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            out = attention(q, k, v, causal=True)
+            grads = torch.autograd.grad(out, (q, k, v), dout)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = attention(q, k, v, causal=True)
+        grads = torch.autograd.grad(out, (q, k, v), dout)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    check((out, *grads), want_for(q, k, v, dout, block=1))
+
+
+def test_causal_compiled():
+    q, k, v, dout = inputs(1, 2, 269, 269)
+    fn = torch.compile(lambda a, b, c: attention(a, b, c, causal=True), fullgraph=True)
+    for t in (q, k, v):
+        t.grad = None
+    out = fn(q, k, v)
+    out.backward(dout)
+    torch.cuda.synchronize()
+    check((out, q.grad, k.grad, v.grad), want_for(q, k, v, dout, block=1))
+
+
+def test_bounded_wait_reports_instead_of_hanging():
+    """A launch that finds the status word already set does no work and returns; clearing the word
+    restores normal operation (the context stays usable)."""
+    q, k, v, dout = inputs(1, 1, 128, 128)
+    word = _lib.status_word(q.device)
+    word.fill_(7)
+    out = attention(q, k, v)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 7
+    _lib.reset_device_status()
+    check(run(q, k, v, dout), want_for(q, k, v, dout))

@@ -1,0 +1,143 @@
+"""CPU tests of the host side: argument handling of ``attention`` (same exceptions as the reference,
+KohakuFA src/kohakufa/api.py:93-109 and sm100/op.py:41-55), the C-ABI library's exported symbols, and
+the header / binding agreement. No kernel runs here."""
+
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+import torch
+
+import kohakufa_b200
+from kohakufa_b200 import _lib, api, op
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def qkv(b=1, h=2, s=16, d=64, dtype=torch.float16):
+    return tuple(torch.zeros(b, h, s, d, dtype=dtype) for _ in range(3))
+
+
+def test_header_declares_what_the_binding_uses():
+    header = (ROOT / "include" / "kfa.h").read_text()
+    declared = set(re.findall(r"\b(kfa_[a-z0-9_]+)\s*\(", header))
+    assert declared == set(_lib.SYMBOLS)
+
+
+def test_library_exports_every_declared_symbol():
+    from kohakufa_b200 import build
+
+    path = build.build()
+    lib = ctypes.CDLL(str(path))
+    for name in _lib.SYMBOLS:
+        assert hasattr(lib, name), name
+    assert lib.kfa_abi_version() == _lib.ABI_VERSION
+    lib.kfa_bwd_stats_bytes.restype = ctypes.c_int64
+    lib.kfa_bwd_stats_bytes.argtypes = [ctypes.c_int64] * 3
+    assert lib.kfa_bwd_stats_bytes(2, 3, 129) == 2 * 3 * 2 * 3 * 128 * 4
+
+
+def test_library_rejects_bad_arguments_without_a_gpu():
+    lib = _lib.load()
+    t = _lib.KfaTensor4()
+    t.ptr = 64
+    for i, (n, s) in enumerate(zip((1, 2, 16, 48), (1536, 768, 48, 1))):
+        t.shape[i], t.stride[i] = n, s
+    rc = lib.kfa_fwd(ctypes.byref(t), ctypes.byref(t), ctypes.byref(t), ctypes.byref(t), 64, 1.0, 0, 0, 64, None)
+    assert rc == -1 and b"head_dim" in lib.kfa_last_error()
+    t.shape[3] = 64
+    t.stride[2] = 60
+    rc = lib.kfa_fwd(ctypes.byref(t), ctypes.byref(t), ctypes.byref(t), ctypes.byref(t), 64, 1.0, 0, 0, 64, None)
+    assert rc == -1 and b"stride" in lib.kfa_last_error()
+
+
+def test_causal_and_block_causal_are_exclusive():
+    q, k, v = qkv()
+    with pytest.raises(ValueError, match="causal is block_causal=1"):
+        api.attention(q, k, v, causal=True, block_causal=4)
+
+
+def test_compute_dtype_must_be_16_bit():
+    q, k, v = qkv()
+    with pytest.raises(TypeError, match="compute_dtype"):
+        api.attention(q, k, v, compute_dtype=torch.float32)
+
+
+def test_head_dim_range():
+    q, k, v = qkv(d=136)
+    with pytest.raises(ValueError, match="head_dim 136"):
+        api.attention(q, k, v)
+
+
+def test_mask_with_block_rejected_first():
+    q, k, v = qkv()
+    with pytest.raises(ValueError, match="mask or causal"):
+        api.attention(q, k, v, causal=True, mask=torch.ones(16, 16, dtype=torch.bool))
+    with pytest.raises(NotImplementedError):
+        api.attention(q, k, v, mask=torch.ones(16, 16, dtype=torch.bool))
+
+
+def test_check_rules():
+    q, k, v = qkv()
+    with pytest.raises(TypeError):
+        op._check(q.float(), k.float(), v.float())
+    with pytest.raises(TypeError):
+        op._check(q, k.bfloat16(), v)
+    with pytest.raises(ValueError, match="k .* vs q"):
+        op._check(q, k, v[:, :, :8])
+    with pytest.raises(ValueError, match="multiple of K / V heads"):
+        op._check(torch.zeros(1, 3, 16, 64, dtype=torch.float16), k, v)
+    with pytest.raises(NotImplementedError):
+        op._check(torch.zeros(1, 4, 16, 64, dtype=torch.float16), k, v)
+    with pytest.raises(ValueError, match="CUDA tensors only"):
+        op._check(q, k, v)
+    with pytest.raises(ValueError, match="head_dim"):
+        op._check(*qkv(d=48))
+
+
+def test_stride_rule():
+    x = torch.zeros(1, 2, 16, 72, dtype=torch.float16)
+    assert op._strides_ok(x)
+    assert not op._strides_ok(x[..., 1:65])  # misaligned start
+    assert not op._strides_ok(x.transpose(-1, -2))  # last dim not contiguous
+    assert not op._strides_ok(torch.zeros(1, 2, 16, 68, dtype=torch.float16)[..., :64])  # 136-byte rows
+    assert not op._strides_ok(torch.zeros(1, 1, 1, 64, dtype=torch.float16).expand(1, 2, 16, 64))
+
+
+def test_pad_head_dim():
+    q, k, v = qkv(d=40)
+    pq, pk, pv = api._pad_head_dim(q, k, v)
+    assert pq.shape[-1] == pk.shape[-1] == pv.shape[-1] == 64
+    q, k, v = qkv(d=72)
+    assert api._pad_head_dim(q, k, v)[0].shape[-1] == 128
+    q, k, v = qkv(d=128)
+    assert api._pad_head_dim(q, k, v)[0] is q
+
+
+def test_center_keys_is_a_pure_shift():
+    k = torch.randn(2, 3, 10, 8)
+    c = api._center_keys(k, torch.float16)
+    assert c.dtype == torch.float16
+    assert float(c.float().mean(-2).abs().max()) < 1e-3
+
+
+def test_other_exports_raise():
+    assert set(kohakufa_b200.__all__) == {"PackedMask", "attention", "attention_varlen", "pack_mask", "varlen_plan"}
+    for name in ("attention_varlen", "varlen_plan", "pack_mask", "PackedMask"):
+        with pytest.raises(NotImplementedError):
+            getattr(kohakufa_b200, name)()
+
+
+def test_fake_kernels_infer_layouts():
+    """The registered fakes give the [B, S, H, D]-storage views without touching a device."""
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    with FakeTensorMode():
+        q = torch.empty(2, 10, 3, 64, dtype=torch.float16, device="cuda").transpose(1, 2)
+        k = torch.empty(2, 14, 3, 64, dtype=torch.float16, device="cuda").transpose(1, 2)
+        out, lse = torch.ops.kohakufa_b200.sm100_forward(q, k, k, 0.125, 0)
+        assert out.shape == (2, 3, 10, 64) and out.stride() == (10 * 3 * 64, 64, 3 * 64, 1)
+        assert lse.shape == (2, 3, 2, 10) and lse.dtype == torch.float32
+        dq, dk, dv = torch.ops.kohakufa_b200.sm100_backward(q, k, k, out, out, lse, 0.125, 0)
+        assert dq.shape == q.shape and dk.shape == k.shape and dv.stride() == k.stride()
