@@ -330,3 +330,11 @@ int kfa_bwd(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const
 }  // extern "C"
 
 #include "kfa_selftest.cuh"
+
+#ifdef KFA_PROFILE
+// Debug builds only (not part of the ABI): where the per-role wait-cycle counters are written.
+extern "C" int kfa_debug_set_profile(long long* device_buffer) {
+  KFA_CUDA(cudaMemcpyToSymbol(kfa::g_kfa_prof, &device_buffer, sizeof(device_buffer)));
+  return KFA_OK;
+}
+#endif

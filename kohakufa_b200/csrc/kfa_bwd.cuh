@@ -96,9 +96,10 @@ __global__ void __launch_bounds__(128) kfa_bwd_prepare_kernel(const PrepParams p
     for (int off = LPR / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
     if (vec == 0) {
       const bool valid = row < p.Sq;
-      st[r_in] = valid ? lse[row] : INFINITY;
-      st[128 + r_in] = valid ? lse[p.Sq + row] : 0.f;
-      st[256 + r_in] = valid ? acc : 0.f;
+      // stored negated, so the consumers only add; padded rows: -m = -inf makes their P exactly 0
+      st[r_in] = valid ? -lse[row] : -INFINITY;
+      st[128 + r_in] = valid ? -lse[p.Sq + row] : 0.f;
+      st[256 + r_in] = valid ? -acc : 0.f;
     }
   }
 }
@@ -127,28 +128,28 @@ struct BwdCfg {
   static constexpr int Q_SMEM_BYTES = Q_SMEM_TILES + 1024 + 256;
 };
 
-// Issue helpers (one thread). Operand tiles are 128B-swizzled [rows][64] boxes, D / 64 of them
-// 16 KB apart.
-// acc[128 x 64] = A[128 rows, D] * B[64 rows starting at row b_row0, D]^T, contraction over D.
+// Issue helpers for the MMA warp (converged; `lead` is true in the one lane that issues). Operand
+// tiles are 128B-swizzled [rows][64] boxes, D / 64 of them 16 KB apart; descriptors are passed as
+// their low words (see sdesc_lo).
+// acc[128 x 64] = A[128 rows, D] * B[64 rows, D]^T, contraction over D. b_lo already points at B's
+// first row.
 template <int D>
-__device__ __forceinline__ void issue_kmajor_n64(uint32_t d_tmem, uint32_t a_smem, uint32_t b_smem,
-                                                 int b_row0, uint32_t idesc) {
+__device__ __forceinline__ void issue_kmajor_n64(bool lead, uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo,
+                                                 uint32_t idesc) {
 #pragma unroll
   for (int kk = 0; kk < D / 16; ++kk) {
-    const uint32_t off = (kk >> 2) * TILE_BYTES_64 + (kk & 3) * 32;
-    umma_ss(d_tmem, make_sdesc(a_smem + off, 16, 1024), make_sdesc(b_smem + b_row0 * 128 + off, 16, 1024),
-            idesc, kk > 0);
+    const uint32_t off = ((kk >> 2) * TILE_BYTES_64 + (kk & 3) * 32) >> 4;
+    umma_ss_lead(lead, d_tmem, a_lo + off, b_lo + off, idesc, kk > 0 ? 1u : 0u);
   }
 }
-// acc[128 x D] (+)= A16[128 x 64 from TMEM] * B[64 rows starting at b_row0, D], contraction over rows.
+// acc[128 x D] (+)= A16[128 x 64 from TMEM] * B[64 rows, D], contraction over B's rows (MN-major B,
+// leading offset = one 16 KB box). b_lo points at B's first row.
 template <int D>
-__device__ __forceinline__ void issue_tmemA_k64(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_smem,
-                                                int b_row0, uint32_t idesc, bool acc) {
+__device__ __forceinline__ void issue_tmemA_k64(bool lead, uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
+                                                uint32_t idesc, bool acc) {
 #pragma unroll
-  for (int kk = 0; kk < 4; ++kk) {
-    umma_ts(d_tmem, a_tmem + kk * 8, make_sdesc(b_smem + (b_row0 + kk * 16) * 128, TILE_BYTES_64, 1024),
-            idesc, (acc || kk > 0) ? 1u : 0u);
-  }
+  for (int kk = 0; kk < 4; ++kk)
+    umma_ts_lead(lead, d_tmem, a_tmem + kk * 8, b_lo + ((kk * 16 * 128) >> 4), idesc, (acc || kk > 0) ? 1u : 0u);
 }
 
 // Writes a row of an fp32 accumulator (TMEM columns [col0, col0 + ncols)) times mul as 16-bit.
@@ -170,6 +171,56 @@ __device__ __forceinline__ void store_acc_row(uint32_t taddr, int col0, int ncol
         *reinterpret_cast<uint4*>(grow + 2 * (cc + i)) = w;
       }
     }
+  }
+}
+
+// 32 columns (queries) of one key row in the dK / dV kernel: from S^T and dP^T (fp32, two columns
+// per float2) and the per-query statistics in shared memory (-m at st[0..], -log2 l at st[128..],
+// -delta at st[256..]) to the packed 16-bit P^T and dS^T words.
+//   P = exp2(fma(S - m, c, -log2 l));  dS = (dP - delta) * P   (fp32 P; dS rounded once, unscaled)
+// MASKED: columns whose query index (q_first + column) is below qmin get P = dS = 0.
+template <bool BF16, bool MASKED>
+__device__ __forceinline__ void pds_cols_by_query(const float2* sv, const float2* dp, const float* st, float2 c2,
+                                                  int q_first, int qmin, uint32_t* pk, uint32_t* dk) {
+#pragma unroll
+  for (int x = 0; x < 32; x += 4) {
+    const float4 nm = *reinterpret_cast<const float4*>(st + x);
+    const float4 nl = *reinterpret_cast<const float4*>(st + 128 + x);
+    const float4 nd = *reinterpret_cast<const float4*>(st + 256 + x);
+    const float2 x0 = __ffma2_rn(__fadd2_rn(sv[x / 2], make_float2(nm.x, nm.y)), c2, make_float2(nl.x, nl.y));
+    const float2 x1 = __ffma2_rn(__fadd2_rn(sv[x / 2 + 1], make_float2(nm.z, nm.w)), c2, make_float2(nl.z, nl.w));
+    float2 p0 = make_float2(ex2(x0.x), ex2(x0.y));
+    float2 p1 = make_float2(ex2(x1.x), ex2(x1.y));
+    if constexpr (MASKED) {
+      if (q_first + x < qmin) p0.x = 0.f;
+      if (q_first + x + 1 < qmin) p0.y = 0.f;
+      if (q_first + x + 2 < qmin) p1.x = 0.f;
+      if (q_first + x + 3 < qmin) p1.y = 0.f;
+    }
+    pk[x / 2] = pack16<BF16>(p0.x, p0.y);
+    pk[x / 2 + 1] = pack16<BF16>(p1.x, p1.y);
+    const float2 d0 = __fmul2_rn(__fadd2_rn(dp[x / 2], make_float2(nd.x, nd.y)), p0);
+    const float2 d1 = __fmul2_rn(__fadd2_rn(dp[x / 2 + 1], make_float2(nd.z, nd.w)), p1);
+    dk[x / 2] = pack16<BF16>(d0.x, d0.y);
+    dk[x / 2 + 1] = pack16<BF16>(d1.x, d1.y);
+  }
+}
+
+// 32 columns (keys) of one query row in the dQ kernel: the row's statistics are scalars.
+// MASKED: columns at or beyond `lim` (relative to this group's first column) get dS = 0.
+template <bool BF16, bool MASKED>
+__device__ __forceinline__ void ds_cols_by_key(const float2* sv, const float2* dp, float2 nm, float2 c2, float2 nl,
+                                               float2 nd, int lim, uint32_t* dk) {
+#pragma unroll
+  for (int x = 0; x < 16; ++x) {
+    const float2 e = __ffma2_rn(__fadd2_rn(sv[x], nm), c2, nl);
+    float2 pr = make_float2(ex2(e.x), ex2(e.y));
+    if constexpr (MASKED) {
+      if (2 * x >= lim) pr.x = 0.f;
+      if (2 * x + 1 >= lim) pr.y = 0.f;
+    }
+    const float2 d = __fmul2_rn(__fadd2_rn(dp[x], nd), pr);
+    dk[x] = pack16<BF16>(d.x, d.y);
   }
 }
 
@@ -240,7 +291,15 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *s_tmem;
+#ifdef KFA_PROFILE
+  long long prof_acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+  long long kfa_prof_tb = 0;
+  (void)kfa_prof_tb;
+  const long long prof_t0 = clock64();
+  const Ctl ctl{s_abort, p.status, prof_acc};
+#else
   const Ctl ctl{s_abort, p.status};
+#endif
   const bool dead = (*s_abort != 0);
 
   if (dead) {
@@ -284,19 +343,24 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
   } else if (warp == 8) {
     // =========================== MMA issue ===========================
-    if (lane == 0 && n_steps > 0) {
+    // The whole warp runs this role converged; one elected lane issues the tcgen05 instructions.
+    if (n_steps > 0) {
+      const bool lead = elect_one();
       constexpr uint32_t IDESC_S = make_idesc(BF16, false, 128, 64);
       constexpr uint32_t IDESC_ACC = make_idesc(BF16, true, 128, D);
       const uint32_t tST = tmem + Cfg::TM_S, tDP = tmem + Cfg::TM_DP;
       const uint32_t tDV = tmem + Cfg::TM_ACC0, tDK = tmem + Cfg::TM_ACC1;
-      bool ok = mbar_wait(bar(B_KV), 0, ctl, 12);
-      if (ok) ok = mbar_wait(bar(B_QREADY + 0), 0, ctl, 13);
+      const uint32_t k_lo = sdesc_lo(sK, 16), v_lo = sdesc_lo(sV, 16);
+      constexpr uint32_t HALF_ROWS = (64 * 128) >> 4;  // 64 rows further down a box, in descriptor units
+      bool ok = mbar_wait_warp(bar(B_KV), 0, ctl, 12);
+      if (ok) ok = mbar_wait_warp(bar(B_QREADY + 0), 0, ctl, 13);
       if (ok) {
         tc_fence_after();
+        const uint32_t q_lo = sdesc_lo(sSlot, 16), do_lo = sdesc_lo(sSlot + Cfg::TILE_BYTES, 16);
         for (int hq = 0; hq < 2; ++hq) {
-          issue_kmajor_n64<D>(tST + 64 * hq, sK, sSlot, 64 * hq, IDESC_S);
-          issue_kmajor_n64<D>(tDP + 64 * hq, sV, sSlot + Cfg::TILE_BYTES, 64 * hq, IDESC_S);
-          umma_commit(bar(B_SDP + hq));
+          issue_kmajor_n64<D>(lead, tST + 64 * hq, k_lo, q_lo + hq * HALF_ROWS, IDESC_S);
+          issue_kmajor_n64<D>(lead, tDP + 64 * hq, v_lo, do_lo + hq * HALF_ROWS, IDESC_S);
+          umma_commit_lead(lead, bar(B_SDP + hq));
         }
       }
       for (int s = 0; s < n_steps && ok; ++s) {
@@ -306,27 +370,31 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const int nslot = (s + 1) % NSL;
         const uint32_t q_n = sSlot + nslot * Cfg::KV_SLOT_BYTES;
         const uint32_t do_n = q_n + Cfg::TILE_BYTES;
+        // as the MN-major B operand of dV / dK (leading offset: the next 64 columns of D)
+        const uint32_t qmn_lo = sdesc_lo(q_s, TILE_BYTES_64), domn_lo = sdesc_lo(do_s, TILE_BYTES_64);
+        // as the K-major B operand of the next step's S^T / dP^T
+        const uint32_t qn_lo = sdesc_lo(q_n, 16), don_lo = sdesc_lo(do_n, 16);
         for (int hq = 0; hq < 2 && ok; ++hq) {
-          ok = mbar_wait(bar(B_PDS + hq), s & 1, ctl, 14);
+          ok = mbar_wait_warp(bar(B_PDS + hq), s & 1, ctl, 14);
           if (!ok) break;
           tc_fence_after();
-          issue_tmemA_k64<D>(tDV, tST + 64 * hq, do_s, 64 * hq, IDESC_ACC, s > 0 || hq > 0);
-          issue_tmemA_k64<D>(tDK, tDP + 64 * hq, q_s, 64 * hq, IDESC_ACC, s > 0 || hq > 0);
-          if (hq == 1) umma_commit(bar(B_QFREE + slot));
+          issue_tmemA_k64<D>(lead, tDV, tST + 64 * hq, domn_lo + hq * HALF_ROWS, IDESC_ACC, s > 0 || hq > 0);
+          issue_tmemA_k64<D>(lead, tDK, tDP + 64 * hq, qmn_lo + hq * HALF_ROWS, IDESC_ACC, s > 0 || hq > 0);
+          if (hq == 1) umma_commit_lead(lead, bar(B_QFREE + slot));
           if (s + 1 < n_steps) {
             if (hq == 0) {
-              ok = mbar_wait(bar(B_QREADY + nslot), ((s + 1) / NSL) & 1, ctl, 15);
+              ok = mbar_wait_warp(bar(B_QREADY + nslot), ((s + 1) / NSL) & 1, ctl, 15);
               if (!ok) break;
               tc_fence_after();
             }
-            issue_kmajor_n64<D>(tST + 64 * hq, sK, q_n, 64 * hq, IDESC_S);
-            issue_kmajor_n64<D>(tDP + 64 * hq, sV, do_n, 64 * hq, IDESC_S);
-            umma_commit(bar(B_SDP + hq));
+            issue_kmajor_n64<D>(lead, tST + 64 * hq, k_lo, qn_lo + hq * HALF_ROWS, IDESC_S);
+            issue_kmajor_n64<D>(lead, tDP + 64 * hq, v_lo, don_lo + hq * HALF_ROWS, IDESC_S);
+            umma_commit_lead(lead, bar(B_SDP + hq));
           }
         }
       }
-      if (ok) umma_commit(bar(B_ACC));
-      umma_commit(bar(B_DRAIN));
+      if (ok) umma_commit_lead(lead, bar(B_ACC));
+      umma_commit_lead(lead, bar(B_DRAIN));
       {
         const long long t0 = clock64();
         while (!mbar_try_wait(bar(B_DRAIN), 0) && clock64() - t0 < KFA_WAIT_CYCLES) {
@@ -360,40 +428,25 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const float* st =
           reinterpret_cast<const float*>(smem + 2 * Cfg::TILE_BYTES + slot * Cfg::KV_SLOT_BYTES +
                                          2 * Cfg::TILE_BYTES) + 64 * hq;
-#pragma unroll
-      for (int g = 0; g < 2; ++g) {
-        float sv[32], dp[32];
-        tmem_ld32(tS + 32 * g, reinterpret_cast<uint32_t*>(sv));
-        tmem_ld32(tDP + 32 * g, reinterpret_cast<uint32_t*>(dp));
+      const float2 c2 = make_float2(c, c);
+      {
+        float2 sv[32], dp[32];  // 64 columns of S^T and of dP^T
+        tmem_ld32(tS, reinterpret_cast<uint32_t*>(sv));
+        tmem_ld32(tDP, reinterpret_cast<uint32_t*>(dp));
+        tmem_ld32(tS + 32, reinterpret_cast<uint32_t*>(sv + 16));
+        tmem_ld32(tDP + 32, reinterpret_cast<uint32_t*>(dp + 16));
         tmem_wait_ld();
-        uint32_t pk[16], dk[16];
 #pragma unroll
-        for (int x = 0; x < 32; x += 4) {
-          const float4 mm = *reinterpret_cast<const float4*>(st + 32 * g + x);
-          const float4 ll = *reinterpret_cast<const float4*>(st + 128 + 32 * g + x);
-          const float4 dd = *reinterpret_cast<const float4*>(st + 256 + 32 * g + x);
-          const float mv[4] = {mm.x, mm.y, mm.z, mm.w};
-          const float lv[4] = {ll.x, ll.y, ll.z, ll.w};
-          const float dv[4] = {dd.x, dd.y, dd.z, dd.w};
-          float pv[4];
-#pragma unroll
-          for (int y = 0; y < 4; ++y) {
-            float pe = ex2(fmaf(__fsub_rn(sv[x + y], mv[y]), c, -lv[y]));
-            if (masked && (q0 + 32 * g + x + y) < qmin) pe = 0.f;
-            pv[y] = pe;
-          }
-          const uint32_t w0 = pack16<BF16>(pv[0], pv[1]);
-          const uint32_t w1 = pack16<BF16>(pv[2], pv[3]);
-          const float2 r0 = unpack16<BF16>(w0);
-          const float2 r1 = unpack16<BF16>(w1);
-          pk[x / 2] = w0;
-          pk[x / 2 + 1] = w1;
-          dk[x / 2] = pack16<BF16>((dp[x] - dv[0]) * r0.x, (dp[x + 1] - dv[1]) * r0.y);
-          dk[x / 2 + 1] = pack16<BF16>((dp[x + 2] - dv[2]) * r1.x, (dp[x + 3] - dv[3]) * r1.y);
+        for (int g = 0; g < 2; ++g) {
+          uint32_t pk[16], dk[16];
+          if (masked)
+            pds_cols_by_query<BF16, true>(sv + 16 * g, dp + 16 * g, st + 32 * g, c2, q0 + 32 * g, qmin, pk, dk);
+          else
+            pds_cols_by_query<BF16, false>(sv + 16 * g, dp + 16 * g, st + 32 * g, c2, q0 + 32 * g, qmin, pk, dk);
+          // 16-bit P^T / dS^T over columns already read
+          tmem_st16(tS + 16 * g, pk);
+          tmem_st16(tDP + 16 * g, dk);
         }
-        // 16-bit P^T / dS^T over columns already read (16 words <= 32 columns read per group)
-        tmem_st16(tS + 16 * g, pk);
-        tmem_st16(tDP + 16 * g, dk);
       }
       tmem_wait_st();
       tc_fence_before();
@@ -419,6 +472,11 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
   }
 
+#ifdef KFA_PROFILE
+  prof_acc[0] = clock64() - prof_t0;
+  if (lane == 0 && (warp == 0 || warp == 4 || warp == 8 || warp == 9))
+    kfa_prof_flush(prof_acc, warp == 0 ? 0 : (warp == 4 ? 1 : (warp == 8 ? 2 : 3)));
+#endif
   tc_fence_before();
   __syncthreads();
   if (warp == 0) {
@@ -494,7 +552,15 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *s_tmem;
+#ifdef KFA_PROFILE
+  long long prof_acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+  long long kfa_prof_tb = 0;
+  (void)kfa_prof_tb;
+  const long long prof_t0 = clock64();
+  const Ctl ctl{s_abort, p.status, prof_acc};
+#else
   const Ctl ctl{s_abort, p.status};
+#endif
   const bool dead = (*s_abort != 0);
 
   if (dead) {
@@ -533,18 +599,23 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       }
     }
   } else if (warp == 8) {
-    if (lane == 0) {
+    // MMA issue: the whole warp converged, one elected lane issues.
+    {
+      const bool lead = elect_one();
       constexpr uint32_t IDESC_S = make_idesc(BF16, false, 128, 64);
       constexpr uint32_t IDESC_ACC = make_idesc(BF16, true, 128, D);
       const uint32_t tS = tmem + Cfg::TM_S, tDP = tmem + Cfg::TM_DP, tDQ = tmem + Cfg::TM_ACC0;
-      bool ok = mbar_wait(bar(B_Q), 0, ctl, 22);
-      if (ok) ok = mbar_wait(bar(B_KVREADY + 0), 0, ctl, 23);
+      const uint32_t q_lo = sdesc_lo(sQ, 16), do_lo = sdesc_lo(sDO, 16);
+      constexpr uint32_t HALF_ROWS = (64 * 128) >> 4;
+      bool ok = mbar_wait_warp(bar(B_Q), 0, ctl, 22);
+      if (ok) ok = mbar_wait_warp(bar(B_KVREADY + 0), 0, ctl, 23);
       if (ok) {
         tc_fence_after();
+        const uint32_t k_lo = sdesc_lo(sSlot, 16), v_lo = sdesc_lo(sSlot + Cfg::TILE_BYTES, 16);
         for (int hk = 0; hk < 2; ++hk) {
-          issue_kmajor_n64<D>(tS + 64 * hk, sQ, sSlot, 64 * hk, IDESC_S);
-          issue_kmajor_n64<D>(tDP + 64 * hk, sDO, sSlot + Cfg::TILE_BYTES, 64 * hk, IDESC_S);
-          umma_commit(bar(B_SDP + hk));
+          issue_kmajor_n64<D>(lead, tS + 64 * hk, q_lo, k_lo + hk * HALF_ROWS, IDESC_S);
+          issue_kmajor_n64<D>(lead, tDP + 64 * hk, do_lo, v_lo + hk * HALF_ROWS, IDESC_S);
+          umma_commit_lead(lead, bar(B_SDP + hk));
         }
       }
       for (int j = 0; j < n_steps && ok; ++j) {
@@ -552,27 +623,28 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         const uint32_t k_s = sSlot + slot * Cfg::Q_SLOT_BYTES;
         const int nslot = (j + 1) % NSL;
         const uint32_t k_n = sSlot + nslot * Cfg::Q_SLOT_BYTES;
-        const uint32_t v_n = k_n + Cfg::TILE_BYTES;
+        const uint32_t kmn_lo = sdesc_lo(k_s, TILE_BYTES_64);
+        const uint32_t kn_lo = sdesc_lo(k_n, 16), vn_lo = sdesc_lo(k_n + Cfg::TILE_BYTES, 16);
         for (int hk = 0; hk < 2 && ok; ++hk) {
-          ok = mbar_wait(bar(B_DS + hk), j & 1, ctl, 24);
+          ok = mbar_wait_warp(bar(B_DS + hk), j & 1, ctl, 24);
           if (!ok) break;
           tc_fence_after();
-          issue_tmemA_k64<D>(tDQ, tDP + 64 * hk, k_s, 64 * hk, IDESC_ACC, j > 0 || hk > 0);
-          if (hk == 1) umma_commit(bar(B_KVFREE + slot));
+          issue_tmemA_k64<D>(lead, tDQ, tDP + 64 * hk, kmn_lo + hk * HALF_ROWS, IDESC_ACC, j > 0 || hk > 0);
+          if (hk == 1) umma_commit_lead(lead, bar(B_KVFREE + slot));
           if (j + 1 < n_steps) {
             if (hk == 0) {
-              ok = mbar_wait(bar(B_KVREADY + nslot), ((j + 1) / NSL) & 1, ctl, 25);
+              ok = mbar_wait_warp(bar(B_KVREADY + nslot), ((j + 1) / NSL) & 1, ctl, 25);
               if (!ok) break;
               tc_fence_after();
             }
-            issue_kmajor_n64<D>(tS + 64 * hk, sQ, k_n, 64 * hk, IDESC_S);
-            issue_kmajor_n64<D>(tDP + 64 * hk, sDO, v_n, 64 * hk, IDESC_S);
-            umma_commit(bar(B_SDP + hk));
+            issue_kmajor_n64<D>(lead, tS + 64 * hk, q_lo, kn_lo + hk * HALF_ROWS, IDESC_S);
+            issue_kmajor_n64<D>(lead, tDP + 64 * hk, do_lo, vn_lo + hk * HALF_ROWS, IDESC_S);
+            umma_commit_lead(lead, bar(B_SDP + hk));
           }
         }
       }
-      if (ok) umma_commit(bar(B_ACC));
-      umma_commit(bar(B_DRAIN));
+      if (ok) umma_commit_lead(lead, bar(B_ACC));
+      umma_commit_lead(lead, bar(B_DRAIN));
       {
         const long long t0 = clock64();
         while (!mbar_try_wait(bar(B_DRAIN), 0) && clock64() - t0 < KFA_WAIT_CYCLES) {
@@ -587,34 +659,33 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     const uint32_t tS = tmem + Cfg::TM_S + 64 * hk + lane_base;
     const uint32_t tDP = tmem + Cfg::TM_DP + 64 * hk + lane_base;
     const float* st = p.stats + (static_cast<long long>(bh) * p.n_q128 + qt) * 384;
-    const float m = st[r_in];
-    const float nl2 = -st[128 + r_in];
-    const float delta = st[256 + r_in];
+    const float2 nm = make_float2(st[r_in], st[r_in]);                // -m
+    const float2 nl = make_float2(st[128 + r_in], st[128 + r_in]);    // -log2 l
+    const float2 nd = make_float2(st[256 + r_in], st[256 + r_in]);    // -delta
     const int my_limit = key_limit(min(row, p.Sq - 1), p.P, p.Skv);
-    const float c = p.c;
+    const float2 c2 = make_float2(p.c, p.c);
     bool ok = true;
     for (int j = 0; j < n_steps; ++j) {
       ok = mbar_wait_warp(bar(B_SDP + hk), j & 1, ctl, 26);
       if (!ok) break;
       tc_fence_after();
-      const int lim = (j >= n_unmasked) ? (my_limit - j * 128 - 64 * hk) : 64;
-#pragma unroll
-      for (int g = 0; g < 2; ++g) {
-        float sv[32], dp[32];
-        tmem_ld32(tS + 32 * g, reinterpret_cast<uint32_t*>(sv));
-        tmem_ld32(tDP + 32 * g, reinterpret_cast<uint32_t*>(dp));
+      const int lim = my_limit - j * 128 - 64 * hk;  // visible columns of this half (masked tiles)
+      {
+        float2 sv[32], dp[32];
+        tmem_ld32(tS, reinterpret_cast<uint32_t*>(sv));
+        tmem_ld32(tDP, reinterpret_cast<uint32_t*>(dp));
+        tmem_ld32(tS + 32, reinterpret_cast<uint32_t*>(sv + 16));
+        tmem_ld32(tDP + 32, reinterpret_cast<uint32_t*>(dp + 16));
         tmem_wait_ld();
-        uint32_t dk[16];
 #pragma unroll
-        for (int x = 0; x < 32; x += 2) {
-          float p0 = ex2(fmaf(__fsub_rn(sv[x], m), c, nl2));
-          float p1 = ex2(fmaf(__fsub_rn(sv[x + 1], m), c, nl2));
-          if (32 * g + x >= lim) p0 = 0.f;
-          if (32 * g + x + 1 >= lim) p1 = 0.f;
-          const float2 r = unpack16<BF16>(pack16<BF16>(p0, p1));
-          dk[x / 2] = pack16<BF16>((dp[x] - delta) * r.x, (dp[x + 1] - delta) * r.y);
+        for (int g = 0; g < 2; ++g) {
+          uint32_t dk[16];
+          if (j >= n_unmasked)
+            ds_cols_by_key<BF16, true>(sv + 16 * g, dp + 16 * g, nm, c2, nl, nd, lim - 32 * g, dk);
+          else
+            ds_cols_by_key<BF16, false>(sv + 16 * g, dp + 16 * g, nm, c2, nl, nd, 32, dk);
+          tmem_st16(tDP + 16 * g, dk);
         }
-        tmem_st16(tDP + 16 * g, dk);
       }
       tmem_wait_st();
       tc_fence_before();
@@ -629,6 +700,11 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     }
   }
 
+#ifdef KFA_PROFILE
+  prof_acc[0] = clock64() - prof_t0;
+  if (lane == 0 && (warp == 0 || warp == 4 || warp == 8 || warp == 9))
+    kfa_prof_flush(prof_acc, warp == 0 ? 0 : (warp == 4 ? 1 : (warp == 8 ? 2 : 3)));
+#endif
   tc_fence_before();
   __syncthreads();
   if (warp == 0) {

