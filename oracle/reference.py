@@ -78,12 +78,19 @@ def rel_l2(got, ref) -> float:
     return float((got.double() - ref.double()).norm() / ref.double().norm())
 
 
-def floor_grads(q, k, v, dout, scale, block=0, bugs=frozenset()):
+def floor_grads(q, k, v, dout, scale, block=0, bugs=frozenset(), scores=None):
     """dq, dk, dv (fp64 tensors) of an emulated flash backward whose only errors are the roundings a
     correct 16-bit tensor-core kernel cannot avoid; ``bugs`` adds "scale*dS", "single lse" and / or
     "scale-shift" (each a known way to lose accuracy at large logits).
 
-    Steps a kernel does in fp32 are rounded to fp32 here; the inputs' dtype is the 16-bit dtype."""
+    Steps a kernel does in fp32 are rounded to fp32 here; the inputs' dtype is the 16-bit dtype.
+
+    ``scores`` (not in the reference's emulation): the raw fp32 scores q k^T as the accumulating
+    hardware produces them. By default they are the exact product rounded once to fp32, which no
+    tensor core delivers: it sums the D products in groups with a truncating fp32 adder and lands a
+    few units in the last place away. At logits ~1e5 one such unit is ~1% of a neighbouring P, so
+    the floor of a kernel whose scores come from the tensor core is the one computed from those
+    scores (every such kernel pays it, whatever else it does right)."""
     dtype = q.dtype
 
     def r16(x):
@@ -94,7 +101,10 @@ def floor_grads(q, k, v, dout, scale, block=0, bugs=frozenset()):
 
     qd, kd, vd, dod = (t.detach().to(torch.float64) for t in (q, k, v, dout))
     c = r32(torch.tensor(scale * LOG2E, dtype=torch.float64))
-    s = r32(torch.matmul(qd, kd.transpose(-1, -2)))  # raw scores, fp32 accumulator
+    if scores is None:
+        s = r32(torch.matmul(qd, kd.transpose(-1, -2)))  # raw scores, fp32 accumulator
+    else:
+        s = scores.detach().to(torch.float32).to(torch.float64)
     mask = visible(q.shape[-2], k.shape[-2], block, q.device)
     if mask is not None:
         s = s.masked_fill(~mask, float("-inf"))
