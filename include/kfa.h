@@ -82,6 +82,30 @@ int kfa_bwd(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const
             const KfaTensor4* dk, const KfaTensor4* dv, float scale, int block, int dtype,
             int* dev_status, void* stream);
 
+/* Backward without a scratch buffer from the caller. No counterpart in the reference (there the
+ * launcher allocates its scratch from torch's caching allocator, bwd.py:1434-1439).
+ *
+ * kfa_bwd needs `stats`, scratch the caller has to allocate. Some hosts have no way to do that at the
+ * point of the call: a binding from a runtime that owns no device allocator and only passes on the
+ * tensors it was given, a serving loop that may not touch cudaMalloc because it synchronises the
+ * device, a process whose memory is fully pre-carved. For them the library keeps ONE statistics
+ * buffer of KFA_STATIC_SCRATCH_BYTES inside its own device image (every GPU that loads libkfa.so
+ * holds these bytes until the process exits) and this entry point runs the same three kernels on it.
+ * It calls no cudaMalloc, cudaFree or other allocating routine.
+ *
+ *   - Limit: kfa_bwd_stats_bytes(B, H, Sq) <= KFA_STATIC_SCRATCH_BYTES, i.e. B * H * ceil(Sq / 128) <=
+ *     5461 query tiles (about 699,000 query rows). Larger problems are refused with KFA_ERR_ARG.
+ *   - The first call on each device looks the buffer's device address up (one runtime query, with that
+ *     device current). Make that first call outside any stream capture.
+ *   - All calls on a device share the one buffer, which keeps the previous call's contents; each call
+ *     rewrites every entry it reads, so nothing has to be cleared. Two calls whose kernels overlap on
+ *     the GPU (different streams) race on it: serialise them, or use kfa_bwd with separate buffers. */
+#define KFA_STATIC_SCRATCH_BYTES (8 * 1024 * 1024)
+int kfa_bwd_static_scratch(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v,
+                           const KfaTensor4* out, const KfaTensor4* dout, const float* lse,
+                           const KfaTensor4* dq, const KfaTensor4* dk, const KfaTensor4* dv, float scale,
+                           int block, int dtype, int* dev_status, void* stream);
+
 /* Hardware self-check of the building blocks (TMA tile load, MMA from shared memory, MMA with a
  * tensor-memory operand, tensor-memory loads / stores) on small fixed matrices. Synchronises.
  * `report` (may be NULL) receives `report_len` bytes of text. No counterpart in the reference. */

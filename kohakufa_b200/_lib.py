@@ -25,6 +25,7 @@ SYMBOLS = (
     "kfa_bwd_dkdv",
     "kfa_bwd_dq",
     "kfa_bwd",
+    "kfa_bwd_static_scratch",
     "kfa_selftest",
 )
 
@@ -71,8 +72,9 @@ def load() -> ctypes.CDLL:
         lib.kfa_bwd_dkdv.argtypes = [T, T, T, T, fp, T, T, ctypes.c_float, ctypes.c_int, ctypes.c_int, ip, vp]
         lib.kfa_bwd_dq.argtypes = [T, T, T, T, fp, T, ctypes.c_float, ctypes.c_int, ctypes.c_int, ip, vp]
         lib.kfa_bwd.argtypes = [T, T, T, T, T, fp, fp, T, T, T, ctypes.c_float, ctypes.c_int, ctypes.c_int, ip, vp]
+        lib.kfa_bwd_static_scratch.argtypes = [T, T, T, T, T, fp, T, T, T, ctypes.c_float, ctypes.c_int, ctypes.c_int, ip, vp]
         lib.kfa_selftest.argtypes = [ctypes.c_char_p, ctypes.c_int]
-        for name in ("kfa_fwd", "kfa_bwd_prepare", "kfa_bwd_dkdv", "kfa_bwd_dq", "kfa_bwd", "kfa_selftest"):
+        for name in ("kfa_fwd", "kfa_bwd_prepare", "kfa_bwd_dkdv", "kfa_bwd_dq", "kfa_bwd", "kfa_bwd_static_scratch", "kfa_selftest"):
             getattr(lib, name).restype = ctypes.c_int
         if lib.kfa_abi_version() != ABI_VERSION:
             raise KfaError(f"libkfa ABI {lib.kfa_abi_version()} != expected {ABI_VERSION}: rebuild")

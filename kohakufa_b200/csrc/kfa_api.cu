@@ -8,6 +8,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -328,6 +329,57 @@ int kfa_bwd(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// kfa_bwd_static_scratch: the backward for callers that cannot hand over scratch memory.
+// The per-row statistics (the only scratch of the backward) live in this fixed array instead of a
+// caller buffer. It exists once per GPU that loads the library, for the life of the process.
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+constexpr long long kStaticStatsFloats = KFA_STATIC_SCRATCH_BYTES / 4;
+static __device__ __align__(256) float g_static_stats[kStaticStatsFloats];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mutex;
+float* g_static_stats_addr[kMaxDevices] = {};  // device address of g_static_stats, per device
+
+// The array's name is only a host-side handle: the address a kernel can use comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+int static_stats_address(float** out) {
+  int dev = -1;
+  KFA_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(KFA_ERR_ARG, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (!g_static_stats_addr[dev]) {
+    void* addr = nullptr;
+    KFA_CUDA(cudaGetSymbolAddress(&addr, g_static_stats));
+    if (!addr) return fail(KFA_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+    g_static_stats_addr[dev] = static_cast<float*>(addr);
+  }
+  *out = g_static_stats_addr[dev];
+  return KFA_OK;
+}
+
+}  // namespace
+
+extern "C" int kfa_bwd_static_scratch(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v,
+                                      const KfaTensor4* out, const KfaTensor4* dout, const float* lse,
+                                      const KfaTensor4* dq, const KfaTensor4* dk, const KfaTensor4* dv,
+                                      float scale, int block, int dtype, int* dev_status, void* stream) {
+  int rc = check_tensor(q, "q");
+  if (rc) return rc;
+  const long long need = kfa_bwd_stats_bytes(q->shape[0], q->shape[1], q->shape[2]);
+  if (need > KFA_STATIC_SCRATCH_BYTES)
+    return fail(KFA_ERR_ARG,
+                "kfa_bwd_static_scratch: B*H*ceil(Sq/128) = %lld tiles need %lld bytes of statistics, the built-in "
+                "scratch holds %lld (%lld tiles): use kfa_bwd with a caller buffer",
+                need / 1536, need, (long long)KFA_STATIC_SCRATCH_BYTES, (long long)KFA_STATIC_SCRATCH_BYTES / 1536);
+  float* stats = nullptr;
+  if ((rc = static_stats_address(&stats))) return rc;
+  // Every float of every tile used is rewritten by the prepare step: nothing has to start at zero.
+  return kfa_bwd(q, k, v, out, dout, lse, stats, dq, dk, dv, scale, block, dtype, dev_status, stream);
+}
 
 #include "kfa_selftest.cuh"
 
