@@ -186,9 +186,13 @@ def config_dict(cfg, n_gpus):
     mode = "dense" if cfg.block == 0 else ("token-causal" if cfg.block == 1 else f"block-causal P={cfg.block}")
     return {
         "workload": f"{cfg.name}: {mode} attention fwd+bwd, B={cfg.batch} H={cfg.heads} S={cfg.seq} D={cfg.dim} per GPU",
-        "global_batch": cfg.batch * n_gpus,
+        "global_batch": cfg.batch if cfg.name.startswith("C5") else cfg.batch * n_gpus,
         "seq_len": cfg.seq,
-        "parallelism": f"batch x heads sharding over {n_gpus} GPU(s), no communication",
+        "parallelism": (
+            f"context-parallel K/V ring over {n_gpus} GPUs (zig-zag sequence shards, NCCL send/recv)"
+            if cfg.name.startswith("C5") and n_gpus > 1
+            else f"batch x heads sharding over {n_gpus} GPU(s), no communication"
+        ),
         "l2": "inputs larger than L2 (4 x 268 MB per step at C3); no flush needed",
     }
 
@@ -232,7 +236,14 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     # ---- inputs: this rank's batch shard, generated on the CPU, resident in HBM ----
-    host = workloads.make_inputs(cfg, seed_offset=rank)
+    # C5 (one 131072-token sequence): context-parallel ring over the N GPUs, strong scaling.
+    ring_mode = cfg.name.startswith("C5") and world > 1
+    if cfg.name.startswith("C5"):
+        chunk = cfg.seq // (2 * world)
+        mine = sorted({rank, 2 * world - 1 - rank}) if ring_mode else [0, 1]
+        host = workloads.make_piecewise_inputs(cfg, [(c * chunk, (c + 1) * chunk) for c in mine])
+    else:
+        host = workloads.make_inputs(cfg, seed_offset=rank)
     host = [t.transpose(1, 2).contiguous().pin_memory() for t in host]  # [B, S, H, D] storage
     q, k, v, dout = (t.to(dev, non_blocking=True).transpose(1, 2) for t in host)
     torch.cuda.synchronize()
@@ -240,9 +251,18 @@ def main():
     fwd_flops = flops / 3.5
     scale, block = cfg.scale, cfg.block
 
-    def step():
-        out, lse = attention_fwd_op(q, k, v, scale, block)
-        return attention_bwd_op(q, k, v, out, dout, lse, scale, block)
+    if ring_mode:
+        from kohakufa_b200 import ring
+
+        def step():
+            out, lse = ring.ring_forward(q, k, v, scale)
+            return ring.ring_backward(q, k, v, out, dout, lse, scale)
+
+    else:
+
+        def step():
+            out, lse = attention_fwd_op(q, k, v, scale, block)
+            return attention_bwd_op(q, k, v, out, dout, lse, scale, block)
 
     def barrier():
         if world > 1:
@@ -271,13 +291,18 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     ms_per_step = ms / args.steps
-    value = world * flops / (ms_per_step * 1e-3) / 1e12
+    # ring: all ranks work on ONE problem (strong scaling); otherwise every rank has its own copy
+    value = (1 if ring_mode else world) * flops / (ms_per_step * 1e-3) / 1e12
     assert _lib.device_status(dev) == 0, "a kernel wait timed out during the timed region"
 
     # ---- end to end: host buffers in, host buffers out, through the public API ----
     e2e = None
     if not args.no_e2e:
-        e2e = end_to_end(cfg, host, dev, attention, world, flops, max(3, args.steps // 4), barrier)
+        if ring_mode:
+            attn = lambda a, b, c, **kw: ring.ring_attention(a, b, c, scale=scale)  # noqa: E731
+            e2e = end_to_end(cfg, host, dev, attn, 1, flops, max(2, args.steps // 4), barrier, reduce_max=True)
+        else:
+            e2e = end_to_end(cfg, host, dev, attention, world, flops, max(3, args.steps // 4), barrier)
 
     if rank != 0:
         if world > 1:
@@ -287,8 +312,15 @@ def main():
     peaks, peak_kind = measured_peaks()
     units = {"fwd": 2, "dkdv": 4, "dq": 1}  # matmuls of the algorithmic count each kernel delivers
     dominant = max(("fwd", "dkdv", "dq"), key=lambda n: kernel_ms[n])
-    achieved = units[dominant] * (fwd_flops / 2) / (kernel_ms[dominant] * 1e-3) / 1e12
+    # the kernels were timed on this rank's local tensors (the whole problem unless ring mode)
+    local_fwd_flops = workloads.attention_flops(q.shape[0], q.shape[1], q.shape[2], q.shape[2], cfg.dim, cfg.block, backward=False)
+    achieved = units[dominant] * (local_fwd_flops / 2) / (kernel_ms[dominant] * 1e-3) / 1e12
     peak = peaks["bf16_tflops_sustained"]
+    # DRAM traffic of the dK/dV kernel from the ncu capture of the same shape at 16 heads
+    # (profiles/attention_kernels_c3_b1h16_ncu.md), scaled by the number of heads (it grows in proportion)
+    traffic = None
+    if dominant == "dkdv" and (cfg.seq, cfg.dim, cfg.block) == (8192, 128, 1) and not ring_mode:
+        traffic = 176.8e6 / 16 * q.shape[0] * q.shape[1]
     line = {
         "metric": METRIC,
         "value": value,
@@ -298,7 +330,7 @@ def main():
         "warmup": args.warmup,
         "ms_per_step": ms_per_step,
         "higher_is_better": True,
-        "scaling": "weak",
+        "scaling": "strong" if ring_mode else "weak",
         "vs_baseline": None,
         "dtype": "bf16" if cfg.dtype == torch.bfloat16 else "fp16",
         "data": "synthetic",
@@ -317,10 +349,10 @@ def main():
             "peak": peak,
             "unit": "TFLOP/s",
             "frac": achieved / peak,
-            "traffic": None,
+            "traffic": traffic,
             "note": f"algorithmic matmuls counted for this kernel: {units[dominant]} of 7; peak = {peak_kind} sustained cuBLAS bf16",
         },
-        "gpu_launches": 4 * args.steps,
+        "gpu_launches": (3 * world + 5 if ring_mode else 4) * args.steps,
         "clocks": sampler.summary(),
         "e2e": e2e,
     }
@@ -368,7 +400,7 @@ def time_kernels(cfg, q, k, v, dout, reps):
     return {n: sum(a.elapsed_time(b) for a, b in ev) / len(ev) for n, ev in events.items()}
 
 
-def end_to_end(cfg, host, dev, attention, world, flops, steps, barrier):
+def end_to_end(cfg, host, dev, attention, world, flops, steps, barrier, reduce_max=False):
     """The same metric through ``kohakufa_b200.attention`` with HOST buffers: every step copies q, k,
     v, dout from pinned host memory, runs forward + backward, and copies out, dq, dk, dv back."""
     hq, hk, hv, hdo = host
@@ -391,7 +423,7 @@ def end_to_end(cfg, host, dev, attention, world, flops, steps, barrier):
     stop.record()
     barrier()
     ms = start.elapsed_time(stop)
-    if world > 1:
+    if world > 1 or reduce_max:
         import torch.distributed as dist
 
         t = torch.tensor([ms], device=dev)

@@ -106,6 +106,48 @@ int kfa_bwd_static_scratch(const KfaTensor4* q, const KfaTensor4* k, const KfaTe
                            const KfaTensor4* dq, const KfaTensor4* dk, const KfaTensor4* dv, float scale,
                            int block, int dtype, int* dev_status, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Context-parallel building blocks: one attention problem whose sequence is spread over several
+ * GPUs, computed as (local queries) x (visiting keys / values) steps. Everything that crosses steps
+ * stays in fp32: the unnormalised O with its (m, l) per row in the forward, dQ / dK / dV accumulators
+ * in the backward; each is rounded to 16 bits once, by a finalize call. No counterpart in the
+ * reference, which is single-GPU. The host side (who sends what to whom) is kohakufa_b200/ring.py.
+ * --------------------------------------------------------------------------------------------- */
+
+/* fp32 rows of D elements: row r of (b, h) starts at ptr + (b * H + h) * head_stride + r * D. */
+typedef struct KfaAcc32 {
+  float* ptr;
+  int64_t head_stride; /* in floats */
+} KfaAcc32;
+
+/* One forward step: attention of q against the visiting k / v (block as in kfa_fwd). The partial
+ * result is written to (merge = 0) or merged into (merge = 1) the carry: o_acc, and ml with m at
+ * ml[(b*H+h) * ml_head_stride + r] and l at the same + ml_plane_stride. */
+int kfa_cp_fwd_step(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaAcc32* o_acc,
+                    float* ml, int64_t ml_head_stride, int64_t ml_plane_stride, int merge, float scale,
+                    int block, int dtype, int* dev_status, void* stream);
+
+/* out = o_acc / l rounded to 16 bits; lse [B, H, 2, Sq] = (m, log2 l), as kfa_fwd would have left them. */
+int kfa_cp_fwd_finalize(const KfaAcc32* o_acc, const float* ml, int64_t ml_head_stride,
+                        int64_t ml_plane_stride, const KfaTensor4* out, float* lse, int dtype, void* stream);
+
+/* One backward step for the visiting k / v: scaled fp32 dK, dV stored to (add = 0) or added to
+ * (add = 1) dk_acc / dv_acc. stats: as written by kfa_bwd_prepare for the local queries, with
+ * stats_head_stride floats between consecutive (b, h) (pass a pointer into the buffer to address a
+ * slice of query tiles). */
+int kfa_cp_bwd_dkdv_step(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* dout,
+                         const float* stats, int64_t stats_head_stride, const KfaAcc32* dk_acc,
+                         const KfaAcc32* dv_acc, int add, float scale, int block, int dtype, int* dev_status,
+                         void* stream);
+
+/* The same for dQ of the local queries. */
+int kfa_cp_bwd_dq_step(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* dout,
+                       const float* stats, int64_t stats_head_stride, const KfaAcc32* dq_acc, int add,
+                       float scale, int block, int dtype, int* dev_status, void* stream);
+
+/* grad = acc rounded to 16 bits. */
+int kfa_cp_grad_finalize(const KfaAcc32* acc, const KfaTensor4* grad, int dtype, void* stream);
+
 /* Hardware self-check of the building blocks (TMA tile load, MMA from shared memory, MMA with a
  * tensor-memory operand, tensor-memory loads / stores) on small fixed matrices. Synchronises.
  * `report` (may be NULL) receives `report_len` bytes of text. No counterpart in the reference. */

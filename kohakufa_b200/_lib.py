@@ -26,6 +26,11 @@ SYMBOLS = (
     "kfa_bwd_dq",
     "kfa_bwd",
     "kfa_bwd_static_scratch",
+    "kfa_cp_fwd_step",
+    "kfa_cp_fwd_finalize",
+    "kfa_cp_bwd_dkdv_step",
+    "kfa_cp_bwd_dq_step",
+    "kfa_cp_grad_finalize",
     "kfa_selftest",
 )
 
@@ -36,6 +41,19 @@ class KfaTensor4(ctypes.Structure):
         ("shape", ctypes.c_int64 * 4),
         ("stride", ctypes.c_int64 * 4),
     ]
+
+
+class KfaAcc32(ctypes.Structure):
+    _fields_ = [("ptr", ctypes.c_void_p), ("head_stride", ctypes.c_int64)]
+
+
+def acc32(t: torch.Tensor, row0: int = 0) -> KfaAcc32:
+    """Descriptor of a contiguous fp32 ``[B, H, S, D]`` accumulator, optionally starting at row ``row0``."""
+    assert t.dtype == torch.float32 and t.is_contiguous() and t.dim() == 4
+    a = KfaAcc32()
+    a.ptr = t.data_ptr() + 4 * row0 * t.shape[3]
+    a.head_stride = t.shape[2] * t.shape[3]
+    return a
 
 
 class KfaError(RuntimeError):
@@ -73,8 +91,15 @@ def load() -> ctypes.CDLL:
         lib.kfa_bwd_dq.argtypes = [T, T, T, T, fp, T, ctypes.c_float, ctypes.c_int, ctypes.c_int, ip, vp]
         lib.kfa_bwd.argtypes = [T, T, T, T, T, fp, fp, T, T, T, ctypes.c_float, ctypes.c_int, ctypes.c_int, ip, vp]
         lib.kfa_bwd_static_scratch.argtypes = [T, T, T, T, T, fp, T, T, T, ctypes.c_float, ctypes.c_int, ctypes.c_int, ip, vp]
+        A = ctypes.POINTER(KfaAcc32)
+        i64, f32, i32 = ctypes.c_int64, ctypes.c_float, ctypes.c_int
+        lib.kfa_cp_fwd_step.argtypes = [T, T, T, A, fp, i64, i64, i32, f32, i32, i32, ip, vp]
+        lib.kfa_cp_fwd_finalize.argtypes = [A, fp, i64, i64, T, fp, i32, vp]
+        lib.kfa_cp_bwd_dkdv_step.argtypes = [T, T, T, T, fp, i64, A, A, i32, f32, i32, i32, ip, vp]
+        lib.kfa_cp_bwd_dq_step.argtypes = [T, T, T, T, fp, i64, A, i32, f32, i32, i32, ip, vp]
+        lib.kfa_cp_grad_finalize.argtypes = [A, T, i32, vp]
         lib.kfa_selftest.argtypes = [ctypes.c_char_p, ctypes.c_int]
-        for name in ("kfa_fwd", "kfa_bwd_prepare", "kfa_bwd_dkdv", "kfa_bwd_dq", "kfa_bwd", "kfa_bwd_static_scratch", "kfa_selftest"):
+        for name in SYMBOLS[3:]:
             getattr(lib, name).restype = ctypes.c_int
         if lib.kfa_abi_version() != ABI_VERSION:
             raise KfaError(f"libkfa ABI {lib.kfa_abi_version()} != expected {ABI_VERSION}: rebuild")

@@ -200,6 +200,7 @@ void fill_bwd_params(kfa::BwdParams& p, const KfaTensor4* q, const KfaTensor4* k
   p.n_q128 = (p.Sq + 127) / 128;
   p.n_k128 = (p.Skv + 127) / 128;
   p.status = dev_status;
+  p.stats_sh = static_cast<long long>(p.n_q128) * 384;
 }
 
 }  // namespace
@@ -381,6 +382,7 @@ extern "C" int kfa_bwd_static_scratch(const KfaTensor4* q, const KfaTensor4* k, 
   return kfa_bwd(q, k, v, out, dout, lse, stats, dq, dk, dv, scale, block, dtype, dev_status, stream);
 }
 
+#include "kfa_cp.cuh"
 #include "kfa_selftest.cuh"
 
 #ifdef KFA_PROFILE

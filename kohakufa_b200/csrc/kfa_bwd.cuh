@@ -1,7 +1,7 @@
 // Attention backward for sm_100a, as three kernels:
 //
-//   kfa_bwd_prepare_kernel   delta = rowsum(fp32(dO) * fp32(O)); packs (m, log2 l, delta) per
-//                            128-row query tile, padded rows get m = +inf so their P is 0
+//   kfa_bwd_prepare_kernel   delta = rowsum(fp32(dO) * fp32(O)); packs (-m, -log2 l, -delta) per
+//                            128-row query tile, padded rows get -m = -inf so their P is 0
 //                            (reference: src/kohakufa/sm100/bwd.py:1358-1388)
 //   kfa_bwd_dkdv_kernel      one CTA per (batch, head, 128-key tile), looping over the query
 //                            tiles that see it, everything transposed (keys on TMEM lanes):
@@ -15,18 +15,23 @@
 // MMAs per tile pair, but no atomics, no fp32 accumulator round trip through HBM, and dQ is
 // bit-reproducible run to run.
 //
-// Both main kernels split every 128x128 score tile into two 64-column halves (a, b), each owned
-// by one warpgroup, so the tensor core works on one half while the warpgroup of the other half
-// computes P and dS:
-//   warps 0-3  half a        warps 4-7  half b        warp 8  MMA issue        warp 9  TMA producer
-// P^T / dS^T (dS in the dQ kernel) are written 16-bit into TMEM over the S / dP columns they came
-// from and are consumed from there as the A operand of the following MMAs.
+// Roles in both main kernels (320 threads):
+//   warps 0-3  columns 0-63 of every 128x128 score tile     warp 8  MMA issue (converged, one lane issues)
+//   warps 4-7  columns 64-127                               warp 9  TMA producer
+// Thread t of a warpgroup owns TMEM lane t (a key row in the dK/dV kernel, a query row in the dQ
+// kernel). A step has two compute phases, P from S and then dS from dP, each followed by an MMA that
+// consumes the 16-bit result straight from TMEM (P^T / dS^T overwrite the S^T / dP^T columns they
+// came from). The MMA warp interleaves the four (three) MMAs of consecutive steps,
+//   dK/dV:  dV(i)  S^T(i+1)  dK(i)  dP^T(i+1)          dQ:  S(j+1)  dQ(j)  dP(j+1)
+// so that while the warpgroups compute one phase the tensor core always has another MMA to run, and
+// every smem x smem MMA is a full 128-column one (64-column ones run at 2/3 rate on this part).
 //
 // Numerics kept from the reference (docs/precision.md:27-34, 90-114; bwd.py:1036-1043, 1083-1086):
 //   * P = exp2(fma(S - m, c, -log2 l)) from the two separate statistics, never a fused lse;
-//   * dS = (dP - delta) * P16 with P16 the 16-bit rounded P; dS, not scale * dS, is rounded to
-//     16 bits and fed to the MMAs; scale multiplies the fp32 dK and dQ accumulators afterwards;
-//   * padded keys and hidden (key, query) pairs get P = 0 exactly; padded query rows carry m = +inf.
+//   * dS, not scale * dS, is rounded to 16 bits and fed to the MMAs; scale multiplies the fp32 dK and
+//     dQ accumulators afterwards;
+//   * padded keys and hidden (key, query) pairs get P = 0 exactly; padded query rows carry -m = -inf.
+// One difference: dS = (dP - delta) * P uses the fp32 P, not the 16-bit rounded one (one rounding less).
 #pragma once
 
 #include "kfa_fwd.cuh"
@@ -40,13 +45,23 @@ struct BwdParams {
   long long dk_sb, dk_sh, dk_ss;
   void* dv;
   long long dv_sb, dv_sh, dv_ss;
-  const float* stats;  // [B*H, n_q128, 3, 128]: m, log2 l, delta
+  const float* stats;  // [B*H, n_q128, 3, 128]: -m, -log2 l, -delta
   int B, H, Sq, Skv;
   int P;
   float c;      // scale * log2(e)
   float scale;  // applied to fp32 dK and dQ
   int n_q128, n_k128;
   int* status;
+  long long stats_sh;  // floats between the statistics of consecutive (b, h): n_q128 * 384 unless a slice
+  // Context-parallel steps (acc_mode != 0): the scaled fp32 gradients are stored to (1) or added to
+  // (2) fp32 accumulators instead of being rounded to 16 bits. Row r of (b, h) at ptr + (b*H+h)*sh + r*D.
+  int acc_mode;
+  float* dq32;
+  long long dq32_sh;
+  float* dk32;
+  long long dk32_sh;
+  float* dv32;
+  long long dv32_sh;
 };
 
 struct PrepParams {
@@ -131,25 +146,50 @@ struct BwdCfg {
 // Issue helpers for the MMA warp (converged; `lead` is true in the one lane that issues). Operand
 // tiles are 128B-swizzled [rows][64] boxes, D / 64 of them 16 KB apart; descriptors are passed as
 // their low words (see sdesc_lo).
-// acc[128 x 64] = A[128 rows, D] * B[64 rows, D]^T, contraction over D. b_lo already points at B's
-// first row.
+// acc[128 x 128] = A[128 rows, D] * B[128 rows, D]^T, contraction over D.
 template <int D>
-__device__ __forceinline__ void issue_kmajor_n64(bool lead, uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo,
-                                                 uint32_t idesc) {
+__device__ __forceinline__ void issue_kmajor_n128(bool lead, uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo,
+                                                  uint32_t idesc) {
 #pragma unroll
   for (int kk = 0; kk < D / 16; ++kk) {
     const uint32_t off = ((kk >> 2) * TILE_BYTES_64 + (kk & 3) * 32) >> 4;
     umma_ss_lead(lead, d_tmem, a_lo + off, b_lo + off, idesc, kk > 0 ? 1u : 0u);
   }
 }
-// acc[128 x D] (+)= A16[128 x 64 from TMEM] * B[64 rows, D], contraction over B's rows (MN-major B,
-// leading offset = one 16 KB box). b_lo points at B's first row.
+// acc[128 x D] (+)= A16[128 x 128] * B[128 rows, D], contraction over B's rows (MN-major B, leading
+// offset = one 16 KB box). The 16-bit A operand sits in TMEM as two 32-column pieces: contraction
+// indices 0-63 at a_tmem, 64-127 at a_tmem + 64 (where the two warpgroups wrote their halves).
 template <int D>
-__device__ __forceinline__ void issue_tmemA_k64(bool lead, uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
-                                                uint32_t idesc, bool acc) {
+__device__ __forceinline__ void issue_tmemA_k128(bool lead, uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
+                                                 uint32_t idesc, bool acc) {
 #pragma unroll
-  for (int kk = 0; kk < 4; ++kk)
-    umma_ts_lead(lead, d_tmem, a_tmem + kk * 8, b_lo + ((kk * 16 * 128) >> 4), idesc, (acc || kk > 0) ? 1u : 0u);
+  for (int kk = 0; kk < 8; ++kk)
+    umma_ts_lead(lead, d_tmem, a_tmem + (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8), b_lo + ((kk * 16 * 128) >> 4), idesc,
+                 (acc || kk > 0) ? 1u : 0u);
+}
+
+// Stores (add = false) or adds (add = true) a row of an fp32 accumulator times mul to fp32 memory.
+__device__ __forceinline__ void store_acc_row_f32(uint32_t taddr, int col0, int ncols, float mul, float* grow,
+                                                  bool valid, bool add) {
+  for (int cc = col0; cc < col0 + ncols; cc += 32) {
+    float o[32];
+    tmem_ld32(taddr + cc, reinterpret_cast<uint32_t*>(o));
+    tmem_wait_ld();
+    if (valid) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {
+        float4 w = make_float4(o[i] * mul, o[i + 1] * mul, o[i + 2] * mul, o[i + 3] * mul);
+        if (add) {
+          const float4 old = *reinterpret_cast<const float4*>(grow + cc + i);
+          w.x += old.x;
+          w.y += old.y;
+          w.z += old.z;
+          w.w += old.w;
+        }
+        *reinterpret_cast<float4*>(grow + cc + i) = w;
+      }
+    }
+  }
 }
 
 // Writes a row of an fp32 accumulator (TMEM columns [col0, col0 + ncols)) times mul as 16-bit.
@@ -174,19 +214,17 @@ __device__ __forceinline__ void store_acc_row(uint32_t taddr, int col0, int ncol
   }
 }
 
-// 32 columns (queries) of one key row in the dK / dV kernel: from S^T and dP^T (fp32, two columns
-// per float2) and the per-query statistics in shared memory (-m at st[0..], -log2 l at st[128..],
-// -delta at st[256..]) to the packed 16-bit P^T and dS^T words.
-//   P = exp2(fma(S - m, c, -log2 l));  dS = (dP - delta) * P   (fp32 P; dS rounded once, unscaled)
-// MASKED: columns whose query index (q_first + column) is below qmin get P = dS = 0.
+// P of 32 columns (queries) of one key row in the dK / dV kernel, from S^T (fp32, two columns per
+// float2) and the per-query statistics in shared memory (-m at st[0..], -log2 l at st[128..]):
+//   P = exp2(fma(S - m, c, -log2 l)), kept in fp32 (pr) and packed to 16 bits (pk).
+// MASKED: columns whose query index (q_first + column) is below qmin get P = 0.
 template <bool BF16, bool MASKED>
-__device__ __forceinline__ void pds_cols_by_query(const float2* sv, const float2* dp, const float* st, float2 c2,
-                                                  int q_first, int qmin, uint32_t* pk, uint32_t* dk) {
+__device__ __forceinline__ void p_cols_by_query(const float2* sv, const float* st, float2 c2, int q_first, int qmin,
+                                                float2* pr, uint32_t* pk) {
 #pragma unroll
   for (int x = 0; x < 32; x += 4) {
     const float4 nm = *reinterpret_cast<const float4*>(st + x);
     const float4 nl = *reinterpret_cast<const float4*>(st + 128 + x);
-    const float4 nd = *reinterpret_cast<const float4*>(st + 256 + x);
     const float2 x0 = __ffma2_rn(__fadd2_rn(sv[x / 2], make_float2(nm.x, nm.y)), c2, make_float2(nl.x, nl.y));
     const float2 x1 = __ffma2_rn(__fadd2_rn(sv[x / 2 + 1], make_float2(nm.z, nm.w)), c2, make_float2(nl.z, nl.w));
     float2 p0 = make_float2(ex2(x0.x), ex2(x0.y));
@@ -197,29 +235,45 @@ __device__ __forceinline__ void pds_cols_by_query(const float2* sv, const float2
       if (q_first + x + 2 < qmin) p1.x = 0.f;
       if (q_first + x + 3 < qmin) p1.y = 0.f;
     }
+    pr[x / 2] = p0;
+    pr[x / 2 + 1] = p1;
     pk[x / 2] = pack16<BF16>(p0.x, p0.y);
     pk[x / 2 + 1] = pack16<BF16>(p1.x, p1.y);
-    const float2 d0 = __fmul2_rn(__fadd2_rn(dp[x / 2], make_float2(nd.x, nd.y)), p0);
-    const float2 d1 = __fmul2_rn(__fadd2_rn(dp[x / 2 + 1], make_float2(nd.z, nd.w)), p1);
+  }
+}
+// dS = (dP - delta) * P of the same 32 columns (-delta at st[256..]), rounded once to 16 bits, unscaled.
+template <bool BF16>
+__device__ __forceinline__ void ds_cols_by_query(const float2* dp, const float2* pr, const float* st, uint32_t* dk) {
+#pragma unroll
+  for (int x = 0; x < 32; x += 4) {
+    const float4 nd = *reinterpret_cast<const float4*>(st + 256 + x);
+    const float2 d0 = __fmul2_rn(__fadd2_rn(dp[x / 2], make_float2(nd.x, nd.y)), pr[x / 2]);
+    const float2 d1 = __fmul2_rn(__fadd2_rn(dp[x / 2 + 1], make_float2(nd.z, nd.w)), pr[x / 2 + 1]);
     dk[x / 2] = pack16<BF16>(d0.x, d0.y);
     dk[x / 2 + 1] = pack16<BF16>(d1.x, d1.y);
   }
 }
 
-// 32 columns (keys) of one query row in the dQ kernel: the row's statistics are scalars.
-// MASKED: columns at or beyond `lim` (relative to this group's first column) get dS = 0.
-template <bool BF16, bool MASKED>
-__device__ __forceinline__ void ds_cols_by_key(const float2* sv, const float2* dp, float2 nm, float2 c2, float2 nl,
-                                               float2 nd, int lim, uint32_t* dk) {
+// The same for one query row of the dQ kernel, whose statistics are scalars. 32 columns (keys);
+// MASKED: columns at or beyond `lim` (relative to this group's first column) get P = 0.
+template <bool MASKED>
+__device__ __forceinline__ void p_cols_by_key(const float2* sv, float2 nm, float2 c2, float2 nl, int lim, float2* pr) {
 #pragma unroll
   for (int x = 0; x < 16; ++x) {
     const float2 e = __ffma2_rn(__fadd2_rn(sv[x], nm), c2, nl);
-    float2 pr = make_float2(ex2(e.x), ex2(e.y));
+    float2 q = make_float2(ex2(e.x), ex2(e.y));
     if constexpr (MASKED) {
-      if (2 * x >= lim) pr.x = 0.f;
-      if (2 * x + 1 >= lim) pr.y = 0.f;
+      if (2 * x >= lim) q.x = 0.f;
+      if (2 * x + 1 >= lim) q.y = 0.f;
     }
-    const float2 d = __fmul2_rn(__fadd2_rn(dp[x], nd), pr);
+    pr[x] = q;
+  }
+}
+template <bool BF16>
+__device__ __forceinline__ void ds_cols_by_key(const float2* dp, const float2* pr, float2 nd, uint32_t* dk) {
+#pragma unroll
+  for (int x = 0; x < 16; ++x) {
+    const float2 d = __fmul2_rn(__fadd2_rn(dp[x], nd), pr[x]);
     dk[x] = pack16<BF16>(d.x, d.y);
   }
 }
@@ -243,13 +297,15 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const uint32_t sV = smem_base + Cfg::TILE_BYTES;
   const uint32_t sSlot = smem_base + 2 * Cfg::TILE_BYTES;  // slot: Q | dO | stats
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::KV_SMEM_TILES);
-  constexpr int B_KV = 0;                 // 1
-  constexpr int B_QREADY = 1;             // NSL
-  constexpr int B_QFREE = 1 + NSL;        // NSL
-  constexpr int B_SDP = 1 + 2 * NSL;      // 2
-  constexpr int B_PDS = 3 + 2 * NSL;      // 2
-  constexpr int B_ACC = 5 + 2 * NSL;      // 1
-  constexpr int B_DRAIN = 6 + 2 * NSL;    // 1
+  constexpr int B_KV = 0;                 // 1       K, V landed
+  constexpr int B_QREADY = 1;             // NSL     Q_i, dO_i, stats_i landed
+  constexpr int B_QFREE = 1 + NSL;        // NSL     the MMAs that read the slot have retired
+  constexpr int B_S = 1 + 2 * NSL;        // S^T(i) in TMEM
+  constexpr int B_DP = 2 + 2 * NSL;       // dP^T(i) in TMEM
+  constexpr int B_P = 3 + 2 * NSL;        // P^T(i) stored by both warpgroups (256 arrivals)
+  constexpr int B_DS = 4 + 2 * NSL;       // dS^T(i) stored by both warpgroups
+  constexpr int B_ACC = 5 + 2 * NSL;      // dV, dK complete
+  constexpr int B_DRAIN = 6 + 2 * NSL;
   constexpr int N_BARS = 7 + 2 * NSL;
   static_assert(N_BARS * 8 + 16 <= 256, "barrier block too small");
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + N_BARS);
@@ -274,10 +330,10 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       mbar_init(bar(B_QREADY + i), 1);
       mbar_init(bar(B_QFREE + i), 1);
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(bar(B_SDP + i), 1);
-      mbar_init(bar(B_PDS + i), 128);
-    }
+    mbar_init(bar(B_S), 1);
+    mbar_init(bar(B_DP), 1);
+    mbar_init(bar(B_P), 256);
+    mbar_init(bar(B_DS), 256);
     mbar_init(bar(B_ACC), 1);
     mbar_init(bar(B_DRAIN), 1);
     *s_abort = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
@@ -319,7 +375,7 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       int issued = 0;
       for (int s = 0; s < n_steps; ++s) {
         const int slot = s % NSL, use = s / NSL;
-        if (use > 0) ok = mbar_wait(bar(B_QFREE + slot), (use - 1) & 1, ctl, 11);
+        if (use > 0) ok = mbar_wait(bar(B_QFREE + slot), (use - 1) & 1, ctl, 1);
         if (!ok) break;
         const int i = first_i + s;
         const uint32_t base = sSlot + slot * Cfg::KV_SLOT_BYTES;
@@ -329,11 +385,11 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           tma_load_4d(base + Cfg::TILE_BYTES + ch * TILE_BYTES_64, &tmDO, bar(B_QREADY + slot), ch * 64,
                       i * 128, h, b);
         }
-        bulk_load(base + 2 * Cfg::TILE_BYTES, p.stats + (static_cast<long long>(bh) * p.n_q128 + i) * 384,
+        bulk_load(base + 2 * Cfg::TILE_BYTES, p.stats + static_cast<long long>(bh) * p.stats_sh + i * 384ll,
                   STATS_BYTES, bar(B_QREADY + slot));
         issued = s + 1;
       }
-      if (!ok) {
+      if (!ok) {  // aborting: let the copies in flight land before the CTA gives up its shared memory
         for (int s = max(issued - NSL, 0); s < issued; ++s) {
           const long long t0 = clock64();
           while (!mbar_try_wait(bar(B_QREADY + s % NSL), (s / NSL) & 1) && clock64() - t0 < 2000000ll) {
@@ -343,25 +399,21 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
   } else if (warp == 8) {
     // =========================== MMA issue ===========================
-    // The whole warp runs this role converged; one elected lane issues the tcgen05 instructions.
     if (n_steps > 0) {
       const bool lead = elect_one();
-      constexpr uint32_t IDESC_S = make_idesc(BF16, false, 128, 64);
+      constexpr uint32_t IDESC_S = make_idesc(BF16, false, 128, 128);
       constexpr uint32_t IDESC_ACC = make_idesc(BF16, true, 128, D);
       const uint32_t tST = tmem + Cfg::TM_S, tDP = tmem + Cfg::TM_DP;
       const uint32_t tDV = tmem + Cfg::TM_ACC0, tDK = tmem + Cfg::TM_ACC1;
       const uint32_t k_lo = sdesc_lo(sK, 16), v_lo = sdesc_lo(sV, 16);
-      constexpr uint32_t HALF_ROWS = (64 * 128) >> 4;  // 64 rows further down a box, in descriptor units
-      bool ok = mbar_wait_warp(bar(B_KV), 0, ctl, 12);
-      if (ok) ok = mbar_wait_warp(bar(B_QREADY + 0), 0, ctl, 13);
+      bool ok = mbar_wait_warp(bar(B_KV), 0, ctl, 2);
+      if (ok) ok = mbar_wait_warp(bar(B_QREADY + 0), 0, ctl, 3);
       if (ok) {
         tc_fence_after();
-        const uint32_t q_lo = sdesc_lo(sSlot, 16), do_lo = sdesc_lo(sSlot + Cfg::TILE_BYTES, 16);
-        for (int hq = 0; hq < 2; ++hq) {
-          issue_kmajor_n64<D>(lead, tST + 64 * hq, k_lo, q_lo + hq * HALF_ROWS, IDESC_S);
-          issue_kmajor_n64<D>(lead, tDP + 64 * hq, v_lo, do_lo + hq * HALF_ROWS, IDESC_S);
-          umma_commit_lead(lead, bar(B_SDP + hq));
-        }
+        issue_kmajor_n128<D>(lead, tST, k_lo, sdesc_lo(sSlot, 16), IDESC_S);
+        umma_commit_lead(lead, bar(B_S));
+        issue_kmajor_n128<D>(lead, tDP, v_lo, sdesc_lo(sSlot + Cfg::TILE_BYTES, 16), IDESC_S);
+        umma_commit_lead(lead, bar(B_DP));
       }
       for (int s = 0; s < n_steps && ok; ++s) {
         const int slot = s % NSL;
@@ -370,27 +422,27 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const int nslot = (s + 1) % NSL;
         const uint32_t q_n = sSlot + nslot * Cfg::KV_SLOT_BYTES;
         const uint32_t do_n = q_n + Cfg::TILE_BYTES;
-        // as the MN-major B operand of dV / dK (leading offset: the next 64 columns of D)
-        const uint32_t qmn_lo = sdesc_lo(q_s, TILE_BYTES_64), domn_lo = sdesc_lo(do_s, TILE_BYTES_64);
-        // as the K-major B operand of the next step's S^T / dP^T
-        const uint32_t qn_lo = sdesc_lo(q_n, 16), don_lo = sdesc_lo(do_n, 16);
-        for (int hq = 0; hq < 2 && ok; ++hq) {
-          ok = mbar_wait_warp(bar(B_PDS + hq), s & 1, ctl, 14);
+        const bool more = s + 1 < n_steps;
+        // dV += P^T(i) dO_i, then S^T(i+1) may overwrite the P^T columns
+        ok = mbar_wait_warp(bar(B_P), s & 1, ctl, 4);
+        if (!ok) break;
+        tc_fence_after();
+        issue_tmemA_k128<D>(lead, tDV, tST, sdesc_lo(do_s, TILE_BYTES_64), IDESC_ACC, s > 0);
+        if (more) {
+          ok = mbar_wait_warp(bar(B_QREADY + nslot), ((s + 1) / NSL) & 1, ctl, 5);
           if (!ok) break;
-          tc_fence_after();
-          issue_tmemA_k64<D>(lead, tDV, tST + 64 * hq, domn_lo + hq * HALF_ROWS, IDESC_ACC, s > 0 || hq > 0);
-          issue_tmemA_k64<D>(lead, tDK, tDP + 64 * hq, qmn_lo + hq * HALF_ROWS, IDESC_ACC, s > 0 || hq > 0);
-          if (hq == 1) umma_commit_lead(lead, bar(B_QFREE + slot));
-          if (s + 1 < n_steps) {
-            if (hq == 0) {
-              ok = mbar_wait_warp(bar(B_QREADY + nslot), ((s + 1) / NSL) & 1, ctl, 15);
-              if (!ok) break;
-              tc_fence_after();
-            }
-            issue_kmajor_n64<D>(lead, tST + 64 * hq, k_lo, qn_lo + hq * HALF_ROWS, IDESC_S);
-            issue_kmajor_n64<D>(lead, tDP + 64 * hq, v_lo, don_lo + hq * HALF_ROWS, IDESC_S);
-            umma_commit_lead(lead, bar(B_SDP + hq));
-          }
+          issue_kmajor_n128<D>(lead, tST, k_lo, sdesc_lo(q_n, 16), IDESC_S);
+          umma_commit_lead(lead, bar(B_S));
+        }
+        // dK += dS^T(i) Q_i, then dP^T(i+1) may overwrite the dS^T columns
+        ok = mbar_wait_warp(bar(B_DS), s & 1, ctl, 6);
+        if (!ok) break;
+        tc_fence_after();
+        issue_tmemA_k128<D>(lead, tDK, tDP, sdesc_lo(q_s, TILE_BYTES_64), IDESC_ACC, s > 0);
+        umma_commit_lead(lead, bar(B_QFREE + slot));
+        if (more) {
+          issue_kmajor_n128<D>(lead, tDP, v_lo, sdesc_lo(do_n, 16), IDESC_S);
+          umma_commit_lead(lead, bar(B_DP));
         }
       }
       if (ok) umma_commit_lead(lead, bar(B_ACC));
@@ -403,7 +455,7 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
   } else {
     // =========================== P^T / dS^T and epilogue ===========================
-    const int hq = warp >> 2;
+    const int hq = warp >> 2;  // which 64 query columns of every tile
     const int k_in = tid & 127;
     const int key = kv0 + k_in;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
@@ -413,61 +465,85 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     int qmin = 0;
     if (key >= p.Skv) qmin = 0x7fffffff;
     else if (p.P > 0) qmin = (key / p.P) * p.P;
-    const float c = p.c;
+    const float2 c2 = make_float2(p.c, p.c);
     bool ok = true;
     for (int s = 0; s < n_steps; ++s) {
       const int slot = s % NSL;
       const int i = first_i + s;
-      const int q0 = i * 128 + 64 * hq;  // query of this half's column 0
+      const int q0 = i * 128 + 64 * hq;  // query of this warpgroup's column 0
       // masked step: some (key, query) pair of this tile pair is hidden, or keys are padded
       const bool masked = ragged_keys || (p.P > 0 && key_limit(i * 128, p.P, p.Skv) < kv0 + 128);
-      ok = mbar_wait_warp(bar(B_QREADY + slot), (s / NSL) & 1, ctl, 16);  // stats of this step
-      if (ok) ok = mbar_wait_warp(bar(B_SDP + hq), s & 1, ctl, 17);
+      ok = mbar_wait_warp(bar(B_QREADY + slot), (s / NSL) & 1, ctl, 7);  // stats of this step
+      if (ok) ok = mbar_wait_warp(bar(B_S), s & 1, ctl, 8);
       if (!ok) break;
       tc_fence_after();
       const float* st =
           reinterpret_cast<const float*>(smem + 2 * Cfg::TILE_BYTES + slot * Cfg::KV_SLOT_BYTES +
                                          2 * Cfg::TILE_BYTES) + 64 * hq;
-      const float2 c2 = make_float2(c, c);
+      float2 pr[32];  // fp32 P of this thread's 64 columns, kept for the dS phase
       {
-        float2 sv[32], dp[32];  // 64 columns of S^T and of dP^T
+        float2 sv[32];
         tmem_ld32(tS, reinterpret_cast<uint32_t*>(sv));
-        tmem_ld32(tDP, reinterpret_cast<uint32_t*>(dp));
         tmem_ld32(tS + 32, reinterpret_cast<uint32_t*>(sv + 16));
+        tmem_wait_ld();
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+          uint32_t pk[16];
+          if (masked)
+            p_cols_by_query<BF16, true>(sv + 16 * g, st + 32 * g, c2, q0 + 32 * g, qmin, pr + 16 * g, pk);
+          else
+            p_cols_by_query<BF16, false>(sv + 16 * g, st + 32 * g, c2, q0 + 32 * g, qmin, pr + 16 * g, pk);
+          tmem_st16(tS + 16 * g, pk);  // 16-bit P^T over columns this thread has already read
+        }
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar(B_P));
+      ok = mbar_wait_warp(bar(B_DP), s & 1, ctl, 9);
+      if (!ok) break;
+      tc_fence_after();
+      {
+        float2 dp[32];
+        tmem_ld32(tDP, reinterpret_cast<uint32_t*>(dp));
         tmem_ld32(tDP + 32, reinterpret_cast<uint32_t*>(dp + 16));
         tmem_wait_ld();
 #pragma unroll
         for (int g = 0; g < 2; ++g) {
-          uint32_t pk[16], dk[16];
-          if (masked)
-            pds_cols_by_query<BF16, true>(sv + 16 * g, dp + 16 * g, st + 32 * g, c2, q0 + 32 * g, qmin, pk, dk);
-          else
-            pds_cols_by_query<BF16, false>(sv + 16 * g, dp + 16 * g, st + 32 * g, c2, q0 + 32 * g, qmin, pk, dk);
-          // 16-bit P^T / dS^T over columns already read
-          tmem_st16(tS + 16 * g, pk);
+          uint32_t dk[16];
+          ds_cols_by_query<BF16>(dp + 16 * g, pr + 16 * g, st + 32 * g, dk);
           tmem_st16(tDP + 16 * g, dk);
         }
       }
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(bar(B_PDS + hq));
+      mbar_arrive(bar(B_DS));
     }
-    // ---- epilogue: half a stores dV, half b stores scale * dK ----
+    // ---- epilogue: warps 0-3 store dV, warps 4-7 store scale * dK ----
     const bool valid = key < p.Skv;
     uint8_t* grow;
     if (hq == 0)
       grow = reinterpret_cast<uint8_t*>(p.dv) + 2 * (b * p.dv_sb + h * p.dv_sh + static_cast<long long>(key) * p.dv_ss);
     else
       grow = reinterpret_cast<uint8_t*>(p.dk) + 2 * (b * p.dk_sb + h * p.dk_sh + static_cast<long long>(key) * p.dk_ss);
+    float* grow32 = nullptr;
+    if (p.acc_mode != 0)
+      grow32 = (hq == 0 ? p.dv32 + (static_cast<long long>(b) * p.H + h) * p.dv32_sh
+                        : p.dk32 + (static_cast<long long>(b) * p.H + h) * p.dk32_sh) +
+               static_cast<long long>(key) * D;
     if (n_steps == 0) {
-      if (valid)
+      if (valid && p.acc_mode == 0)
         for (int cc = 0; cc < D; cc += 8) *reinterpret_cast<uint4*>(grow + 2 * cc) = make_uint4(0, 0, 0, 0);
+      if (valid && p.acc_mode == 1)
+        for (int cc = 0; cc < D; cc += 4) *reinterpret_cast<float4*>(grow32 + cc) = make_float4(0.f, 0.f, 0.f, 0.f);
     } else {
-      ok = mbar_wait_warp(bar(B_ACC), 0, ctl, 18) && ok;
+      ok = mbar_wait_warp(bar(B_ACC), 0, ctl, 9) && ok;
       if (ok) {
         tc_fence_after();
-        store_acc_row<BF16>(tmem + (hq ? Cfg::TM_ACC1 : Cfg::TM_ACC0) + lane_base, 0, D,
-                            hq ? p.scale : 1.0f, grow, valid);
+        const uint32_t tacc = tmem + (hq ? Cfg::TM_ACC1 : Cfg::TM_ACC0) + lane_base;
+        if (p.acc_mode == 0)
+          store_acc_row<BF16>(tacc, 0, D, hq ? p.scale : 1.0f, grow, valid);
+        else
+          store_acc_row_f32(tacc, 0, D, hq ? p.scale : 1.0f, grow32, valid, p.acc_mode == 2);
       }
     }
   }
@@ -504,11 +580,13 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   const uint32_t sDO = smem_base + Cfg::TILE_BYTES;
   const uint32_t sSlot = smem_base + 2 * Cfg::TILE_BYTES;  // slot: K | V
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::Q_SMEM_TILES);
-  constexpr int B_Q = 0;
-  constexpr int B_KVREADY = 1;
-  constexpr int B_KVFREE = 1 + NSL;
-  constexpr int B_SDP = 1 + 2 * NSL;
-  constexpr int B_DS = 3 + 2 * NSL;
+  constexpr int B_Q = 0;                  // Q, dO landed
+  constexpr int B_KVREADY = 1;            // NSL
+  constexpr int B_KVFREE = 1 + NSL;       // NSL
+  constexpr int B_S = 1 + 2 * NSL;        // S(j) in TMEM
+  constexpr int B_DP = 2 + 2 * NSL;       // dP(j) in TMEM
+  constexpr int B_SREAD = 3 + 2 * NSL;    // both warpgroups have read S(j) (256 arrivals)
+  constexpr int B_DS = 4 + 2 * NSL;       // dS(j) stored by both warpgroups
   constexpr int B_ACC = 5 + 2 * NSL;
   constexpr int B_DRAIN = 6 + 2 * NSL;
   constexpr int N_BARS = 7 + 2 * NSL;
@@ -535,10 +613,10 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       mbar_init(bar(B_KVREADY + i), 1);
       mbar_init(bar(B_KVFREE + i), 1);
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(bar(B_SDP + i), 1);
-      mbar_init(bar(B_DS + i), 128);
-    }
+    mbar_init(bar(B_S), 1);
+    mbar_init(bar(B_DP), 1);
+    mbar_init(bar(B_SREAD), 256);
+    mbar_init(bar(B_DS), 256);
     mbar_init(bar(B_ACC), 1);
     mbar_init(bar(B_DRAIN), 1);
     *s_abort = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
@@ -579,7 +657,7 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       int issued = 0;
       for (int j = 0; j < n_steps; ++j) {
         const int slot = j % NSL, use = j / NSL;
-        if (use > 0) ok = mbar_wait(bar(B_KVFREE + slot), (use - 1) & 1, ctl, 21);
+        if (use > 0) ok = mbar_wait(bar(B_KVFREE + slot), (use - 1) & 1, ctl, 1);
         if (!ok) break;
         const uint32_t base = sSlot + slot * Cfg::Q_SLOT_BYTES;
         mbar_expect_tx(bar(B_KVREADY + slot), 2 * Cfg::TILE_BYTES);
@@ -602,45 +680,42 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     // MMA issue: the whole warp converged, one elected lane issues.
     {
       const bool lead = elect_one();
-      constexpr uint32_t IDESC_S = make_idesc(BF16, false, 128, 64);
+      constexpr uint32_t IDESC_S = make_idesc(BF16, false, 128, 128);
       constexpr uint32_t IDESC_ACC = make_idesc(BF16, true, 128, D);
       const uint32_t tS = tmem + Cfg::TM_S, tDP = tmem + Cfg::TM_DP, tDQ = tmem + Cfg::TM_ACC0;
       const uint32_t q_lo = sdesc_lo(sQ, 16), do_lo = sdesc_lo(sDO, 16);
-      constexpr uint32_t HALF_ROWS = (64 * 128) >> 4;
-      bool ok = mbar_wait_warp(bar(B_Q), 0, ctl, 22);
-      if (ok) ok = mbar_wait_warp(bar(B_KVREADY + 0), 0, ctl, 23);
+      bool ok = mbar_wait_warp(bar(B_Q), 0, ctl, 2);
+      if (ok) ok = mbar_wait_warp(bar(B_KVREADY + 0), 0, ctl, 3);
       if (ok) {
         tc_fence_after();
-        const uint32_t k_lo = sdesc_lo(sSlot, 16), v_lo = sdesc_lo(sSlot + Cfg::TILE_BYTES, 16);
-        for (int hk = 0; hk < 2; ++hk) {
-          issue_kmajor_n64<D>(lead, tS + 64 * hk, q_lo, k_lo + hk * HALF_ROWS, IDESC_S);
-          issue_kmajor_n64<D>(lead, tDP + 64 * hk, do_lo, v_lo + hk * HALF_ROWS, IDESC_S);
-          umma_commit_lead(lead, bar(B_SDP + hk));
-        }
+        issue_kmajor_n128<D>(lead, tS, q_lo, sdesc_lo(sSlot, 16), IDESC_S);
+        umma_commit_lead(lead, bar(B_S));
+        issue_kmajor_n128<D>(lead, tDP, do_lo, sdesc_lo(sSlot + Cfg::TILE_BYTES, 16), IDESC_S);
+        umma_commit_lead(lead, bar(B_DP));
       }
       for (int j = 0; j < n_steps && ok; ++j) {
         const int slot = j % NSL;
         const uint32_t k_s = sSlot + slot * Cfg::Q_SLOT_BYTES;
         const int nslot = (j + 1) % NSL;
         const uint32_t k_n = sSlot + nslot * Cfg::Q_SLOT_BYTES;
-        const uint32_t kmn_lo = sdesc_lo(k_s, TILE_BYTES_64);
-        const uint32_t kn_lo = sdesc_lo(k_n, 16), vn_lo = sdesc_lo(k_n + Cfg::TILE_BYTES, 16);
-        for (int hk = 0; hk < 2 && ok; ++hk) {
-          ok = mbar_wait_warp(bar(B_DS + hk), j & 1, ctl, 24);
+        const bool more = j + 1 < n_steps;
+        if (more) {  // S(j+1) as soon as the warpgroups hold S(j) in registers
+          ok = mbar_wait_warp(bar(B_KVREADY + nslot), ((j + 1) / NSL) & 1, ctl, 4);
+          if (ok) ok = mbar_wait_warp(bar(B_SREAD), j & 1, ctl, 5);
           if (!ok) break;
           tc_fence_after();
-          issue_tmemA_k64<D>(lead, tDQ, tDP + 64 * hk, kmn_lo + hk * HALF_ROWS, IDESC_ACC, j > 0 || hk > 0);
-          if (hk == 1) umma_commit_lead(lead, bar(B_KVFREE + slot));
-          if (j + 1 < n_steps) {
-            if (hk == 0) {
-              ok = mbar_wait_warp(bar(B_KVREADY + nslot), ((j + 1) / NSL) & 1, ctl, 25);
-              if (!ok) break;
-              tc_fence_after();
-            }
-            issue_kmajor_n64<D>(lead, tS + 64 * hk, q_lo, kn_lo + hk * HALF_ROWS, IDESC_S);
-            issue_kmajor_n64<D>(lead, tDP + 64 * hk, do_lo, vn_lo + hk * HALF_ROWS, IDESC_S);
-            umma_commit_lead(lead, bar(B_SDP + hk));
-          }
+          issue_kmajor_n128<D>(lead, tS, q_lo, sdesc_lo(k_n, 16), IDESC_S);
+          umma_commit_lead(lead, bar(B_S));
+        }
+        // dQ += dS(j) K_j, then dP(j+1) may overwrite the dS columns
+        ok = mbar_wait_warp(bar(B_DS), j & 1, ctl, 6);
+        if (!ok) break;
+        tc_fence_after();
+        issue_tmemA_k128<D>(lead, tDQ, tDP, sdesc_lo(k_s, TILE_BYTES_64), IDESC_ACC, j > 0);
+        umma_commit_lead(lead, bar(B_KVFREE + slot));
+        if (more) {
+          issue_kmajor_n128<D>(lead, tDP, do_lo, sdesc_lo(k_n + Cfg::TILE_BYTES, 16), IDESC_S);
+          umma_commit_lead(lead, bar(B_DP));
         }
       }
       if (ok) umma_commit_lead(lead, bar(B_ACC));
@@ -652,13 +727,13 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       }
     }
   } else {
-    const int hk = warp >> 2;
+    const int hk = warp >> 2;  // which 64 key columns of every tile
     const int r_in = tid & 127;
     const int row = row0 + r_in;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tS = tmem + Cfg::TM_S + 64 * hk + lane_base;
     const uint32_t tDP = tmem + Cfg::TM_DP + 64 * hk + lane_base;
-    const float* st = p.stats + (static_cast<long long>(bh) * p.n_q128 + qt) * 384;
+    const float* st = p.stats + static_cast<long long>(bh) * p.stats_sh + qt * 384ll;
     const float2 nm = make_float2(st[r_in], st[r_in]);                // -m
     const float2 nl = make_float2(st[128 + r_in], st[128 + r_in]);    // -log2 l
     const float2 nd = make_float2(st[256 + r_in], st[256 + r_in]);    // -delta
@@ -666,37 +741,57 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     const float2 c2 = make_float2(p.c, p.c);
     bool ok = true;
     for (int j = 0; j < n_steps; ++j) {
-      ok = mbar_wait_warp(bar(B_SDP + hk), j & 1, ctl, 26);
+      ok = mbar_wait_warp(bar(B_S), j & 1, ctl, 7);
       if (!ok) break;
       tc_fence_after();
-      const int lim = my_limit - j * 128 - 64 * hk;  // visible columns of this half (masked tiles)
+      const int lim = my_limit - j * 128 - 64 * hk;  // visible columns of this warpgroup (masked tiles)
+      float2 pr[32];
       {
-        float2 sv[32], dp[32];
+        float2 sv[32];
         tmem_ld32(tS, reinterpret_cast<uint32_t*>(sv));
-        tmem_ld32(tDP, reinterpret_cast<uint32_t*>(dp));
         tmem_ld32(tS + 32, reinterpret_cast<uint32_t*>(sv + 16));
+        tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(bar(B_SREAD));  // S(j) is in registers: the tensor core may write S(j+1)
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+          if (j >= n_unmasked)
+            p_cols_by_key<true>(sv + 16 * g, nm, c2, nl, lim - 32 * g, pr + 16 * g);
+          else
+            p_cols_by_key<false>(sv + 16 * g, nm, c2, nl, 32, pr + 16 * g);
+        }
+      }
+      ok = mbar_wait_warp(bar(B_DP), j & 1, ctl, 8);
+      if (!ok) break;
+      tc_fence_after();
+      {
+        float2 dp[32];
+        tmem_ld32(tDP, reinterpret_cast<uint32_t*>(dp));
         tmem_ld32(tDP + 32, reinterpret_cast<uint32_t*>(dp + 16));
         tmem_wait_ld();
 #pragma unroll
         for (int g = 0; g < 2; ++g) {
           uint32_t dk[16];
-          if (j >= n_unmasked)
-            ds_cols_by_key<BF16, true>(sv + 16 * g, dp + 16 * g, nm, c2, nl, nd, lim - 32 * g, dk);
-          else
-            ds_cols_by_key<BF16, false>(sv + 16 * g, dp + 16 * g, nm, c2, nl, nd, 32, dk);
-          tmem_st16(tDP + 16 * g, dk);
+          ds_cols_by_key<BF16>(dp + 16 * g, pr + 16 * g, nd, dk);
+          tmem_st16(tDP + 16 * g, dk);  // 16-bit dS over dP columns this thread has already read
         }
       }
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(bar(B_DS + hk));
+      mbar_arrive(bar(B_DS));
     }
-    ok = mbar_wait_warp(bar(B_ACC), 0, ctl, 27) && ok;
+    ok = mbar_wait_warp(bar(B_ACC), 0, ctl, 9) && ok;
     if (ok) {
       tc_fence_after();
-      uint8_t* grow = reinterpret_cast<uint8_t*>(p.dq) +
-                      2 * (b * p.dq_sb + h * p.dq_sh + static_cast<long long>(row) * p.dq_ss);
-      store_acc_row<BF16>(tmem + Cfg::TM_ACC0 + lane_base, hk * (D / 2), D / 2, p.scale, grow, row < p.Sq);
+      if (p.acc_mode == 0) {
+        uint8_t* grow = reinterpret_cast<uint8_t*>(p.dq) +
+                        2 * (b * p.dq_sb + h * p.dq_sh + static_cast<long long>(row) * p.dq_ss);
+        store_acc_row<BF16>(tmem + Cfg::TM_ACC0 + lane_base, hk * (D / 2), D / 2, p.scale, grow, row < p.Sq);
+      } else {
+        float* grow32 = p.dq32 + (static_cast<long long>(b) * p.H + h) * p.dq32_sh + static_cast<long long>(row) * D;
+        store_acc_row_f32(tmem + Cfg::TM_ACC0 + lane_base, hk * (D / 2), D / 2, p.scale, grow32, row < p.Sq,
+                          p.acc_mode == 2);
+      }
     }
   }
 

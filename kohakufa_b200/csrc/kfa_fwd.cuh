@@ -35,6 +35,13 @@ struct FwdParams {
   float c;  // scale * log2(e)
   int n_q_tiles;
   int* status;
+  // Context-parallel steps (mode != 0): instead of the normalised 16-bit O and (m, log2 l), the
+  // kernel leaves the unnormalised fp32 O and (m, l) in a carry that the next step merges with.
+  int mode;            // 0 normal; 1 write the carry; 2 merge with the existing carry and write it
+  float* o_acc;        // fp32 rows of D, row r of (b, h) at o_acc + (b * H + h) * oa_sh + r * D
+  long long oa_sh;
+  float* ml;           // m at ml[(b * H + h) * ml_sh + r], l at the same + ml_plane
+  long long ml_sh, ml_plane;
 };
 
 constexpr int FWD_THREADS = 320;
@@ -401,7 +408,49 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     }
     // ---- epilogue ----
     if (nt > 0) ok = mbar_wait_warp(bar(B_OFINAL + hf), 0, ctl, 6) && ok;
-    if (ok && nt > 0) {
+    if (ok && nt > 0 && p.mode != 0) {
+      // Partial result of a context-parallel step: the unnormalised fp32 O with its (m, l) goes to
+      // (mode 1), or is merged into (mode 2), the carry in global memory. Merging keeps the two
+      // statistics apart and shifts both sides to the common row max before anything is rounded.
+      tc_fence_after();
+      const bool valid = row < p.Sq;
+      const long long bhl = static_cast<long long>(b) * p.H + h;
+      float* mlp = p.ml + bhl * p.ml_sh + row;
+      float* arow = p.o_acc + bhl * p.oa_sh + static_cast<long long>(row) * D;
+      float a_new = 1.0f, a_old = 0.0f;
+      if (p.mode == 2 && valid) {
+        const float m_old = mlp[0], l_old = mlp[p.ml_plane];
+        const float m_tot = fmaxf(m, m_old);
+        a_new = ex2(__fmul_rn(__fsub_rn(m, m_tot), c));
+        a_old = ex2(__fmul_rn(__fsub_rn(m_old, m_tot), c));
+        l = l * a_new + l_old * a_old;
+        m = m_tot;
+      }
+#pragma unroll
+      for (int cc = 0; cc < D; cc += 32) {
+        float o[32];
+        tmem_ld32(tO + cc, reinterpret_cast<uint32_t*>(o));
+        tmem_wait_ld();
+        if (valid) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            float4 w = make_float4(o[i] * a_new, o[i + 1] * a_new, o[i + 2] * a_new, o[i + 3] * a_new);
+            if (p.mode == 2) {
+              const float4 old = *reinterpret_cast<const float4*>(arow + cc + i);
+              w.x = fmaf(old.x, a_old, w.x);
+              w.y = fmaf(old.y, a_old, w.y);
+              w.z = fmaf(old.z, a_old, w.z);
+              w.w = fmaf(old.w, a_old, w.w);
+            }
+            *reinterpret_cast<float4*>(arow + cc + i) = w;
+          }
+        }
+      }
+      if (valid) {
+        mlp[0] = m;
+        mlp[p.ml_plane] = l;
+      }
+    } else if (ok && nt > 0) {
       tc_fence_after();
       const float inv = 1.0f / l;
       const bool valid = row < p.Sq;
