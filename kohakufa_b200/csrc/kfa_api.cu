@@ -96,8 +96,9 @@ int check_qkv(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, int
   for (int i = 0; i < 4; ++i)
     if (k->shape[i] != v->shape[i]) return fail(KFA_ERR_ARG, "k and v shapes differ");
   if (k->shape[0] != q->shape[0] || k->shape[3] != D) return fail(KFA_ERR_ARG, "k / v batch or head_dim differ from q");
-  if (k->shape[1] != q->shape[1]) return fail(KFA_ERR_ARG, "q heads %lld != k / v heads %lld (grouped-query attention is not built)",
-                                               (long long)q->shape[1], (long long)k->shape[1]);
+  if (q->shape[1] % k->shape[1])
+    return fail(KFA_ERR_ARG, "q heads %lld must be a multiple of k / v heads %lld", (long long)q->shape[1],
+                (long long)k->shape[1]);
   if (block < 0) return fail(KFA_ERR_ARG, "block %d < 0", block);
   return KFA_OK;
 }
@@ -145,7 +146,7 @@ int launch_dkdv(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap&
   auto kern = kfa::kfa_bwd_dkdv_kernel<D, BF16>;
   int rc = set_smem(kern, kfa::BwdCfg<D>::KV_SMEM_BYTES);
   if (rc) return rc;
-  const long long grid = static_cast<long long>(p.B) * p.H * p.n_k128;
+  const long long grid = static_cast<long long>(p.B) * p.Hkv * p.n_k128;
   if (grid > 0x7fffffffll) return fail(KFA_ERR_ARG, "too many tiles");
   kern<<<static_cast<unsigned>(grid), kfa::BWD_THREADS, kfa::BwdCfg<D>::KV_SMEM_BYTES, s>>>(mq, mk, mv, mdo, p);
   KFA_CUDA(cudaGetLastError());
@@ -192,6 +193,8 @@ void fill_bwd_params(kfa::BwdParams& p, const KfaTensor4* q, const KfaTensor4* k
   p.stats = stats;
   p.B = static_cast<int>(q->shape[0]);
   p.H = static_cast<int>(q->shape[1]);
+  p.Hkv = static_cast<int>(k->shape[1]);
+  p.group = p.H / p.Hkv;
   p.Sq = static_cast<int>(q->shape[2]);
   p.Skv = static_cast<int>(k->shape[2]);
   p.P = block;
@@ -238,6 +241,7 @@ int kfa_fwd(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const
   p.c = scale * LOG2E;
   p.n_q_tiles = (p.Sq + 255) / 256;
   p.status = dev_status;
+  p.group = static_cast<int>(q->shape[1] / k->shape[1]);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   KFA_DISPATCH(q->shape[3], dtype, (launch_fwd<KD, KB>(mq, mk, mv, p, s)));
 }

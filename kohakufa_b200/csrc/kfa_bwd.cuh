@@ -47,6 +47,7 @@ struct BwdParams {
   long long dv_sb, dv_sh, dv_ss;
   const float* stats;  // [B*H, n_q128, 3, 128]: -m, -log2 l, -delta
   int B, H, Sq, Skv;
+  int Hkv, group;  // K / V heads; query heads per K / V head (H = Hkv * group)
   int P;
   float c;      // scale * log2(e)
   float scale;  // applied to fp32 dK and dQ
@@ -316,12 +317,14 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   // tile decode: head-major; when causal the first key tiles see the most queries and come first
-  const int bh = blockIdx.x / p.n_k128;
+  const int bh = blockIdx.x / p.n_k128;  // over batch x K / V heads
   const int kt = blockIdx.x % p.n_k128;
-  const int b = bh / p.H, h = bh % p.H;
+  const int b = bh / p.Hkv, hk = bh % p.Hkv;
   const int kv0 = kt * 128;
   const int first_i = (p.P > 0) ? static_cast<int>((static_cast<long long>(kv0 / p.P) * p.P) / 128) : 0;
-  const int n_steps = max(p.n_q128 - first_i, 0);
+  // steps: for every query head of this K / V head's group, the query tiles that see these keys
+  const int n_per = max(p.n_q128 - first_i, 0);
+  const int n_steps = n_per * p.group;
   const bool ragged_keys = kv0 + 128 > p.Skv;
 
   if (tid == 0) {
@@ -368,8 +371,8 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       prefetch_tensormap(&tmDO);
       mbar_expect_tx(bar(B_KV), 2 * Cfg::TILE_BYTES);
       for (int ch = 0; ch < CH; ++ch) {
-        tma_load_4d(sK + ch * TILE_BYTES_64, &tmK, bar(B_KV), ch * 64, kv0, h, b);
-        tma_load_4d(sV + ch * TILE_BYTES_64, &tmV, bar(B_KV), ch * 64, kv0, h, b);
+        tma_load_4d(sK + ch * TILE_BYTES_64, &tmK, bar(B_KV), ch * 64, kv0, hk, b);
+        tma_load_4d(sV + ch * TILE_BYTES_64, &tmV, bar(B_KV), ch * 64, kv0, hk, b);
       }
       bool ok = true;
       int issued = 0;
@@ -377,15 +380,17 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const int slot = s % NSL, use = s / NSL;
         if (use > 0) ok = mbar_wait(bar(B_QFREE + slot), (use - 1) & 1, ctl, 1);
         if (!ok) break;
-        const int i = first_i + s;
+        const int i = first_i + s % n_per;
+        const int head = hk * p.group + s / n_per;
         const uint32_t base = sSlot + slot * Cfg::KV_SLOT_BYTES;
         mbar_expect_tx(bar(B_QREADY + slot), 2 * Cfg::TILE_BYTES + STATS_BYTES);
         for (int ch = 0; ch < CH; ++ch) {
-          tma_load_4d(base + ch * TILE_BYTES_64, &tmQ, bar(B_QREADY + slot), ch * 64, i * 128, h, b);
+          tma_load_4d(base + ch * TILE_BYTES_64, &tmQ, bar(B_QREADY + slot), ch * 64, i * 128, head, b);
           tma_load_4d(base + Cfg::TILE_BYTES + ch * TILE_BYTES_64, &tmDO, bar(B_QREADY + slot), ch * 64,
-                      i * 128, h, b);
+                      i * 128, head, b);
         }
-        bulk_load(base + 2 * Cfg::TILE_BYTES, p.stats + static_cast<long long>(bh) * p.stats_sh + i * 384ll,
+        bulk_load(base + 2 * Cfg::TILE_BYTES,
+                  p.stats + (static_cast<long long>(b) * p.H + head) * p.stats_sh + i * 384ll,
                   STATS_BYTES, bar(B_QREADY + slot));
         issued = s + 1;
       }
@@ -469,7 +474,7 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     bool ok = true;
     for (int s = 0; s < n_steps; ++s) {
       const int slot = s % NSL;
-      const int i = first_i + s;
+      const int i = first_i + s % n_per;
       const int q0 = i * 128 + 64 * hq;  // query of this warpgroup's column 0
       // masked step: some (key, query) pair of this tile pair is hidden, or keys are padded
       const bool masked = ragged_keys || (p.P > 0 && key_limit(i * 128, p.P, p.Skv) < kv0 + 128);
@@ -522,13 +527,13 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const bool valid = key < p.Skv;
     uint8_t* grow;
     if (hq == 0)
-      grow = reinterpret_cast<uint8_t*>(p.dv) + 2 * (b * p.dv_sb + h * p.dv_sh + static_cast<long long>(key) * p.dv_ss);
+      grow = reinterpret_cast<uint8_t*>(p.dv) + 2 * (b * p.dv_sb + hk * p.dv_sh + static_cast<long long>(key) * p.dv_ss);
     else
-      grow = reinterpret_cast<uint8_t*>(p.dk) + 2 * (b * p.dk_sb + h * p.dk_sh + static_cast<long long>(key) * p.dk_ss);
+      grow = reinterpret_cast<uint8_t*>(p.dk) + 2 * (b * p.dk_sb + hk * p.dk_sh + static_cast<long long>(key) * p.dk_ss);
     float* grow32 = nullptr;
     if (p.acc_mode != 0)
-      grow32 = (hq == 0 ? p.dv32 + (static_cast<long long>(b) * p.H + h) * p.dv32_sh
-                        : p.dk32 + (static_cast<long long>(b) * p.H + h) * p.dk32_sh) +
+      grow32 = (hq == 0 ? p.dv32 + (static_cast<long long>(b) * p.Hkv + hk) * p.dv32_sh
+                        : p.dk32 + (static_cast<long long>(b) * p.Hkv + hk) * p.dk32_sh) +
                static_cast<long long>(key) * D;
     if (n_steps == 0) {
       if (valid && p.acc_mode == 0)
@@ -662,9 +667,9 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         const uint32_t base = sSlot + slot * Cfg::Q_SLOT_BYTES;
         mbar_expect_tx(bar(B_KVREADY + slot), 2 * Cfg::TILE_BYTES);
         for (int ch = 0; ch < CH; ++ch) {
-          tma_load_4d(base + ch * TILE_BYTES_64, &tmK, bar(B_KVREADY + slot), ch * 64, j * 128, h, b);
+          tma_load_4d(base + ch * TILE_BYTES_64, &tmK, bar(B_KVREADY + slot), ch * 64, j * 128, h / p.group, b);
           tma_load_4d(base + Cfg::TILE_BYTES + ch * TILE_BYTES_64, &tmV, bar(B_KVREADY + slot), ch * 64,
-                      j * 128, h, b);
+                      j * 128, h / p.group, b);
         }
         issued = j + 1;
       }

@@ -93,6 +93,7 @@ int kfa_cp_fwd_step(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* 
   p.c = scale * LOG2E;
   p.n_q_tiles = (p.Sq + 255) / 256;
   p.status = dev_status;
+  p.group = static_cast<int>(q->shape[1] / k->shape[1]);
   p.mode = merge ? 2 : 1;
   p.o_acc = o_acc->ptr;
   p.oa_sh = o_acc->head_stride;

@@ -35,6 +35,7 @@ struct FwdParams {
   float c;  // scale * log2(e)
   int n_q_tiles;
   int* status;
+  int group;  // query heads per K / V head (grouped-query attention): K / V head of query head h is h / group
   // Context-parallel steps (mode != 0): instead of the normalised 16-bit O and (m, log2 l), the
   // kernel leaves the unnormalised fp32 O and (m, l) in a carry that the next step merges with.
   int mode;            // 0 normal; 1 write the carry; 2 merge with the existing carry and write it
@@ -188,7 +189,7 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const CUtensorMap* map = (idx & 1) ? &tmV : &tmK;
         for (int ch = 0; ch < CH; ++ch)
           tma_load_4d(sKV + (stage * CH + ch) * TILE_BYTES_64, map, bar(B_KVREADY + stage), ch * 64,
-                      j * 128, h, b);
+                      j * 128, h / p.group, b);
         armed[stage] = use;
       }
       if (!ok) {

@@ -49,8 +49,6 @@ def _check(q: Tensor, k: Tensor, v: Tensor) -> None:
         raise ValueError(f"attention: k {tuple(k.shape)} / v {tuple(v.shape)} vs q {tuple(q.shape)}")
     if q.shape[1] % k.shape[1]:
         raise ValueError("attention: query heads must be a multiple of K / V heads (GQA)")
-    if q.shape[1] != k.shape[1]:
-        raise NotImplementedError("attention: grouped-query attention (H != Hkv) is not built yet")
     if not q.is_cuda:
         raise ValueError("attention: CUDA tensors only (there is no CPU path)")
     for t in (q, k, v):

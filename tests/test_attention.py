@@ -155,6 +155,27 @@ def test_head_dims(dim, causal):
     check(run(q, k, v, dout, causal=causal), want_for(q, k, v, dout, block=int(causal)))
 
 
+@pytest.mark.parametrize("heads,kv_heads,mode", [(4, 2, {"causal": True}), (6, 1, {}), (8, 2, {"block_causal": 100})])
+@pytest.mark.parametrize("dim,dtype,tol", [(64, torch.float16, TOL), (128, torch.bfloat16, BF16_TOL)])
+def test_gqa(heads, kv_heads, mode, dim, dtype, tol):
+    """Grouped-query / multi-query attention: query head h uses K / V head h // (H / Hkv); dK / dV sum
+    over the group (reference test: tests/test_attention.py:189-211)."""
+    gen = torch.Generator().manual_seed(heads)
+    sq, skv = 300, 389
+    q = torch.randn(2, sq, heads, dim, generator=gen).to(dtype).cuda().transpose(1, 2).requires_grad_()
+    k = torch.randn(2, skv, kv_heads, dim, generator=gen).to(dtype).cuda().transpose(1, 2).requires_grad_()
+    v = torch.randn(2, skv, kv_heads, dim, generator=gen).to(dtype).cuda().transpose(1, 2).requires_grad_()
+    dout = torch.randn(2, heads, sq, dim, generator=gen).to(dtype).cuda()
+    got = run(q, k, v, dout, **mode)
+    block = 1 if mode.get("causal") else mode.get("block_causal", 0)
+    group = heads // kv_heads
+    kk, vv = (t.detach().repeat_interleave(group, dim=1) for t in (k, v))
+    out, dq, dkk, dvv = oracle.attention_fp64(q, kk, vv, dout, dim**-0.5, block=block)
+    dk = dkk.reshape(2, kv_heads, group, skv, dim).sum(2)
+    dv = dvv.reshape(2, kv_heads, group, skv, dim).sum(2)
+    check(got, (out, dq, dk, dv), tol=tol)
+
+
 def test_config1_dense():
     cfg = workloads.CONFIGS["C1"]
     q, k, v, dout = (t.cuda() for t in workloads.make_inputs(cfg))

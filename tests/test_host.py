@@ -88,8 +88,6 @@ def test_check_rules():
         op._check(q, k, v[:, :, :8])
     with pytest.raises(ValueError, match="multiple of K / V heads"):
         op._check(torch.zeros(1, 3, 16, 64, dtype=torch.float16), k, v)
-    with pytest.raises(NotImplementedError):
-        op._check(torch.zeros(1, 4, 16, 64, dtype=torch.float16), k, v)
     with pytest.raises(ValueError, match="CUDA tensors only"):
         op._check(q, k, v)
     with pytest.raises(ValueError, match="head_dim"):
