@@ -90,8 +90,14 @@ __device__ __forceinline__ void kfa_prof_flush(const long long* acc, int role) {
 // Debug-build section timers (compile to nothing otherwise): cycles between BEGIN and END are added
 // to counter `slot` of the calling thread.
 #ifdef KFA_PROFILE
-#define KFA_PROF_BEGIN() kfa_prof_tb = clock64()
-#define KFA_PROF_END(slot) prof_acc[slot] += clock64() - kfa_prof_tb
+// A time stamp the compiler cannot move across other volatile statements (clock64() may be).
+__device__ __forceinline__ long long kfa_clock() {
+  long long t;
+  asm volatile("mov.u64 %0, %%clock64;" : "=l"(t)::"memory");
+  return t;
+}
+#define KFA_PROF_BEGIN() kfa_prof_tb = kfa_clock()
+#define KFA_PROF_END(slot) prof_acc[slot] += kfa_clock() - kfa_prof_tb
 #else
 #define KFA_PROF_BEGIN() do { } while (0)
 #define KFA_PROF_END(slot) do { } while (0)
@@ -102,9 +108,9 @@ __device__ __forceinline__ void kfa_prof_flush(const long long* acc, int role) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const Ctl& ctl, int site) {
 #ifdef KFA_PROFILE
   {  // try_wait may block inside the hardware for a while: time the first attempt too
-    const long long tp = clock64();
+    const long long tp = kfa_clock();
     const bool hit = mbar_try_wait(bar, parity);
-    ctl.acc[site % 10] += clock64() - tp;
+    ctl.acc[site % 10] += kfa_clock() - tp;
     if (hit) return true;
   }
 #else
@@ -115,7 +121,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const C
   for (;;) {
     if (mbar_try_wait(bar, parity)) {
 #ifdef KFA_PROFILE
-      ctl.acc[site % 10] += clock64() - t0;
+      ctl.acc[site % 10] += kfa_clock() - t0;
 #endif
       return true;
     }
@@ -139,9 +145,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const C
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, const Ctl& ctl, int site) {
   const bool ok = mbar_wait(bar, parity, ctl, site);
 #ifdef KFA_PROFILE
-  const long long tp = clock64();
+  const long long tp = kfa_clock();
   const bool all = __all_sync(0xffffffffu, ok);
-  ctl.acc[2] += clock64() - tp;  // (slot 2 doubles as "time to reconverge" in debug builds)
+  ctl.acc[2] += kfa_clock() - tp;  // (slot 2 doubles as "time to reconverge" in debug builds)
   return all;
 #else
   return __all_sync(0xffffffffu, ok);
