@@ -404,17 +404,29 @@ def end_to_end(cfg, host, dev, attention, world, flops, steps, barrier, reduce_m
     """The same metric through ``kohakufa_b200.attention`` with HOST buffers: every step copies q, k,
     v, dout from pinned host memory, runs forward + backward, and copies out, dq, dk, dv back."""
     hq, hk, hv, hdo = host
-    outs = [torch.empty_like(hq).pin_memory() for _ in range(4)]
+    if reduce_max:  # ring mode: one sequence over all ranks, no batch to pipeline over
+        outs = [torch.empty_like(hq).pin_memory() for _ in range(4)]
 
-    def step():
-        q, k, v, dout = (t.to(dev, non_blocking=True).transpose(1, 2) for t in (hq, hk, hv, hdo))
-        q, k, v = (t.requires_grad_() for t in (q, k, v))
-        out = attention(q, k, v, causal=(cfg.block == 1), block_causal=0 if cfg.block == 1 else cfg.block)
-        dq, dk, dv = torch.autograd.grad(out, (q, k, v), dout)
-        for dst, src in zip(outs, (out, dq, dk, dv)):
-            dst.copy_(src.transpose(1, 2), non_blocking=True)
+        def step():
+            q, k, v, dout = (t.to(dev, non_blocking=True).transpose(1, 2) for t in (hq, hk, hv, hdo))
+            q, k, v = (t.requires_grad_() for t in (q, k, v))
+            out = attention(q, k, v, causal=(cfg.block == 1), block_causal=0 if cfg.block == 1 else cfg.block)
+            dq, dk, dv = torch.autograd.grad(out, (q, k, v), dout)
+            for dst, src in zip(outs, (out, dq, dk, dv)):
+                dst.copy_(src.transpose(1, 2), non_blocking=True)
 
-    step()
+    else:  # the host-buffer entry point: batch slices pipelined over copy-in / compute / copy-out streams
+        from kohakufa_b200 import hostio
+
+        views = [t.transpose(1, 2) for t in (hq, hk, hv, hdo)]
+        pipe = hostio.HostPipeline(*views[:3], dev)
+
+        def step():
+            hostio.attention_fwd_bwd_host(*views, causal=(cfg.block == 1), block_causal=0 if cfg.block == 1 else cfg.block,
+                                          scale=cfg.scale, pipeline=pipe)
+
+    for _ in range(3):
+        step()
     barrier()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
