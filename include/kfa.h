@@ -83,6 +83,27 @@ int kfa_bwd(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const
             const KfaTensor4* dk, const KfaTensor4* dv, float scale, int block, int dtype,
             int* dev_status, void* stream);
 
+/* Packed variable-length batches. Replace attention_forward_varlen (fwd.py:1277-1320) and
+ * attention_backward_varlen (bwd.py:1591-1647); the reference's host-built tile tables (fwd.py:1265-1274,
+ * bwd.py:1559-1588) are not needed: the kernels read the sequence boundaries themselves.
+ *
+ * q / out / dout / dq are [1, H, Tq, D] views and k / v / dk / dv [1, Hkv, Tk, D] views of the packed
+ * [T, H, D] tensors; sequence b (0 <= b < n_seqs) owns query rows cu_seqlens_q[b] .. cu_seqlens_q[b + 1]
+ * and key rows cu_seqlens_k[b] .. cu_seqlens_k[b + 1] (int32[n_seqs + 1] in DEVICE memory, ascending,
+ * first entry 0) and is its own attention problem: `block` applies inside each sequence. max_q / max_k:
+ * the longest sequence's queries / keys (host ints: they size the grids, so no call reads device
+ * memory on the host). lse is [1, H, 2, Tq]. `stats`: kfa_bwd_stats_bytes(n_seqs, H, max_q) bytes.
+ * A sequence with queries but no keys is skipped (its output rows are left unwritten); rows of
+ * neighbouring sequences that share a tile are read and masked, so they must hold finite numbers. */
+int kfa_fwd_varlen(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* out,
+                   float* lse, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, int n_seqs,
+                   int max_q, int max_k, float scale, int block, int dtype, int* dev_status, void* stream);
+int kfa_bwd_varlen(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* out,
+                   const KfaTensor4* dout, const float* lse, float* stats, const KfaTensor4* dq,
+                   const KfaTensor4* dk, const KfaTensor4* dv, const int32_t* cu_seqlens_q,
+                   const int32_t* cu_seqlens_k, int n_seqs, int max_q, int max_k, float scale, int block,
+                   int dtype, int* dev_status, void* stream);
+
 /* Backward without a scratch buffer from the caller. No counterpart in the reference (there the
  * launcher allocates its scratch from torch's caching allocator, bwd.py:1434-1439).
  *

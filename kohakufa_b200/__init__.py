@@ -4,11 +4,13 @@
     from kohakufa_b200 import attention
     out = attention(q, k, v, causal=True)  # q [B, H, Sq, D], k / v [B, H, Skv, D]
 
-``attention_varlen``, ``varlen_plan``, ``pack_mask`` and ``PackedMask`` (the reference's other
-exports, ``src/kohakufa/__init__.py:12``) are not built: they raise ``NotImplementedError``.
+    out = attention_varlen(q, k, v, cu_seqlens, cu_seqlens, causal=True)  # packed [T, H, D]
+
+``pack_mask`` and ``PackedMask`` (the reference's other exports, ``src/kohakufa/__init__.py:12``)
+are not built: they raise ``NotImplementedError``.
 """
 
-from kohakufa_b200.api import attention
+from kohakufa_b200.api import attention, attention_varlen, varlen_plan
 
 
 def _not_built(name):
@@ -19,8 +21,6 @@ def _not_built(name):
     return stub
 
 
-attention_varlen = _not_built("attention_varlen")
-varlen_plan = _not_built("varlen_plan")
 pack_mask = _not_built("pack_mask")
 
 

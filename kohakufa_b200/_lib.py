@@ -26,6 +26,8 @@ SYMBOLS = (
     "kfa_bwd_dq",
     "kfa_bwd",
     "kfa_bwd_static_scratch",
+    "kfa_fwd_varlen",
+    "kfa_bwd_varlen",
     "kfa_cp_fwd_step",
     "kfa_cp_fwd_finalize",
     "kfa_cp_bwd_dkdv_step",
@@ -93,6 +95,8 @@ def load() -> ctypes.CDLL:
         lib.kfa_bwd_static_scratch.argtypes = [T, T, T, T, T, fp, T, T, T, ctypes.c_float, ctypes.c_int, ctypes.c_int, ip, vp]
         A = ctypes.POINTER(KfaAcc32)
         i64, f32, i32 = ctypes.c_int64, ctypes.c_float, ctypes.c_int
+        lib.kfa_fwd_varlen.argtypes = [T, T, T, T, fp, ip, ip, i32, i32, i32, f32, i32, i32, ip, vp]
+        lib.kfa_bwd_varlen.argtypes = [T, T, T, T, T, fp, fp, T, T, T, ip, ip, i32, i32, i32, f32, i32, i32, ip, vp]
         lib.kfa_cp_fwd_step.argtypes = [T, T, T, A, fp, i64, i64, i32, f32, i32, i32, ip, vp]
         lib.kfa_cp_fwd_finalize.argtypes = [A, fp, i64, i64, T, fp, i32, vp]
         lib.kfa_cp_bwd_dkdv_step.argtypes = [T, T, T, T, fp, i64, A, A, i32, f32, i32, i32, ip, vp]

@@ -9,6 +9,8 @@ from torch import Tensor
 
 from kohakufa_b200.op import KERNEL_DIMS, MAX_KERNEL_DIM
 from kohakufa_b200.op import attention as _sm100_attention
+from kohakufa_b200.op import attention_varlen as _sm100_attention_varlen
+from kohakufa_b200.op import varlen_plan  # noqa: F401 (re-exported)
 
 COMPUTE_DTYPES = (torch.float16, torch.bfloat16)
 MAX_HEAD_DIM = MAX_KERNEL_DIM
@@ -38,6 +40,17 @@ def _center_keys(k: Tensor, dtype: torch.dtype) -> Tensor:
     Exact: every logit of a query row moves by the same amount, which the softmax drops, and dK
     picks up ``- mean(dK')`` through autograd."""
     return _centered(k, k.float().mean(-2, keepdim=True), dtype)
+
+
+def _center_keys_varlen(k: Tensor, cu_seqlens_k: Tensor) -> Tensor:
+    """``_center_keys`` per packed sequence (``k [Tk, Hkv, D]``), without host syncs (reference
+    api.py:46-53): the fp32 mean of each sequence's keys is subtracted from them."""
+    rows = torch.arange(k.shape[0], device=k.device)
+    seq = torch.searchsorted(cu_seqlens_k[1:].contiguous(), rows, right=True)
+    k32 = k.float()
+    sums = k32.new_zeros(cu_seqlens_k.numel() - 1, *k.shape[1:]).index_add_(0, seq, k32)
+    counts = (cu_seqlens_k[1:] - cu_seqlens_k[:-1]).clamp(min=1).float()
+    return _centered(k, (sums / counts[:, None, None])[seq], k.dtype)
 
 
 def attention(
@@ -88,3 +101,36 @@ def attention(
         raise ValueError("give a mask or causal / block_causal, not both (fold them in)")
     out = _sm100_attention(q, k, v, scale, block, mask)[..., :dim]
     return out if out.dtype == in_dtype else out.to(in_dtype)
+
+
+def attention_varlen(
+    q: Tensor,
+    k: Tensor,
+    v: Tensor,
+    cu_seqlens_q: Tensor,
+    cu_seqlens_k: Tensor,
+    *,
+    causal: bool = False,
+    block_causal: int = 0,
+    scale: float | None = None,
+    plan: tuple | None = None,
+    center_keys: bool = False,
+) -> Tensor:
+    """Variable-length attention over packed sequences, each its own problem (no padding computed):
+    ``q [Tq, H, D]``, ``k / v [Tk, Hkv, D]`` (fp16 / bf16), sequence ``b`` at rows
+    ``cu_seqlens[b] : cu_seqlens[b + 1]`` (int32 [B + 1]). ``causal`` / ``block_causal`` apply within
+    each sequence. ``plan``: ``varlen_plan(cu_seqlens_q, cu_seqlens_k, H, Hkv, block)``, built once per
+    batch of lengths (it reads the lengths on the host), e.g. to keep the call free of host syncs
+    inside a CUDA graph. ``center_keys``: as in ``attention``, with the mean taken per sequence.
+    Same signature and exceptions as the reference's (api.py:114-146)."""
+    if causal and block_causal not in (0, 1):
+        raise ValueError("causal is block_causal=1: give one of them")
+    block = 1 if causal else int(block_causal)
+    dim = q.shape[-1]
+    if scale is None:
+        scale = dim**-0.5
+    if center_keys:
+        k = _center_keys_varlen(k, cu_seqlens_k)
+    q, k, v = _pad_head_dim(q, k, v)
+    out = _sm100_attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, scale=scale, block_causal=block, plan=plan)
+    return out[..., :dim]

@@ -187,6 +187,23 @@ int launch_dq(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& m
     }                                                      \
   } while (0)
 
+// A packed variable-length batch: n_seqs sequences inside [1, H, T, D] tensors.
+struct Varlen {
+  const int32_t* cu_q;
+  const int32_t* cu_k;
+  int n_seqs, max_q, max_k;
+};
+
+int check_varlen(const Varlen* vl, const KfaTensor4* q, const KfaTensor4* k) {
+  if (!vl) return KFA_OK;
+  if (!vl->cu_q || !vl->cu_k) return fail(KFA_ERR_ARG, "cu_seqlens: null pointer");
+  if (q->shape[0] != 1 || k->shape[0] != 1) return fail(KFA_ERR_ARG, "packed batches are [1, H, T, D] tensors");
+  if (vl->n_seqs < 1 || vl->max_q < 1 || vl->max_k < 1 || vl->max_q > q->shape[2] || vl->max_k > k->shape[2])
+    return fail(KFA_ERR_ARG, "packed batch: n_seqs %d, longest sequence %d queries / %d keys, tensors hold %lld / %lld rows",
+                vl->n_seqs, vl->max_q, vl->max_k, (long long)q->shape[2], (long long)k->shape[2]);
+  return KFA_OK;
+}
+
 void fill_bwd_params(kfa::BwdParams& p, const KfaTensor4* q, const KfaTensor4* k, const float* stats, float scale,
                      int block, int* dev_status) {
   std::memset(&p, 0, sizeof(p));
@@ -206,22 +223,21 @@ void fill_bwd_params(kfa::BwdParams& p, const KfaTensor4* q, const KfaTensor4* k
   p.stats_sh = static_cast<long long>(p.n_q128) * 384;
 }
 
-}  // namespace
-
-extern "C" {
-
-int kfa_abi_version(void) { return KFA_ABI_VERSION; }
-
-const char* kfa_last_error(void) { return g_err; }
-
-int64_t kfa_bwd_stats_bytes(int64_t B, int64_t H, int64_t Sq) {
-  return B * H * ((Sq + 127) / 128) * 3 * 128 * 4;
+void apply_varlen(kfa::BwdParams& p, const Varlen* vl) {
+  if (!vl) return;
+  p.B = vl->n_seqs;
+  p.n_q128 = (vl->max_q + 127) / 128;
+  p.n_k128 = (vl->max_k + 127) / 128;
+  p.stats_sh = static_cast<long long>(p.n_q128) * 384;
+  p.cu_q = vl->cu_q;
+  p.cu_k = vl->cu_k;
 }
 
-int kfa_fwd(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* out, float* lse,
-            float scale, int block, int dtype, int* dev_status, void* stream) {
+int fwd_impl(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* out, float* lse,
+             const Varlen* vl, float scale, int block, int dtype, int* dev_status, void* stream) {
   int rc;
-  if ((rc = check_qkv(q, k, v, dtype, block)) || (rc = check_like(out, q, "out"))) return rc;
+  if ((rc = check_qkv(q, k, v, dtype, block)) || (rc = check_like(out, q, "out")) || (rc = check_varlen(vl, q, k)))
+    return rc;
   if (!lse || !dev_status) return fail(KFA_ERR_ARG, "lse / dev_status: null pointer");
   CUtensorMap mq, mk, mv;
   if ((rc = make_map(q, dtype, &mq, "q")) || (rc = make_map(k, dtype, &mk, "k")) || (rc = make_map(v, dtype, &mv, "v")))
@@ -242,12 +258,18 @@ int kfa_fwd(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const
   p.n_q_tiles = (p.Sq + 255) / 256;
   p.status = dev_status;
   p.group = static_cast<int>(q->shape[1] / k->shape[1]);
+  if (vl) {
+    p.B = vl->n_seqs;
+    p.n_q_tiles = (vl->max_q + 255) / 256;
+    p.cu_q = vl->cu_q;
+    p.cu_k = vl->cu_k;
+  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   KFA_DISPATCH(q->shape[3], dtype, (launch_fwd<KD, KB>(mq, mk, mv, p, s)));
 }
 
-int kfa_bwd_prepare(const KfaTensor4* out, const KfaTensor4* dout, const float* lse, float* stats, int dtype,
-                    void* stream) {
+int prepare_impl(const KfaTensor4* out, const KfaTensor4* dout, const float* lse, float* stats, const Varlen* vl,
+                 int dtype, void* stream) {
   int rc;
   if ((rc = check_tensor(out, "out")) || (rc = check_like(dout, out, "dout"))) return rc;
   if (!lse || !stats) return fail(KFA_ERR_ARG, "lse / stats: null pointer");
@@ -270,17 +292,22 @@ int kfa_bwd_prepare(const KfaTensor4* out, const KfaTensor4* dout, const float* 
   p.H = static_cast<int>(out->shape[1]);
   p.Sq = static_cast<int>(out->shape[2]);
   p.n_q128 = (p.Sq + 127) / 128;
+  if (vl) {
+    p.B = vl->n_seqs;
+    p.n_q128 = (vl->max_q + 127) / 128;
+    p.cu_q = vl->cu_q;
+  }
   if (static_cast<long long>(p.B) * p.H > 65535) return fail(KFA_ERR_ARG, "B * H > 65535");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   KFA_DISPATCH(D, dtype, (launch_prepare<KD, KB>(p, s)));
 }
 
-int kfa_bwd_dkdv(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* dout,
-                 const float* stats, const KfaTensor4* dk, const KfaTensor4* dv, float scale, int block, int dtype,
-                 int* dev_status, void* stream) {
+int dkdv_impl(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* dout,
+              const float* stats, const KfaTensor4* dk, const KfaTensor4* dv, const Varlen* vl, float scale, int block,
+              int dtype, int* dev_status, void* stream) {
   int rc;
   if ((rc = check_qkv(q, k, v, dtype, block)) || (rc = check_like(dout, q, "dout")) ||
-      (rc = check_like(dk, k, "dk")) || (rc = check_like(dv, v, "dv")))
+      (rc = check_like(dk, k, "dk")) || (rc = check_like(dv, v, "dv")) || (rc = check_varlen(vl, q, k)))
     return rc;
   if (!stats || !dev_status) return fail(KFA_ERR_ARG, "stats / dev_status: null pointer");
   CUtensorMap mq, mk, mv, mdo;
@@ -289,6 +316,7 @@ int kfa_bwd_dkdv(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, 
     return rc;
   kfa::BwdParams p;
   fill_bwd_params(p, q, k, stats, scale, block, dev_status);
+  apply_varlen(p, vl);
   p.dk = dk->ptr;
   p.dk_sb = dk->stride[0];
   p.dk_sh = dk->stride[1];
@@ -301,12 +329,11 @@ int kfa_bwd_dkdv(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, 
   KFA_DISPATCH(q->shape[3], dtype, (launch_dkdv<KD, KB>(mq, mk, mv, mdo, p, s)));
 }
 
-int kfa_bwd_dq(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* dout,
-               const float* stats, const KfaTensor4* dq, float scale, int block, int dtype, int* dev_status,
-               void* stream) {
+int dq_impl(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* dout, const float* stats,
+            const KfaTensor4* dq, const Varlen* vl, float scale, int block, int dtype, int* dev_status, void* stream) {
   int rc;
   if ((rc = check_qkv(q, k, v, dtype, block)) || (rc = check_like(dout, q, "dout")) ||
-      (rc = check_like(dq, q, "dq")))
+      (rc = check_like(dq, q, "dq")) || (rc = check_varlen(vl, q, k)))
     return rc;
   if (!stats || !dev_status) return fail(KFA_ERR_ARG, "stats / dev_status: null pointer");
   CUtensorMap mq, mk, mv, mdo;
@@ -315,12 +342,66 @@ int kfa_bwd_dq(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, co
     return rc;
   kfa::BwdParams p;
   fill_bwd_params(p, q, k, stats, scale, block, dev_status);
+  apply_varlen(p, vl);
   p.dq = dq->ptr;
   p.dq_sb = dq->stride[0];
   p.dq_sh = dq->stride[1];
   p.dq_ss = dq->stride[2];
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   KFA_DISPATCH(q->shape[3], dtype, (launch_dq<KD, KB>(mq, mk, mv, mdo, p, s)));
+}
+
+}  // namespace
+
+extern "C" {
+
+int kfa_abi_version(void) { return KFA_ABI_VERSION; }
+
+const char* kfa_last_error(void) { return g_err; }
+
+int64_t kfa_bwd_stats_bytes(int64_t B, int64_t H, int64_t Sq) {
+  return B * H * ((Sq + 127) / 128) * 3 * 128 * 4;
+}
+
+int kfa_fwd(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* out, float* lse,
+            float scale, int block, int dtype, int* dev_status, void* stream) {
+  return fwd_impl(q, k, v, out, lse, nullptr, scale, block, dtype, dev_status, stream);
+}
+
+int kfa_bwd_prepare(const KfaTensor4* out, const KfaTensor4* dout, const float* lse, float* stats, int dtype,
+                    void* stream) {
+  return prepare_impl(out, dout, lse, stats, nullptr, dtype, stream);
+}
+
+int kfa_bwd_dkdv(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* dout,
+                 const float* stats, const KfaTensor4* dk, const KfaTensor4* dv, float scale, int block, int dtype,
+                 int* dev_status, void* stream) {
+  return dkdv_impl(q, k, v, dout, stats, dk, dv, nullptr, scale, block, dtype, dev_status, stream);
+}
+
+int kfa_bwd_dq(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* dout,
+               const float* stats, const KfaTensor4* dq, float scale, int block, int dtype, int* dev_status,
+               void* stream) {
+  return dq_impl(q, k, v, dout, stats, dq, nullptr, scale, block, dtype, dev_status, stream);
+}
+
+int kfa_fwd_varlen(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* out, float* lse,
+                   const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, int n_seqs, int max_q, int max_k,
+                   float scale, int block, int dtype, int* dev_status, void* stream) {
+  const Varlen vl{cu_seqlens_q, cu_seqlens_k, n_seqs, max_q, max_k};
+  return fwd_impl(q, k, v, out, lse, &vl, scale, block, dtype, dev_status, stream);
+}
+
+int kfa_bwd_varlen(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* out,
+                   const KfaTensor4* dout, const float* lse, float* stats, const KfaTensor4* dq, const KfaTensor4* dk,
+                   const KfaTensor4* dv, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, int n_seqs,
+                   int max_q, int max_k, float scale, int block, int dtype, int* dev_status, void* stream) {
+  const Varlen vl{cu_seqlens_q, cu_seqlens_k, n_seqs, max_q, max_k};
+  int rc;
+  if ((rc = check_like(out, q, "out"))) return rc;
+  if ((rc = prepare_impl(out, dout, lse, stats, &vl, dtype, stream))) return rc;
+  if ((rc = dkdv_impl(q, k, v, dout, stats, dk, dv, &vl, scale, block, dtype, dev_status, stream))) return rc;
+  return dq_impl(q, k, v, dout, stats, dq, &vl, scale, block, dtype, dev_status, stream);
 }
 
 int kfa_bwd(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* out,

@@ -63,6 +63,12 @@ struct BwdParams {
   long long dk32_sh;
   float* dv32;
   long long dv32_sh;
+  // Packed variable-length batches (cu_q != nullptr): tensors [1, H, T, D], sequence b (of B) owns query
+  // rows cu_q[b] .. cu_q[b + 1] and key rows cu_k[b] .. cu_k[b + 1]. Sq, Skv are then the tensors' row
+  // counts and n_q128 / n_k128 the tile counts of the longest sequence (they size the grid and the
+  // statistics, whose tiles are numbered from each sequence's first row).
+  const int* cu_q;
+  const int* cu_k;
 };
 
 struct PrepParams {
@@ -73,6 +79,7 @@ struct PrepParams {
   const float* lse;  // [B, H, 2, Sq]
   float* stats;      // [B*H, n_q128, 3, 128]
   int B, H, Sq, n_q128;
+  const int* cu_q;  // packed variable-length batches: see BwdParams
 };
 
 // ---------------------------------------------------------------------------------------
@@ -87,15 +94,22 @@ __global__ void __launch_bounds__(128) kfa_bwd_prepare_kernel(const PrepParams p
   const int b = bh / p.H, h = bh % p.H;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sub = lane / LPR, vec = lane % LPR;
-  const uint8_t* ob = reinterpret_cast<const uint8_t*>(p.o) + 2 * (b * p.o_sb + h * p.o_sh);
-  const uint8_t* gb = reinterpret_cast<const uint8_t*>(p.dout) + 2 * (b * p.do_sb + h * p.do_sh);
+  int Sq = p.Sq, bc = b;
+  long long q_base = 0;
+  if (p.cu_q != nullptr) {
+    q_base = p.cu_q[b];
+    Sq = p.cu_q[b + 1] - static_cast<int>(q_base);
+    bc = 0;
+  }
+  const uint8_t* ob = reinterpret_cast<const uint8_t*>(p.o) + 2 * (bc * p.o_sb + h * p.o_sh + q_base * p.o_ss);
+  const uint8_t* gb = reinterpret_cast<const uint8_t*>(p.dout) + 2 * (bc * p.do_sb + h * p.do_sh + q_base * p.do_ss);
   float* st = p.stats + (static_cast<long long>(bh) * p.n_q128 + tile) * 384;
-  const float* lse = p.lse + static_cast<long long>(bh) * 2 * p.Sq;
+  const float* lse = p.lse + (static_cast<long long>(bc) * p.H + h) * 2 * p.Sq + q_base;
   for (int r0 = warp * 32; r0 < warp * 32 + 32; r0 += RPW) {
     const int r_in = r0 + sub;
     const int row = tile * 128 + r_in;
     float acc = 0.f;
-    if (row < p.Sq) {
+    if (row < Sq) {
       const uint4 ov = *reinterpret_cast<const uint4*>(ob + 2 * (row * p.o_ss + vec * 8));
       const uint4 gv = *reinterpret_cast<const uint4*>(gb + 2 * (row * p.do_ss + vec * 8));
       const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w};
@@ -111,7 +125,7 @@ __global__ void __launch_bounds__(128) kfa_bwd_prepare_kernel(const PrepParams p
 #pragma unroll
     for (int off = LPR / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
     if (vec == 0) {
-      const bool valid = row < p.Sq;
+      const bool valid = row < Sq;
       // stored negated, so the consumers only add; padded rows: -m = -inf makes their P exactly 0
       st[r_in] = valid ? -lse[row] : -INFINITY;
       st[128 + r_in] = valid ? -lse[p.Sq + row] : 0.f;
@@ -320,12 +334,21 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int bh = blockIdx.x / p.n_k128;  // over batch x K / V heads
   const int kt = blockIdx.x % p.n_k128;
   const int b = bh / p.Hkv, hk = bh % p.Hkv;
-  const int kv0 = kt * 128;
+  const int kv0 = kt * 128;  // relative to the sequence's first key
+  int Sq = p.Sq, Skv = p.Skv, q_base = 0, k_base = 0, bc = b;  // bc: batch coordinate in the tensors
+  if (p.cu_q != nullptr) {
+    q_base = p.cu_q[b];
+    Sq = p.cu_q[b + 1] - q_base;
+    k_base = p.cu_k[b];
+    Skv = p.cu_k[b + 1] - k_base;
+    bc = 0;
+    if (kv0 >= Skv) return;  // the whole CTA, before anything is set up
+  }
   const int first_i = (p.P > 0) ? static_cast<int>((static_cast<long long>(kv0 / p.P) * p.P) / 128) : 0;
   // steps: for every query head of this K / V head's group, the query tiles that see these keys
-  const int n_per = max(p.n_q128 - first_i, 0);
+  const int n_per = max((Sq + 127) / 128 - first_i, 0);
   const int n_steps = n_per * p.group;
-  const bool ragged_keys = kv0 + 128 > p.Skv;
+  const bool ragged_keys = kv0 + 128 > Skv;
 
   if (tid == 0) {
     mbar_init(bar(B_KV), 1);
@@ -371,8 +394,8 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       prefetch_tensormap(&tmDO);
       mbar_expect_tx(bar(B_KV), 2 * Cfg::TILE_BYTES);
       for (int ch = 0; ch < CH; ++ch) {
-        tma_load_4d(sK + ch * TILE_BYTES_64, &tmK, bar(B_KV), ch * 64, kv0, hk, b);
-        tma_load_4d(sV + ch * TILE_BYTES_64, &tmV, bar(B_KV), ch * 64, kv0, hk, b);
+        tma_load_4d(sK + ch * TILE_BYTES_64, &tmK, bar(B_KV), ch * 64, k_base + kv0, hk, bc);
+        tma_load_4d(sV + ch * TILE_BYTES_64, &tmV, bar(B_KV), ch * 64, k_base + kv0, hk, bc);
       }
       bool ok = true;
       int issued = 0;
@@ -385,9 +408,9 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const uint32_t base = sSlot + slot * Cfg::KV_SLOT_BYTES;
         mbar_expect_tx(bar(B_QREADY + slot), 2 * Cfg::TILE_BYTES + STATS_BYTES);
         for (int ch = 0; ch < CH; ++ch) {
-          tma_load_4d(base + ch * TILE_BYTES_64, &tmQ, bar(B_QREADY + slot), ch * 64, i * 128, head, b);
+          tma_load_4d(base + ch * TILE_BYTES_64, &tmQ, bar(B_QREADY + slot), ch * 64, q_base + i * 128, head, bc);
           tma_load_4d(base + Cfg::TILE_BYTES + ch * TILE_BYTES_64, &tmDO, bar(B_QREADY + slot), ch * 64,
-                      i * 128, head, b);
+                      q_base + i * 128, head, bc);
         }
         bulk_load(base + 2 * Cfg::TILE_BYTES,
                   p.stats + (static_cast<long long>(b) * p.H + head) * p.stats_sh + i * 384ll,
@@ -468,7 +491,7 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const uint32_t tDP = tmem + Cfg::TM_DP + 64 * hq + lane_base;
     // first query that sees this key; padded keys see nothing
     int qmin = 0;
-    if (key >= p.Skv) qmin = 0x7fffffff;
+    if (key >= Skv) qmin = 0x7fffffff;
     else if (p.P > 0) qmin = (key / p.P) * p.P;
     const float2 c2 = make_float2(p.c, p.c);
     bool ok = true;
@@ -477,7 +500,7 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const int i = first_i + s % n_per;
       const int q0 = i * 128 + 64 * hq;  // query of this warpgroup's column 0
       // masked step: some (key, query) pair of this tile pair is hidden, or keys are padded
-      const bool masked = ragged_keys || (p.P > 0 && key_limit(i * 128, p.P, p.Skv) < kv0 + 128);
+      const bool masked = ragged_keys || (p.P > 0 && key_limit(i * 128, p.P, Skv) < kv0 + 128);
       ok = mbar_wait_warp(bar(B_QREADY + slot), (s / NSL) & 1, ctl, 7);  // stats of this step
       if (ok) ok = mbar_wait_warp(bar(B_S), s & 1, ctl, 8);
       if (!ok) break;
@@ -524,12 +547,13 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       mbar_arrive(bar(B_DS));
     }
     // ---- epilogue: warps 0-3 store dV, warps 4-7 store scale * dK ----
-    const bool valid = key < p.Skv;
+    const bool valid = key < Skv;
+    const long long grow_row = static_cast<long long>(k_base) + key;
     uint8_t* grow;
     if (hq == 0)
-      grow = reinterpret_cast<uint8_t*>(p.dv) + 2 * (b * p.dv_sb + hk * p.dv_sh + static_cast<long long>(key) * p.dv_ss);
+      grow = reinterpret_cast<uint8_t*>(p.dv) + 2 * (bc * p.dv_sb + hk * p.dv_sh + grow_row * p.dv_ss);
     else
-      grow = reinterpret_cast<uint8_t*>(p.dk) + 2 * (b * p.dk_sb + hk * p.dk_sh + static_cast<long long>(key) * p.dk_ss);
+      grow = reinterpret_cast<uint8_t*>(p.dk) + 2 * (bc * p.dk_sb + hk * p.dk_sh + grow_row * p.dk_ss);
     float* grow32 = nullptr;
     if (p.acc_mode != 0)
       grow32 = (hq == 0 ? p.dv32 + (static_cast<long long>(b) * p.Hkv + hk) * p.dv32_sh
@@ -607,10 +631,19 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   const int t = blockIdx.x % p.n_q128;
   const int qt = (p.P > 0) ? (p.n_q128 - 1 - t) : t;
   const int b = bh / p.H, h = bh % p.H;
-  const int row0 = qt * 128;
-  const int last = min(row0 + 127, p.Sq - 1);
-  const int n_steps = (key_limit(last, p.P, p.Skv) + 127) / 128;
-  const int n_unmasked = key_limit(row0, p.P, p.Skv) / 128;
+  const int row0 = qt * 128;  // relative to the sequence's first row
+  int Sq = p.Sq, Skv = p.Skv, q_base = 0, k_base = 0, bc = b;  // bc: batch coordinate in the tensors
+  if (p.cu_q != nullptr) {
+    q_base = p.cu_q[b];
+    Sq = p.cu_q[b + 1] - q_base;
+    k_base = p.cu_k[b];
+    Skv = p.cu_k[b + 1] - k_base;
+    bc = 0;
+    if (row0 >= Sq || Skv <= 0) return;  // the whole CTA, before anything is set up
+  }
+  const int last = min(row0 + 127, Sq - 1);
+  const int n_steps = (key_limit(last, p.P, Skv) + 127) / 128;
+  const int n_unmasked = key_limit(row0, p.P, Skv) / 128;
 
   if (tid == 0) {
     mbar_init(bar(B_Q), 1);
@@ -655,8 +688,8 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       prefetch_tensormap(&tmDO);
       mbar_expect_tx(bar(B_Q), 2 * Cfg::TILE_BYTES);
       for (int ch = 0; ch < CH; ++ch) {
-        tma_load_4d(sQ + ch * TILE_BYTES_64, &tmQ, bar(B_Q), ch * 64, row0, h, b);
-        tma_load_4d(sDO + ch * TILE_BYTES_64, &tmDO, bar(B_Q), ch * 64, row0, h, b);
+        tma_load_4d(sQ + ch * TILE_BYTES_64, &tmQ, bar(B_Q), ch * 64, q_base + row0, h, bc);
+        tma_load_4d(sDO + ch * TILE_BYTES_64, &tmDO, bar(B_Q), ch * 64, q_base + row0, h, bc);
       }
       bool ok = true;
       int issued = 0;
@@ -667,9 +700,10 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         const uint32_t base = sSlot + slot * Cfg::Q_SLOT_BYTES;
         mbar_expect_tx(bar(B_KVREADY + slot), 2 * Cfg::TILE_BYTES);
         for (int ch = 0; ch < CH; ++ch) {
-          tma_load_4d(base + ch * TILE_BYTES_64, &tmK, bar(B_KVREADY + slot), ch * 64, j * 128, h / p.group, b);
+          tma_load_4d(base + ch * TILE_BYTES_64, &tmK, bar(B_KVREADY + slot), ch * 64, k_base + j * 128,
+                      h / p.group, bc);
           tma_load_4d(base + Cfg::TILE_BYTES + ch * TILE_BYTES_64, &tmV, bar(B_KVREADY + slot), ch * 64,
-                      j * 128, h / p.group, b);
+                      k_base + j * 128, h / p.group, bc);
         }
         issued = j + 1;
       }
@@ -742,7 +776,7 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     const float2 nm = make_float2(st[r_in], st[r_in]);                // -m
     const float2 nl = make_float2(st[128 + r_in], st[128 + r_in]);    // -log2 l
     const float2 nd = make_float2(st[256 + r_in], st[256 + r_in]);    // -delta
-    const int my_limit = key_limit(min(row, p.Sq - 1), p.P, p.Skv);
+    const int my_limit = key_limit(min(row, Sq - 1), p.P, Skv);
     const float2 c2 = make_float2(p.c, p.c);
     bool ok = true;
     for (int j = 0; j < n_steps; ++j) {
@@ -790,11 +824,11 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       tc_fence_after();
       if (p.acc_mode == 0) {
         uint8_t* grow = reinterpret_cast<uint8_t*>(p.dq) +
-                        2 * (b * p.dq_sb + h * p.dq_sh + static_cast<long long>(row) * p.dq_ss);
-        store_acc_row<BF16>(tmem + Cfg::TM_ACC0 + lane_base, hk * (D / 2), D / 2, p.scale, grow, row < p.Sq);
+                        2 * (bc * p.dq_sb + h * p.dq_sh + static_cast<long long>(q_base + row) * p.dq_ss);
+        store_acc_row<BF16>(tmem + Cfg::TM_ACC0 + lane_base, hk * (D / 2), D / 2, p.scale, grow, row < Sq);
       } else {
         float* grow32 = p.dq32 + (static_cast<long long>(b) * p.H + h) * p.dq32_sh + static_cast<long long>(row) * D;
-        store_acc_row_f32(tmem + Cfg::TM_ACC0 + lane_base, hk * (D / 2), D / 2, p.scale, grow32, row < p.Sq,
+        store_acc_row_f32(tmem + Cfg::TM_ACC0 + lane_base, hk * (D / 2), D / 2, p.scale, grow32, row < Sq,
                           p.acc_mode == 2);
       }
     }

@@ -43,6 +43,12 @@ struct FwdParams {
   long long oa_sh;
   float* ml;           // m at ml[(b * H + h) * ml_sh + r], l at the same + ml_plane
   long long ml_sh, ml_plane;
+  // Packed variable-length batches (cu_q != nullptr): the tensors are [1, H, T, D]; sequence b (of B)
+  // owns query rows cu_q[b] .. cu_q[b + 1] and key rows cu_k[b] .. cu_k[b + 1] and is its own attention
+  // problem. Sq is then the tensors' row count T (it sizes the statistics planes) and n_q_tiles counts
+  // the tiles of the longest sequence; CTAs past the end of a shorter one return at once.
+  const int* cu_q;
+  const int* cu_k;
 };
 
 constexpr int FWD_THREADS = 320;
@@ -106,16 +112,25 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   const int q_tile = (p.P > 0) ? (p.n_q_tiles - 1 - t) : t;
   const int b = bh / p.H;
   const int h = bh % p.H;
-  const int row0 = q_tile * 256;
+  const int row0 = q_tile * 256;  // relative to the sequence's first row
+  int Sq = p.Sq, Skv = p.Skv, q_base = 0, k_base = 0, bc = b;  // bc: batch coordinate in the tensors
+  if (p.cu_q != nullptr) {
+    q_base = p.cu_q[b];
+    Sq = p.cu_q[b + 1] - q_base;
+    k_base = p.cu_k[b];
+    Skv = p.cu_k[b + 1] - k_base;
+    bc = 0;
+    if (row0 >= Sq || Skv <= 0) return;  // the whole CTA, before anything is set up
+  }
 
   int n_tiles[2], n_unmasked[2];
 #pragma unroll
   for (int hf = 0; hf < 2; ++hf) {
     const int first = row0 + 128 * hf;
-    if (first < p.Sq) {
-      const int last = min(first + 127, p.Sq - 1);
-      n_tiles[hf] = (key_limit(last, p.P, p.Skv) + 127) / 128;
-      n_unmasked[hf] = key_limit(first, p.P, p.Skv) / 128;
+    if (first < Sq) {
+      const int last = min(first + 127, Sq - 1);
+      n_tiles[hf] = (key_limit(last, p.P, Skv) + 127) / 128;
+      n_unmasked[hf] = key_limit(first, p.P, Skv) / 128;
     } else {
       n_tiles[hf] = 0;
       n_unmasked[hf] = 0;
@@ -174,7 +189,7 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         mbar_expect_tx(bar(B_QREADY + hf), Cfg::TILE_BYTES);
         for (int ch = 0; ch < CH; ++ch)
           tma_load_4d(sQ + (hf * CH + ch) * TILE_BYTES_64, &tmQ, bar(B_QREADY + hf), ch * 64,
-                      row0 + 128 * hf, h, b);
+                      q_base + row0 + 128 * hf, h, bc);
       }
       int armed[NS];  // last use index armed per stage (for the drain on abort)
       for (int i = 0; i < NS; ++i) armed[i] = -1;
@@ -189,7 +204,7 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const CUtensorMap* map = (idx & 1) ? &tmV : &tmK;
         for (int ch = 0; ch < CH; ++ch)
           tma_load_4d(sKV + (stage * CH + ch) * TILE_BYTES_64, map, bar(B_KVREADY + stage), ch * 64,
-                      j * 128, h / p.group, b);
+                      k_base + j * 128, h / p.group, bc);
         armed[stage] = use;
       }
       if (!ok) {
@@ -307,7 +322,7 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const uint32_t tO = tmem + (hf ? Cfg::TM_O1 : Cfg::TM_O0) + lane_base;
     const int nt = n_tiles[hf];
     const int nu = n_unmasked[hf];
-    const int my_limit = key_limit(min(row, p.Sq - 1), p.P, p.Skv);
+    const int my_limit = key_limit(min(row, Sq - 1), p.P, Skv);
     const float c = p.c;
 
     float m = -INFINITY;
@@ -414,7 +429,7 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       // (mode 1), or is merged into (mode 2), the carry in global memory. Merging keeps the two
       // statistics apart and shifts both sides to the common row max before anything is rounded.
       tc_fence_after();
-      const bool valid = row < p.Sq;
+      const bool valid = row < Sq;
       const long long bhl = static_cast<long long>(b) * p.H + h;
       float* mlp = p.ml + bhl * p.ml_sh + row;
       float* arow = p.o_acc + bhl * p.oa_sh + static_cast<long long>(row) * D;
@@ -454,9 +469,9 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     } else if (ok && nt > 0) {
       tc_fence_after();
       const float inv = 1.0f / l;
-      const bool valid = row < p.Sq;
+      const bool valid = row < Sq;
       uint8_t* orow = reinterpret_cast<uint8_t*>(p.o) +
-                      2 * (b * p.o_sb + h * p.o_sh + static_cast<long long>(row) * p.o_ss);
+                      2 * (bc * p.o_sb + h * p.o_sh + static_cast<long long>(q_base + row) * p.o_ss);
 #pragma unroll
       for (int cc = 0; cc < D; cc += 32) {
         float o[32];
@@ -475,7 +490,7 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
       }
       if (valid) {
-        float* lse = p.lse + (static_cast<long long>(b) * p.H + h) * 2 * p.Sq;
+        float* lse = p.lse + (static_cast<long long>(bc) * p.H + h) * 2 * p.Sq + q_base;
         lse[row] = m;
         lse[p.Sq + row] = log2f(l);
       }

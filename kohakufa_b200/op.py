@@ -165,3 +165,148 @@ def attention(
         scale = q.shape[-1] ** -0.5
     out, _ = attention_fwd_op(q, k, v, float(scale), int(block_causal))
     return out
+
+
+# --------------------------------------------------------------------------------------
+# Variable-length (packed) sequences. Mirrors the reference's varlen ops (op.py:183-289); the plan is
+# three host integers instead of device tile tables, because the kernels read the sequence
+# boundaries themselves and return at once for tiles past a sequence's end.
+# --------------------------------------------------------------------------------------
+
+
+def _as4(t: Tensor) -> Tensor:
+    """``[T, H, D]`` packed tensor as the ``[1, H, T, D]`` view the library takes."""
+    return t.unsqueeze(0).transpose(1, 2)
+
+
+@torch.library.custom_op("kohakufa_b200::sm100_varlen_forward", mutates_args=(), device_types="cuda")
+def varlen_fwd_op(
+    q: Tensor, k: Tensor, v: Tensor, cu_seqlens_q: Tensor, cu_seqlens_k: Tensor, max_q: int, max_k: int,
+    scale: float, block: int,
+) -> tuple[Tensor, Tensor]:  # fmt: skip
+    lib = _lib.load()
+    total_q, heads, _ = q.shape
+    out = torch.empty_like(q)
+    lse = q.new_empty(1, heads, 2, total_q, dtype=torch.float32)
+    with torch.cuda.device(q.device):
+        rc = lib.kfa_fwd_varlen(
+            *(ctypes.byref(_lib.tensor4(_as4(t))) for t in (q, k, v, out)),
+            lse.data_ptr(),
+            cu_seqlens_q.data_ptr(),
+            cu_seqlens_k.data_ptr(),
+            cu_seqlens_q.numel() - 1,
+            max_q,
+            max_k,
+            float(scale),
+            int(block),
+            _lib.dtype_code(q.dtype),
+            _lib.status_word(q.device).data_ptr(),
+            _lib.stream_ptr(q.device),
+        )
+    _lib.check(rc)
+    return out, lse
+
+
+@varlen_fwd_op.register_fake
+def _(q, k, v, cu_seqlens_q, cu_seqlens_k, max_q, max_k, scale, block):
+    return torch.empty_like(q), q.new_empty(1, q.shape[1], 2, q.shape[0], dtype=torch.float32)
+
+
+@torch.library.custom_op("kohakufa_b200::sm100_varlen_backward", mutates_args=(), device_types="cuda")
+def varlen_bwd_op(
+    q: Tensor, k: Tensor, v: Tensor, out: Tensor, dout: Tensor, lse: Tensor, cu_seqlens_q: Tensor,
+    cu_seqlens_k: Tensor, max_q: int, max_k: int, scale: float, block: int,
+) -> tuple[Tensor, Tensor, Tensor]:  # fmt: skip
+    lib = _lib.load()
+    n_seqs = cu_seqlens_q.numel() - 1
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    stats = q.new_empty(lib.kfa_bwd_stats_bytes(n_seqs, q.shape[1], max_q) // 4, dtype=torch.float32)
+    with torch.cuda.device(q.device):
+        rc = lib.kfa_bwd_varlen(
+            *(ctypes.byref(_lib.tensor4(_as4(t))) for t in (q, k, v, out, dout)),
+            lse.data_ptr(),
+            stats.data_ptr(),
+            *(ctypes.byref(_lib.tensor4(_as4(t))) for t in (dq, dk, dv)),
+            cu_seqlens_q.data_ptr(),
+            cu_seqlens_k.data_ptr(),
+            n_seqs,
+            max_q,
+            max_k,
+            float(scale),
+            int(block),
+            _lib.dtype_code(q.dtype),
+            _lib.status_word(q.device).data_ptr(),
+            _lib.stream_ptr(q.device),
+        )
+    _lib.check(rc)
+    return dq, dk, dv
+
+
+@varlen_bwd_op.register_fake
+def _(q, k, v, out, dout, lse, cu_seqlens_q, cu_seqlens_k, max_q, max_k, scale, block):
+    return torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+
+
+def _varlen_setup(ctx, inputs, output):
+    q, k, v, cu_q, cu_k, max_q, max_k, scale, block = inputs
+    out, lse = output
+    ctx.save_for_backward(q, k, v, out, lse, cu_q, cu_k)
+    ctx.plan = (max_q, max_k)
+    ctx.scale, ctx.block = scale, block
+    ctx.mark_non_differentiable(lse)
+
+
+def _varlen_backward(ctx, dout, dlse):
+    q, k, v, out, lse, cu_q, cu_k = ctx.saved_tensors
+    dq, dk, dv = varlen_bwd_op(q, k, v, out, dout.contiguous(), lse, cu_q, cu_k, *ctx.plan, ctx.scale, ctx.block)
+    return dq, dk, dv, None, None, None, None, None, None
+
+
+varlen_fwd_op.register_autograd(_varlen_backward, setup_context=_varlen_setup)
+
+
+def varlen_plan(
+    cu_seqlens_q: Tensor, cu_seqlens_k: Tensor, heads: int = 0, kv_heads: int = 0, block: int = 0
+) -> tuple[int, int, int]:
+    """What a call needs to know about a batch of packed sequences on the HOST: (number of sequences,
+    longest query length, longest key length). Reads ``cu_seqlens`` once (a device-to-host copy):
+    build it outside CUDA-graph capture and reuse it for every call with the same lengths
+    (reference: op.py:252-261; ``heads``, ``kv_heads``, ``block`` are accepted for signature
+    compatibility, the plan does not depend on them). A sequence with queries but no keys is refused."""
+    len_q = (cu_seqlens_q[1:] - cu_seqlens_q[:-1]).tolist()
+    len_k = (cu_seqlens_k[1:] - cu_seqlens_k[:-1]).tolist()
+    if len(len_q) != len(len_k) or not len_q:
+        raise ValueError("varlen_plan: cu_seqlens_q and cu_seqlens_k must describe the same (non-zero) number of sequences")
+    if min(len_q) < 0 or min(len_k) < 0:
+        raise ValueError("varlen_plan: cu_seqlens must be non-decreasing")
+    if any(nq > 0 and nk == 0 for nq, nk in zip(len_q, len_k)):
+        raise ValueError("varlen_plan: a sequence with queries needs at least one key")
+    return len(len_q), max(max(len_q), 1), max(max(len_k), 1)
+
+
+def attention_varlen(
+    q: Tensor,
+    k: Tensor,
+    v: Tensor,
+    cu_seqlens_q: Tensor,
+    cu_seqlens_k: Tensor,
+    scale: float | None = None,
+    block_causal: int = 0,
+    plan: tuple | None = None,
+) -> Tensor:
+    """Packed sequences, each its own attention problem: ``q [Tq, H, D]``, ``k / v [Tk, Hkv, D]``;
+    sequence ``b`` is rows ``cu_seqlens[b] : cu_seqlens[b + 1]`` (int32 [B + 1] on the device).
+    ``plan`` from ``varlen_plan`` (built here if None). Reference: op.py:264-289."""
+    if q.dim() != 3 or k.dim() != 3 or v.dim() != 3:
+        raise ValueError("attention_varlen: q, k, v must be [T, H, D]")
+    _check(*(_as4(t) for t in (q, k, v)))
+    if scale is None:
+        scale = q.shape[-1] ** -0.5
+    cu_seqlens_q, cu_seqlens_k = cu_seqlens_q.int(), cu_seqlens_k.int()
+    if plan is None:
+        plan = varlen_plan(cu_seqlens_q, cu_seqlens_k, q.shape[1], k.shape[1], block_causal)
+    n_seqs, max_q, max_k = plan
+    if cu_seqlens_q.numel() != n_seqs + 1 or cu_seqlens_k.numel() != n_seqs + 1:
+        raise ValueError(f"attention_varlen: the plan is for {n_seqs} sequences")
+    out, _ = varlen_fwd_op(q, k, v, cu_seqlens_q, cu_seqlens_k, int(max_q), int(max_k), float(scale), int(block_causal))
+    return out

@@ -121,9 +121,43 @@ def test_center_keys_is_a_pure_shift():
 
 def test_other_exports_raise():
     assert set(kohakufa_b200.__all__) == {"PackedMask", "attention", "attention_varlen", "pack_mask", "varlen_plan"}
-    for name in ("attention_varlen", "varlen_plan", "pack_mask", "PackedMask"):
+    for name in ("pack_mask", "PackedMask"):
         with pytest.raises(NotImplementedError):
             getattr(kohakufa_b200, name)()
+
+
+def test_varlen_plan_reads_lengths_once_and_validates():
+    cu_q = torch.tensor([0, 5, 5, 300], dtype=torch.int32)
+    cu_k = torch.tensor([0, 9, 9, 100], dtype=torch.int32)
+    assert kohakufa_b200.varlen_plan(cu_q, cu_k, 4, 2, 1) == (3, 295, 91)
+    with pytest.raises(ValueError):  # queries without keys
+        kohakufa_b200.varlen_plan(cu_q, torch.tensor([0, 9, 100, 100], dtype=torch.int32))
+    with pytest.raises(ValueError):  # different numbers of sequences
+        kohakufa_b200.varlen_plan(cu_q, cu_k[:-1])
+    with pytest.raises(ValueError):  # decreasing
+        kohakufa_b200.varlen_plan(torch.tensor([0, 9, 5], dtype=torch.int32), torch.tensor([0, 9, 12], dtype=torch.int32))
+
+
+def test_varlen_fake_kernels_infer_layouts():
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    with FakeTensorMode():
+        q = torch.empty(300, 4, 64, dtype=torch.float16, device="cuda")
+        k = torch.empty(100, 2, 64, dtype=torch.float16, device="cuda")
+        cu = torch.empty(4, dtype=torch.int32, device="cuda")
+        out, lse = torch.ops.kohakufa_b200.sm100_varlen_forward(q, k, k, cu, cu, 295, 91, 0.125, 1)
+        assert out.shape == q.shape and lse.shape == (1, 4, 2, 300) and lse.dtype == torch.float32
+        dq, dk, dv = torch.ops.kohakufa_b200.sm100_varlen_backward(q, k, k, out, out, lse, cu, cu, 295, 91, 0.125, 1)
+        assert dq.shape == q.shape and dk.shape == k.shape and dv.shape == k.shape
+
+
+def test_center_keys_varlen_subtracts_each_sequence_mean():
+    from kohakufa_b200.api import _center_keys_varlen
+
+    k = torch.randn(12, 2, 8) + 3.0
+    cu = torch.tensor([0, 5, 5, 12], dtype=torch.int32)
+    c = _center_keys_varlen(k, cu)
+    assert float(c[:5].mean(0).abs().max()) < 1e-5 and float(c[5:].mean(0).abs().max()) < 1e-5
 
 
 def test_fake_kernels_infer_layouts():
