@@ -151,10 +151,13 @@ struct BwdCfg {
   static constexpr int KV_SLOT_BYTES = 2 * TILE_BYTES + 2048;  // stats padded to keep 1 KB alignment
   static constexpr int KV_SMEM_TILES = 2 * TILE_BYTES + KV_SLOTS * KV_SLOT_BYTES;
   static constexpr int KV_SMEM_BYTES = KV_SMEM_TILES + 1024 + 256;
-  // dQ kernel: Q, dO resident; ring of (K_j, V_j) slots.
-  static constexpr int Q_SLOTS = (D == 128) ? 2 : 3;
-  static constexpr int Q_SLOT_BYTES = 2 * TILE_BYTES;
-  static constexpr int Q_SMEM_TILES = 2 * TILE_BYTES + Q_SLOTS * Q_SLOT_BYTES;
+  // dQ kernel: Q, dO resident; K_j and V_j through rings of their own. K_j is read by S(j) and, a step
+  // later, by dQ(j); V_j only by dP(j): three K buffers and two V buffers let the copy of tile j + 2
+  // start a whole step before it is needed (with K and V sharing two slots it could start only when
+  // dQ(j) had retired, and the tensor core waited for the copy at every step).
+  static constexpr int NK = (D == 128) ? 3 : 4;
+  static constexpr int NV = (D == 128) ? 2 : 3;
+  static constexpr int Q_SMEM_TILES = (2 + NK + NV) * TILE_BYTES;
   static constexpr int Q_SMEM_BYTES = Q_SMEM_TILES + 1024 + 256;
 };
 
@@ -600,25 +603,28 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                   const BwdParams p) {
   using Cfg = BwdCfg<D>;
   constexpr int CH = Cfg::CHUNKS;
-  constexpr int NSL = Cfg::Q_SLOTS;
+  constexpr int NK = Cfg::NK, NV = Cfg::NV;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t sQ = smem_base;
   const uint32_t sDO = smem_base + Cfg::TILE_BYTES;
-  const uint32_t sSlot = smem_base + 2 * Cfg::TILE_BYTES;  // slot: K | V
+  const uint32_t sKr = smem_base + 2 * Cfg::TILE_BYTES;         // K ring
+  const uint32_t sVr = smem_base + (2 + NK) * Cfg::TILE_BYTES;  // V ring
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::Q_SMEM_TILES);
-  constexpr int B_Q = 0;                  // Q, dO landed
-  constexpr int B_KVREADY = 1;            // NSL
-  constexpr int B_KVFREE = 1 + NSL;       // NSL
-  constexpr int B_S = 1 + 2 * NSL;        // S(j) in TMEM
-  constexpr int B_DP = 2 + 2 * NSL;       // dP(j) in TMEM
-  constexpr int B_SREAD = 3 + 2 * NSL;    // both warpgroups have read S(j) (256 arrivals)
-  constexpr int B_DS = 4 + 2 * NSL;       // dS(j) stored by both warpgroups
-  constexpr int B_ACC = 5 + 2 * NSL;
-  constexpr int B_DRAIN = 6 + 2 * NSL;
-  constexpr int N_BARS = 7 + 2 * NSL;
+  constexpr int B_Q = 0;                       // Q, dO landed
+  constexpr int B_KREADY = 1;                  // NK
+  constexpr int B_KFREE = 1 + NK;              // NK   dQ(j), the last reader of K_j, has retired
+  constexpr int B_VREADY = 1 + 2 * NK;         // NV
+  constexpr int B_VFREE = 1 + 2 * NK + NV;     // NV   dP(j), the only reader of V_j, has retired
+  constexpr int B_S = 1 + 2 * NK + 2 * NV;     // S(j) in TMEM
+  constexpr int B_DP = B_S + 1;                // dP(j) in TMEM
+  constexpr int B_SREAD = B_S + 2;             // both warpgroups have read S(j) (256 arrivals)
+  constexpr int B_DS = B_S + 3;                // dS(j) stored by both warpgroups
+  constexpr int B_ACC = B_S + 4;
+  constexpr int B_DRAIN = B_S + 5;
+  constexpr int N_BARS = B_S + 6;
   static_assert(N_BARS * 8 + 16 <= 256, "barrier block too small");
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + N_BARS);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
@@ -647,9 +653,13 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 
   if (tid == 0) {
     mbar_init(bar(B_Q), 1);
-    for (int i = 0; i < NSL; ++i) {
-      mbar_init(bar(B_KVREADY + i), 1);
-      mbar_init(bar(B_KVFREE + i), 1);
+    for (int i = 0; i < NK; ++i) {
+      mbar_init(bar(B_KREADY + i), 1);
+      mbar_init(bar(B_KFREE + i), 1);
+    }
+    for (int i = 0; i < NV; ++i) {
+      mbar_init(bar(B_VREADY + i), 1);
+      mbar_init(bar(B_VFREE + i), 1);
     }
     mbar_init(bar(B_S), 1);
     mbar_init(bar(B_DP), 1);
@@ -692,25 +702,33 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         tma_load_4d(sDO + ch * TILE_BYTES_64, &tmDO, bar(B_Q), ch * 64, q_base + row0, h, bc);
       }
       bool ok = true;
-      int issued = 0;
+      int issued_k = 0, issued_v = 0;
       for (int j = 0; j < n_steps; ++j) {
-        const int slot = j % NSL, use = j / NSL;
-        if (use > 0) ok = mbar_wait(bar(B_KVFREE + slot), (use - 1) & 1, ctl, 1);
+        const int ks = j % NK, vs = j % NV;
+        if (j >= NK) ok = mbar_wait(bar(B_KFREE + ks), (j / NK - 1) & 1, ctl, 1);
         if (!ok) break;
-        const uint32_t base = sSlot + slot * Cfg::Q_SLOT_BYTES;
-        mbar_expect_tx(bar(B_KVREADY + slot), 2 * Cfg::TILE_BYTES);
-        for (int ch = 0; ch < CH; ++ch) {
-          tma_load_4d(base + ch * TILE_BYTES_64, &tmK, bar(B_KVREADY + slot), ch * 64, k_base + j * 128,
-                      h / p.group, bc);
-          tma_load_4d(base + Cfg::TILE_BYTES + ch * TILE_BYTES_64, &tmV, bar(B_KVREADY + slot), ch * 64,
+        mbar_expect_tx(bar(B_KREADY + ks), Cfg::TILE_BYTES);
+        for (int ch = 0; ch < CH; ++ch)
+          tma_load_4d(sKr + ks * Cfg::TILE_BYTES + ch * TILE_BYTES_64, &tmK, bar(B_KREADY + ks), ch * 64,
                       k_base + j * 128, h / p.group, bc);
-        }
-        issued = j + 1;
+        issued_k = j + 1;
+        if (j >= NV) ok = mbar_wait(bar(B_VFREE + vs), (j / NV - 1) & 1, ctl, 1);
+        if (!ok) break;
+        mbar_expect_tx(bar(B_VREADY + vs), Cfg::TILE_BYTES);
+        for (int ch = 0; ch < CH; ++ch)
+          tma_load_4d(sVr + vs * Cfg::TILE_BYTES + ch * TILE_BYTES_64, &tmV, bar(B_VREADY + vs), ch * 64,
+                      k_base + j * 128, h / p.group, bc);
+        issued_v = j + 1;
       }
-      if (!ok) {
-        for (int j = max(issued - NSL, 0); j < issued; ++j) {
+      if (!ok) {  // aborting: let the copies in flight land before the CTA gives up its shared memory
+        for (int j = max(issued_k - NK, 0); j < issued_k; ++j) {
           const long long t0 = clock64();
-          while (!mbar_try_wait(bar(B_KVREADY + j % NSL), (j / NSL) & 1) && clock64() - t0 < 2000000ll) {
+          while (!mbar_try_wait(bar(B_KREADY + j % NK), (j / NK) & 1) && clock64() - t0 < 2000000ll) {
+          }
+        }
+        for (int j = max(issued_v - NV, 0); j < issued_v; ++j) {
+          const long long t0 = clock64();
+          while (!mbar_try_wait(bar(B_VREADY + j % NV), (j / NV) & 1) && clock64() - t0 < 2000000ll) {
           }
         }
       }
@@ -724,26 +742,29 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       const uint32_t tS = tmem + Cfg::TM_S, tDP = tmem + Cfg::TM_DP, tDQ = tmem + Cfg::TM_ACC0;
       const uint32_t q_lo = sdesc_lo(sQ, 16), do_lo = sdesc_lo(sDO, 16);
       bool ok = mbar_wait_warp(bar(B_Q), 0, ctl, 2);
-      if (ok) ok = mbar_wait_warp(bar(B_KVREADY + 0), 0, ctl, 3);
+      if (ok) ok = mbar_wait_warp(bar(B_KREADY + 0), 0, ctl, 3);
       if (ok) {
         tc_fence_after();
-        issue_kmajor_n128<D>(lead, tS, q_lo, sdesc_lo(sSlot, 16), IDESC_S);
+        issue_kmajor_n128<D>(lead, tS, q_lo, sdesc_lo(sKr, 16), IDESC_S);
         umma_commit_lead(lead, bar(B_S));
-        issue_kmajor_n128<D>(lead, tDP, do_lo, sdesc_lo(sSlot + Cfg::TILE_BYTES, 16), IDESC_S);
+        ok = mbar_wait_warp(bar(B_VREADY + 0), 0, ctl, 3);
+      }
+      if (ok) {
+        tc_fence_after();
+        issue_kmajor_n128<D>(lead, tDP, do_lo, sdesc_lo(sVr, 16), IDESC_S);
         umma_commit_lead(lead, bar(B_DP));
+        umma_commit_lead(lead, bar(B_VFREE + 0));
       }
       for (int j = 0; j < n_steps && ok; ++j) {
-        const int slot = j % NSL;
-        const uint32_t k_s = sSlot + slot * Cfg::Q_SLOT_BYTES;
-        const int nslot = (j + 1) % NSL;
-        const uint32_t k_n = sSlot + nslot * Cfg::Q_SLOT_BYTES;
+        const uint32_t k_s = sKr + (j % NK) * Cfg::TILE_BYTES;
+        const int nk = (j + 1) % NK, nv = (j + 1) % NV;
         const bool more = j + 1 < n_steps;
         if (more) {  // S(j+1) as soon as the warpgroups hold S(j) in registers
-          ok = mbar_wait_warp(bar(B_KVREADY + nslot), ((j + 1) / NSL) & 1, ctl, 4);
+          ok = mbar_wait_warp(bar(B_KREADY + nk), ((j + 1) / NK) & 1, ctl, 4);
           if (ok) ok = mbar_wait_warp(bar(B_SREAD), j & 1, ctl, 5);
           if (!ok) break;
           tc_fence_after();
-          issue_kmajor_n128<D>(lead, tS, q_lo, sdesc_lo(k_n, 16), IDESC_S);
+          issue_kmajor_n128<D>(lead, tS, q_lo, sdesc_lo(sKr + nk * Cfg::TILE_BYTES, 16), IDESC_S);
           umma_commit_lead(lead, bar(B_S));
         }
         // dQ += dS(j) K_j, then dP(j+1) may overwrite the dS columns
@@ -751,10 +772,14 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         if (!ok) break;
         tc_fence_after();
         issue_tmemA_k128<D>(lead, tDQ, tDP, sdesc_lo(k_s, TILE_BYTES_64), IDESC_ACC, j > 0);
-        umma_commit_lead(lead, bar(B_KVFREE + slot));
+        umma_commit_lead(lead, bar(B_KFREE + j % NK));
         if (more) {
-          issue_kmajor_n128<D>(lead, tDP, do_lo, sdesc_lo(k_n + Cfg::TILE_BYTES, 16), IDESC_S);
+          ok = mbar_wait_warp(bar(B_VREADY + nv), ((j + 1) / NV) & 1, ctl, 4);
+          if (!ok) break;
+          tc_fence_after();
+          issue_kmajor_n128<D>(lead, tDP, do_lo, sdesc_lo(sVr + nv * Cfg::TILE_BYTES, 16), IDESC_S);
           umma_commit_lead(lead, bar(B_DP));
+          umma_commit_lead(lead, bar(B_VFREE + nv));
         }
       }
       if (ok) umma_commit_lead(lead, bar(B_ACC));

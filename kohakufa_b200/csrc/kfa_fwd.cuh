@@ -58,7 +58,11 @@ template <int D>
 struct FwdCfg {
   static constexpr int CHUNKS = D / 64;
   static constexpr int TILE_BYTES = CHUNKS * TILE_BYTES_64;
+#ifdef KFA_FWD_STAGES_128
+  static constexpr int STAGES = (D == 128) ? KFA_FWD_STAGES_128 : 6;
+#else
   static constexpr int STAGES = (D == 128) ? 4 : 6;
+#endif
   static constexpr int SMEM_TILES = 2 * TILE_BYTES + STAGES * TILE_BYTES;
   static constexpr int SMEM_BYTES = SMEM_TILES + 1024 /*alignment slack*/ + 256 /*barriers*/;
   static constexpr uint32_t TMEM_COLS = 512;
