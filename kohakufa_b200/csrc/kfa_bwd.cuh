@@ -232,43 +232,51 @@ __device__ __forceinline__ void store_acc_row(uint32_t taddr, int col0, int ncol
   }
 }
 
-// P of 32 columns (queries) of one key row in the dK / dV kernel, from S^T (fp32, two columns per
-// float2) and the per-query statistics in shared memory (-m at st[0..], -log2 l at st[128..]):
+// P^T and dS^T in the dK / dV kernel. The per-query statistics (-m at st[0..], -log2 l at st[128..],
+// -delta at st[256..], in shared memory) belong to COLUMNS of the transposed tile, so every thread
+// needs them for every column it touches. With one TMEM lane (key) per thread that is all 64 columns
+// of its warpgroup: 192 floats per thread and step, whose broadcast loads cost about 1000 shared-memory
+// cycles per step on top of the 1500 the tensor core's operands and 500 the TMA need, and shared
+// memory, not the tensor core, bounds the kernel. The fragment shape (tcgen05.ld.16x256b) gives a thread
+// 4 keys x 16 queries instead: a quarter of the statistics, as 8-byte loads shared by 8 lanes.
+//
+// Element order of sv / pr / the packed words: index 16 * half + 2 * j + sel is the column pair
+// 8j + 2(lane % 4), +1 of key row (lane / 4 + 8 * sel) of the warp's 16-lane half `half`.
 //   P = exp2(fma(S - m, c, -log2 l)), kept in fp32 (pr) and packed to 16 bits (pk).
-// MASKED: columns whose query index (q_first + column) is below qmin get P = 0.
+// MASKED: a pair whose query index is below the key's first visible query (qmin[2 * half + sel]) gets P = 0.
 template <bool BF16, bool MASKED>
-__device__ __forceinline__ void p_cols_by_query(const float2* sv, const float* st, float2 c2, int q_first, int qmin,
-                                                float2* pr, uint32_t* pk) {
+__device__ __forceinline__ void p_frag(const float2* sv, const float* st, float2 c2, int q_first, const int* qmin,
+                                       float2* pr, uint32_t* pk) {
 #pragma unroll
-  for (int x = 0; x < 32; x += 4) {
-    const float4 nm = *reinterpret_cast<const float4*>(st + x);
-    const float4 nl = *reinterpret_cast<const float4*>(st + 128 + x);
-    const float2 x0 = __ffma2_rn(__fadd2_rn(sv[x / 2], make_float2(nm.x, nm.y)), c2, make_float2(nl.x, nl.y));
-    const float2 x1 = __ffma2_rn(__fadd2_rn(sv[x / 2 + 1], make_float2(nm.z, nm.w)), c2, make_float2(nl.z, nl.w));
-    float2 p0 = make_float2(ex2(x0.x), ex2(x0.y));
-    float2 p1 = make_float2(ex2(x1.x), ex2(x1.y));
-    if constexpr (MASKED) {
-      if (q_first + x < qmin) p0.x = 0.f;
-      if (q_first + x + 1 < qmin) p0.y = 0.f;
-      if (q_first + x + 2 < qmin) p1.x = 0.f;
-      if (q_first + x + 3 < qmin) p1.y = 0.f;
+  for (int j = 0; j < 8; ++j) {
+    const float2 nm = *reinterpret_cast<const float2*>(st + 8 * j);
+    const float2 nl = *reinterpret_cast<const float2*>(st + 128 + 8 * j);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {  // e = 2 * half + sel
+      const int idx = 16 * (e >> 1) + 2 * j + (e & 1);
+      const float2 x = __ffma2_rn(__fadd2_rn(sv[idx], nm), c2, nl);
+      float2 pv = make_float2(ex2(x.x), ex2(x.y));
+      if constexpr (MASKED) {
+        if (q_first + 8 * j < qmin[e]) pv.x = 0.f;
+        if (q_first + 8 * j + 1 < qmin[e]) pv.y = 0.f;
+      }
+      pr[idx] = pv;
+      pk[idx] = pack16<BF16>(pv.x, pv.y);
     }
-    pr[x / 2] = p0;
-    pr[x / 2 + 1] = p1;
-    pk[x / 2] = pack16<BF16>(p0.x, p0.y);
-    pk[x / 2 + 1] = pack16<BF16>(p1.x, p1.y);
   }
 }
-// dS = (dP - delta) * P of the same 32 columns (-delta at st[256..]), rounded once to 16 bits, unscaled.
+// dS = (dP - delta) * P of the same elements, rounded once to 16 bits, unscaled.
 template <bool BF16>
-__device__ __forceinline__ void ds_cols_by_query(const float2* dp, const float2* pr, const float* st, uint32_t* dk) {
+__device__ __forceinline__ void ds_frag(const float2* dp, const float2* pr, const float* st, uint32_t* dk) {
 #pragma unroll
-  for (int x = 0; x < 32; x += 4) {
-    const float4 nd = *reinterpret_cast<const float4*>(st + 256 + x);
-    const float2 d0 = __fmul2_rn(__fadd2_rn(dp[x / 2], make_float2(nd.x, nd.y)), pr[x / 2]);
-    const float2 d1 = __fmul2_rn(__fadd2_rn(dp[x / 2 + 1], make_float2(nd.z, nd.w)), pr[x / 2 + 1]);
-    dk[x / 2] = pack16<BF16>(d0.x, d0.y);
-    dk[x / 2 + 1] = pack16<BF16>(d1.x, d1.y);
+  for (int j = 0; j < 8; ++j) {
+    const float2 nd = *reinterpret_cast<const float2*>(st + 256 + 8 * j);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int idx = 16 * (e >> 1) + 2 * j + (e & 1);
+      const float2 d = __fmul2_rn(__fadd2_rn(dp[idx], nd), pr[idx]);
+      dk[idx] = pack16<BF16>(d.x, d.y);
+    }
   }
 }
 
@@ -488,20 +496,29 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     // =========================== P^T / dS^T and epilogue ===========================
     const int hq = warp >> 2;  // which 64 query columns of every tile
     const int k_in = tid & 127;
-    const int key = kv0 + k_in;
+    const int key = kv0 + k_in;  // the epilogue's row (one TMEM lane per thread)
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tS = tmem + Cfg::TM_S + 64 * hq + lane_base;
     const uint32_t tDP = tmem + Cfg::TM_DP + 64 * hq + lane_base;
-    // first query that sees this key; padded keys see nothing
-    int qmin = 0;
-    if (key >= Skv) qmin = 0x7fffffff;
-    else if (p.P > 0) qmin = (key / p.P) * p.P;
+    constexpr uint32_t HALF = 16u << 16;  // the warp's second 16 lanes
+    // In the compute phases a thread works on 4 key rows x 16 query columns (see p_frag):
+    // first query that sees each of its keys; padded keys see nothing
+    const int col0 = 2 * (lane & 3);  // its first column inside every block of 8
+    int qmin[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int kr = kv0 + (warp & 3) * 32 + 16 * (e >> 1) + (lane >> 2) + 8 * (e & 1);
+      qmin[e] = 0;
+      if (kr >= Skv) qmin[e] = 0x7fffffff;
+      else if (p.P > 0) qmin[e] = (kr / p.P) * p.P;
+    }
     const float2 c2 = make_float2(p.c, p.c);
     bool ok = true;
     for (int s = 0; s < n_steps; ++s) {
+      KFA_PROF_BEGIN();
       const int slot = s % NSL;
       const int i = first_i + s % n_per;
-      const int q0 = i * 128 + 64 * hq;  // query of this warpgroup's column 0
+      const int q0 = i * 128 + 64 * hq + col0;  // query of this thread's first column
       // masked step: some (key, query) pair of this tile pair is hidden, or keys are padded
       const bool masked = ragged_keys || (p.P > 0 && key_limit(i * 128, p.P, Skv) < kv0 + 128);
       ok = mbar_wait_warp(bar(B_QREADY + slot), (s / NSL) & 1, ctl, 7);  // stats of this step
@@ -510,44 +527,48 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tc_fence_after();
       const float* st =
           reinterpret_cast<const float*>(smem + 2 * Cfg::TILE_BYTES + slot * Cfg::KV_SLOT_BYTES +
-                                         2 * Cfg::TILE_BYTES) + 64 * hq;
-      float2 pr[32];  // fp32 P of this thread's 64 columns, kept for the dS phase
+                                         2 * Cfg::TILE_BYTES) + 64 * hq + col0;
+      float2 pr[32];  // fp32 P of this thread's 64 elements, kept for the dS phase
+      KFA_PROF_END(5);
+      KFA_PROF_BEGIN();
       {
         float2 sv[32];
-        tmem_ld32(tS, reinterpret_cast<uint32_t*>(sv));
-        tmem_ld32(tS + 32, reinterpret_cast<uint32_t*>(sv + 16));
+        tmem_ld_16x256b_x8(tS, reinterpret_cast<uint32_t*>(sv));
+        tmem_ld_16x256b_x8(tS + HALF, reinterpret_cast<uint32_t*>(sv + 16));
         tmem_wait_ld();
-#pragma unroll
-        for (int g = 0; g < 2; ++g) {
-          uint32_t pk[16];
-          if (masked)
-            p_cols_by_query<BF16, true>(sv + 16 * g, st + 32 * g, c2, q0 + 32 * g, qmin, pr + 16 * g, pk);
-          else
-            p_cols_by_query<BF16, false>(sv + 16 * g, st + 32 * g, c2, q0 + 32 * g, qmin, pr + 16 * g, pk);
-          tmem_st16(tS + 16 * g, pk);  // 16-bit P^T over columns this thread has already read
-        }
+        uint32_t pk[32];
+        if (masked)
+          p_frag<BF16, true>(sv, st, c2, q0, qmin, pr, pk);
+        else
+          p_frag<BF16, false>(sv, st, c2, q0, qmin, pr, pk);
+        // 16-bit P^T over the first 32 of the 64 columns this warp has just read (all its lanes)
+        tmem_st_16x128b_x8(tS, pk);
+        tmem_st_16x128b_x8(tS + HALF, pk + 16);
       }
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar(B_P));
+      KFA_PROF_END(3);
+      KFA_PROF_BEGIN();
       ok = mbar_wait_warp(bar(B_DP), s & 1, ctl, 9);
       if (!ok) break;
       tc_fence_after();
+      KFA_PROF_END(6);
+      KFA_PROF_BEGIN();
       {
         float2 dp[32];
-        tmem_ld32(tDP, reinterpret_cast<uint32_t*>(dp));
-        tmem_ld32(tDP + 32, reinterpret_cast<uint32_t*>(dp + 16));
+        tmem_ld_16x256b_x8(tDP, reinterpret_cast<uint32_t*>(dp));
+        tmem_ld_16x256b_x8(tDP + HALF, reinterpret_cast<uint32_t*>(dp + 16));
         tmem_wait_ld();
-#pragma unroll
-        for (int g = 0; g < 2; ++g) {
-          uint32_t dk[16];
-          ds_cols_by_query<BF16>(dp + 16 * g, pr + 16 * g, st + 32 * g, dk);
-          tmem_st16(tDP + 16 * g, dk);
-        }
+        uint32_t dk[32];
+        ds_frag<BF16>(dp, pr, st, dk);
+        tmem_st_16x128b_x8(tDP, dk);
+        tmem_st_16x128b_x8(tDP + HALF, dk + 16);
       }
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar(B_DS));
+      KFA_PROF_END(4);
     }
     // ---- epilogue: warps 0-3 store dV, warps 4-7 store scale * dK ----
     const bool valid = key < Skv;
@@ -810,6 +831,7 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       tc_fence_after();
       const int lim = my_limit - j * 128 - 64 * hk;  // visible columns of this warpgroup (masked tiles)
       float2 pr[32];
+      KFA_PROF_BEGIN();
       {
         float2 sv[32];
         tmem_ld32(tS, reinterpret_cast<uint32_t*>(sv));
@@ -825,9 +847,11 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             p_cols_by_key<false>(sv + 16 * g, nm, c2, nl, 32, pr + 16 * g);
         }
       }
+      KFA_PROF_END(3);
       ok = mbar_wait_warp(bar(B_DP), j & 1, ctl, 8);
       if (!ok) break;
       tc_fence_after();
+      KFA_PROF_BEGIN();
       {
         float2 dp[32];
         tmem_ld32(tDP, reinterpret_cast<uint32_t*>(dp));
@@ -843,6 +867,7 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar(B_DS));
+      KFA_PROF_END(4);
     }
     ok = mbar_wait_warp(bar(B_ACC), 0, ctl, 9) && ok;
     if (ok) {

@@ -116,7 +116,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const C
 #else
   if (mbar_try_wait(bar, parity)) return true;
 #endif
+#ifdef KFA_PROFILE
+  const long long t0 = kfa_clock();
+#else
   const long long t0 = clock64();
+#endif
   uint32_t spins = 0;
   for (;;) {
     if (mbar_try_wait(bar, parity)) {
@@ -365,6 +369,37 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
       "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
       "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
       "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+
+// Fragment shapes (16 TMEM lanes per instruction; a warp reaches its 32 lanes with lane offsets 0 and 16).
+// Register <-> element maps, checked on hardware against the 32x32b shape:
+//   ld.16x256b.x8 (16 lanes x 64 columns, 32 registers): thread l holds for column block j = 0..7
+//     r[4j], r[4j+1] = (lane l/4, columns 8j + 2(l%4), +1);  r[4j+2], r[4j+3] = (lane l/4 + 8, same columns)
+//   st.16x128b.x8 (16 lanes x 32 columns, 16 registers): r[2j] -> (lane l/4, column 4j + l%4),
+//     r[2j+1] -> (lane l/4 + 8, same column)
+// so a thread that packs the two adjacent fp32 columns it loaded into one 32-bit word of two 16-bit values
+// stores exactly the word the 16-bit MMA operand layout wants at that lane.
+__device__ __forceinline__ void tmem_ld_16x256b_x8(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x8.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+        "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+        "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+        "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_st_16x128b_x8(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.16x128b.x8.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+      "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
 
