@@ -104,6 +104,34 @@ int kfa_bwd_varlen(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v
                    const int32_t* cu_seqlens_k, int n_seqs, int max_q, int max_k, float scale, int block,
                    int dtype, int* dev_status, void* stream);
 
+/* Boolean masks. Replace the mask arguments of attention_forward / attention_backward (fwd.py:1188-1232,
+ * bwd.py:1413-1482: mask_words, mask_words_t) and the packing kernel (mask.py:32-72).
+ *
+ * A mask is passed as packed words, bit set = the key is visible: `words` hold 32 keys per 32-bit word
+ * along each query row (bit c % 32 of word c / 32 is key c), `words_t` 32 queries per word along each key
+ * row. Rows are 4 * ceil(n / 128) words long (whole 128-wide tiles) with zero bits past the end. The words
+ * of row r of (batch b, head h) start at words + b * stride_batch + h * stride_head + r * stride_row
+ * (in words; multiples of 4; a batch / head stride of 0 broadcasts one mask). A query row with no
+ * visible key gets output 0 and zero gradients (its statistics are m = +inf, log2 l = 0). The
+ * reference's per-tile classes and tile lists are not used: every key tile is visited. */
+typedef struct KfaMaskWords {
+  const int32_t* words;
+  int64_t stride_batch, stride_head, stride_row;
+} KfaMaskWords;
+
+/* mask: bytes, nonzero = visible, element (b, h, r, c) at mask[b * s[0] + h * s[1] + r * s[2] + c * s[3]]
+ * with mask_batch x mask_heads x Sq x Skv elements. words: int32[mask_batch * mask_heads * Sq *
+ * 4 ceil(Skv / 128)], words_t: int32[mask_batch * mask_heads * Skv * 4 ceil(Sq / 128)], both contiguous. */
+int kfa_pack_mask(const void* mask, const int64_t* mask_stride, int mask_batch, int mask_heads, int Sq,
+                  int Skv, int32_t* words, int32_t* words_t, void* stream);
+int kfa_fwd_masked(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* out,
+                   float* lse, const KfaMaskWords* words, float scale, int dtype, int* dev_status,
+                   void* stream);
+int kfa_bwd_masked(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* out,
+                   const KfaTensor4* dout, const float* lse, float* stats, const KfaTensor4* dq,
+                   const KfaTensor4* dk, const KfaTensor4* dv, const KfaMaskWords* words,
+                   const KfaMaskWords* words_t, float scale, int dtype, int* dev_status, void* stream);
+
 /* Backward without a scratch buffer from the caller. No counterpart in the reference (there the
  * launcher allocates its scratch from torch's caching allocator, bwd.py:1434-1439).
  *

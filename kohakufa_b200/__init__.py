@@ -5,29 +5,13 @@
     out = attention(q, k, v, causal=True)  # q [B, H, Sq, D], k / v [B, H, Skv, D]
 
     out = attention_varlen(q, k, v, cu_seqlens, cu_seqlens, causal=True)  # packed [T, H, D]
+    out = attention(q, k, v, mask=pack_mask(mask, B, H, Sq, Skv))  # boolean mask, packed once
 
-``pack_mask`` and ``PackedMask`` (the reference's other exports, ``src/kohakufa/__init__.py:12``)
-are not built: they raise ``NotImplementedError``.
+Same exports as the reference (``src/kohakufa/__init__.py:12``).
 """
 
 from kohakufa_b200.api import attention, attention_varlen, varlen_plan
-
-
-def _not_built(name):
-    def stub(*args, **kwargs):
-        raise NotImplementedError(f"kohakufa_b200.{name} is not built (only attention() is)")
-
-    stub.__name__ = name
-    return stub
-
-
-pack_mask = _not_built("pack_mask")
-
-
-class PackedMask:
-    def __init__(self, *args, **kwargs):
-        raise NotImplementedError("kohakufa_b200.PackedMask is not built (only attention() is)")
-
+from kohakufa_b200.mask import PackedMask, pack_mask
 
 __all__ = ["PackedMask", "attention", "attention_varlen", "pack_mask", "varlen_plan"]
 __version__ = "0.1.0"

@@ -28,6 +28,9 @@ SYMBOLS = (
     "kfa_bwd_static_scratch",
     "kfa_fwd_varlen",
     "kfa_bwd_varlen",
+    "kfa_pack_mask",
+    "kfa_fwd_masked",
+    "kfa_bwd_masked",
     "kfa_cp_fwd_step",
     "kfa_cp_fwd_finalize",
     "kfa_cp_bwd_dkdv_step",
@@ -42,6 +45,15 @@ class KfaTensor4(ctypes.Structure):
         ("ptr", ctypes.c_void_p),
         ("shape", ctypes.c_int64 * 4),
         ("stride", ctypes.c_int64 * 4),
+    ]
+
+
+class KfaMaskWords(ctypes.Structure):
+    _fields_ = [
+        ("words", ctypes.c_void_p),
+        ("stride_batch", ctypes.c_int64),
+        ("stride_head", ctypes.c_int64),
+        ("stride_row", ctypes.c_int64),
     ]
 
 
@@ -95,6 +107,10 @@ def load() -> ctypes.CDLL:
         lib.kfa_bwd_static_scratch.argtypes = [T, T, T, T, T, fp, T, T, T, ctypes.c_float, ctypes.c_int, ctypes.c_int, ip, vp]
         A = ctypes.POINTER(KfaAcc32)
         i64, f32, i32 = ctypes.c_int64, ctypes.c_float, ctypes.c_int
+        M = ctypes.POINTER(KfaMaskWords)
+        lib.kfa_pack_mask.argtypes = [vp, ctypes.POINTER(ctypes.c_int64), i32, i32, i32, i32, ip, ip, vp]
+        lib.kfa_fwd_masked.argtypes = [T, T, T, T, fp, M, f32, i32, ip, vp]
+        lib.kfa_bwd_masked.argtypes = [T, T, T, T, T, fp, fp, T, T, T, M, M, f32, i32, ip, vp]
         lib.kfa_fwd_varlen.argtypes = [T, T, T, T, fp, ip, ip, i32, i32, i32, f32, i32, i32, ip, vp]
         lib.kfa_bwd_varlen.argtypes = [T, T, T, T, T, fp, fp, T, T, T, ip, ip, i32, i32, i32, f32, i32, i32, ip, vp]
         lib.kfa_cp_fwd_step.argtypes = [T, T, T, A, fp, i64, i64, i32, f32, i32, i32, ip, vp]

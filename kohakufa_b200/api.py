@@ -61,7 +61,7 @@ def attention(
     causal: bool = False,
     block_causal: int = 0,
     scale: float | None = None,
-    mask: Tensor | None = None,
+    mask=None,
     compute_dtype: torch.dtype | None = None,
     center_keys: bool = False,
 ) -> Tensor:
@@ -74,7 +74,9 @@ def attention(
         block_causal: frame size ``P > 0``: query ``r`` sees keys of frames up to its own,
             ``c // P <= r // P``. ``causal`` is ``block_causal=1``.
         scale: softmax scale, ``D ** -0.5`` by default.
-        mask: boolean masks are not built; anything but ``None`` raises ``NotImplementedError``.
+        mask: bool, broadcastable to ``[B, H, Sq, Skv]``, True = visible, or a ``pack_mask(...)``
+            result to reuse one packing across calls (exclusive with ``causal`` / ``block_causal``:
+            fold them into the mask). A query row with no visible key outputs 0.
         compute_dtype: tensor-core operand dtype; inputs of another dtype (e.g. fp32) are cast.
             Defaults to the inputs' dtype if it is fp16 / bf16, else fp16.
         center_keys: subtract the mean key (over keys, per batch and head, in fp32) before the

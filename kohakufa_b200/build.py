@@ -22,6 +22,8 @@ HEADERS = [
     CSRC / "kfa_fwd.cuh",
     CSRC / "kfa_bwd.cuh",
     CSRC / "kfa_selftest.cuh",
+    CSRC / "kfa_cp.cuh",
+    CSRC / "kfa_mask.cuh",
     PKG.parent / "include" / "kfa.h",
 ]
 NVCC_FLAGS = [

@@ -119,10 +119,10 @@ int set_smem(K kernel, int bytes) {
 
 constexpr float LOG2E = 1.4426950408889634f;
 
-template <int D, bool BF16>
-int launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const kfa::FwdParams& p,
-               cudaStream_t s) {
-  auto kern = kfa::kfa_fwd_kernel<D, BF16>;
+template <int D, bool BF16, bool MASKW>
+int launch_fwd_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const kfa::FwdParams& p,
+                 cudaStream_t s) {
+  auto kern = kfa::kfa_fwd_kernel<D, BF16, MASKW>;
   int rc = set_smem(kern, kfa::FwdCfg<D>::SMEM_BYTES);
   if (rc) return rc;
   const long long grid = static_cast<long long>(p.B) * p.H * p.n_q_tiles;
@@ -133,6 +133,12 @@ int launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& 
 }
 
 template <int D, bool BF16>
+int launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const kfa::FwdParams& p,
+               cudaStream_t s) {
+  return p.mw ? launch_fwd_t<D, BF16, true>(mq, mk, mv, p, s) : launch_fwd_t<D, BF16, false>(mq, mk, mv, p, s);
+}
+
+template <int D, bool BF16>
 int launch_prepare(const kfa::PrepParams& p, cudaStream_t s) {
   dim3 grid(p.n_q128, p.B * p.H);
   kfa::kfa_bwd_prepare_kernel<D, BF16><<<grid, 128, 0, s>>>(p);
@@ -140,10 +146,10 @@ int launch_prepare(const kfa::PrepParams& p, cudaStream_t s) {
   return KFA_OK;
 }
 
-template <int D, bool BF16>
-int launch_dkdv(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mdo,
-                const kfa::BwdParams& p, cudaStream_t s) {
-  auto kern = kfa::kfa_bwd_dkdv_kernel<D, BF16>;
+template <int D, bool BF16, bool MASKW>
+int launch_dkdv_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mdo,
+                  const kfa::BwdParams& p, cudaStream_t s) {
+  auto kern = kfa::kfa_bwd_dkdv_kernel<D, BF16, MASKW>;
   int rc = set_smem(kern, kfa::BwdCfg<D>::KV_SMEM_BYTES);
   if (rc) return rc;
   const long long grid = static_cast<long long>(p.B) * p.Hkv * p.n_k128;
@@ -154,9 +160,15 @@ int launch_dkdv(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap&
 }
 
 template <int D, bool BF16>
-int launch_dq(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mdo,
-              const kfa::BwdParams& p, cudaStream_t s) {
-  auto kern = kfa::kfa_bwd_dq_kernel<D, BF16>;
+int launch_dkdv(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mdo,
+                const kfa::BwdParams& p, cudaStream_t s) {
+  return p.mwt ? launch_dkdv_t<D, BF16, true>(mq, mk, mv, mdo, p, s) : launch_dkdv_t<D, BF16, false>(mq, mk, mv, mdo, p, s);
+}
+
+template <int D, bool BF16, bool MASKW>
+int launch_dq_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mdo,
+                const kfa::BwdParams& p, cudaStream_t s) {
+  auto kern = kfa::kfa_bwd_dq_kernel<D, BF16, MASKW>;
   int rc = set_smem(kern, kfa::BwdCfg<D>::Q_SMEM_BYTES);
   if (rc) return rc;
   const long long grid = static_cast<long long>(p.B) * p.H * p.n_q128;
@@ -164,6 +176,12 @@ int launch_dq(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& m
   kern<<<static_cast<unsigned>(grid), kfa::BWD_THREADS, kfa::BwdCfg<D>::Q_SMEM_BYTES, s>>>(mq, mk, mv, mdo, p);
   KFA_CUDA(cudaGetLastError());
   return KFA_OK;
+}
+
+template <int D, bool BF16>
+int launch_dq(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mdo,
+              const kfa::BwdParams& p, cudaStream_t s) {
+  return p.mw ? launch_dq_t<D, BF16, true>(mq, mk, mv, mdo, p, s) : launch_dq_t<D, BF16, false>(mq, mk, mv, mdo, p, s);
 }
 
 #define KFA_DISPATCH(D_, dtype_, call)                     \
@@ -194,6 +212,24 @@ struct Varlen {
   int n_seqs, max_q, max_k;
 };
 
+// What a call may add to the plain problem: a packed variable-length batch, or a boolean mask.
+struct Extra {
+  const Varlen* vl = nullptr;
+  const KfaMaskWords* mw = nullptr;   // words along query rows
+  const KfaMaskWords* mwt = nullptr;  // words along key rows
+};
+
+// rows: the rows the words must cover; cols: the bits per row (padded to whole 128-wide tiles)
+int check_mask(const KfaMaskWords* m, int64_t cols, const char* name) {
+  if (!m) return KFA_OK;
+  if (!m->words || reinterpret_cast<uintptr_t>(m->words) % 16) return fail(KFA_ERR_ARG, "%s: null or unaligned words", name);
+  if (m->stride_row < 4 * ((cols + 127) / 128) || m->stride_row % 4 || m->stride_batch % 4 || m->stride_head % 4 ||
+      m->stride_batch < 0 || m->stride_head < 0)
+    return fail(KFA_ERR_ARG, "%s: strides must be multiples of 4 words, rows at least %lld words long", name,
+                (long long)(4 * ((cols + 127) / 128)));
+  return KFA_OK;
+}
+
 int check_varlen(const Varlen* vl, const KfaTensor4* q, const KfaTensor4* k) {
   if (!vl) return KFA_OK;
   if (!vl->cu_q || !vl->cu_k) return fail(KFA_ERR_ARG, "cu_seqlens: null pointer");
@@ -223,7 +259,20 @@ void fill_bwd_params(kfa::BwdParams& p, const KfaTensor4* q, const KfaTensor4* k
   p.stats_sh = static_cast<long long>(p.n_q128) * 384;
 }
 
-void apply_varlen(kfa::BwdParams& p, const Varlen* vl) {
+void apply_extra(kfa::BwdParams& p, const Extra& ex) {
+  if (ex.mw) {
+    p.mw = ex.mw->words;
+    p.mw_sb = ex.mw->stride_batch;
+    p.mw_sh = ex.mw->stride_head;
+    p.mw_row = static_cast<int>(ex.mw->stride_row);
+  }
+  if (ex.mwt) {
+    p.mwt = ex.mwt->words;
+    p.mwt_sb = ex.mwt->stride_batch;
+    p.mwt_sh = ex.mwt->stride_head;
+    p.mwt_row = static_cast<int>(ex.mwt->stride_row);
+  }
+  const Varlen* vl = ex.vl;
   if (!vl) return;
   p.B = vl->n_seqs;
   p.n_q128 = (vl->max_q + 127) / 128;
@@ -234,10 +283,13 @@ void apply_varlen(kfa::BwdParams& p, const Varlen* vl) {
 }
 
 int fwd_impl(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* out, float* lse,
-             const Varlen* vl, float scale, int block, int dtype, int* dev_status, void* stream) {
+             const Extra& ex, float scale, int block, int dtype, int* dev_status, void* stream) {
+  const Varlen* vl = ex.vl;
   int rc;
-  if ((rc = check_qkv(q, k, v, dtype, block)) || (rc = check_like(out, q, "out")) || (rc = check_varlen(vl, q, k)))
+  if ((rc = check_qkv(q, k, v, dtype, block)) || (rc = check_like(out, q, "out")) || (rc = check_varlen(vl, q, k)) ||
+      (rc = check_mask(ex.mw, k->shape[2], "mask words")))
     return rc;
+  if (ex.mw && (block != 0 || vl)) return fail(KFA_ERR_ARG, "a boolean mask excludes block-causal and packed batches");
   if (!lse || !dev_status) return fail(KFA_ERR_ARG, "lse / dev_status: null pointer");
   CUtensorMap mq, mk, mv;
   if ((rc = make_map(q, dtype, &mq, "q")) || (rc = make_map(k, dtype, &mk, "k")) || (rc = make_map(v, dtype, &mv, "v")))
@@ -263,6 +315,12 @@ int fwd_impl(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, cons
     p.n_q_tiles = (vl->max_q + 255) / 256;
     p.cu_q = vl->cu_q;
     p.cu_k = vl->cu_k;
+  }
+  if (ex.mw) {
+    p.mw = ex.mw->words;
+    p.mw_sb = ex.mw->stride_batch;
+    p.mw_sh = ex.mw->stride_head;
+    p.mw_row = static_cast<int>(ex.mw->stride_row);
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   KFA_DISPATCH(q->shape[3], dtype, (launch_fwd<KD, KB>(mq, mk, mv, p, s)));
@@ -303,12 +361,14 @@ int prepare_impl(const KfaTensor4* out, const KfaTensor4* dout, const float* lse
 }
 
 int dkdv_impl(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* dout,
-              const float* stats, const KfaTensor4* dk, const KfaTensor4* dv, const Varlen* vl, float scale, int block,
+              const float* stats, const KfaTensor4* dk, const KfaTensor4* dv, const Extra& ex, float scale, int block,
               int dtype, int* dev_status, void* stream) {
   int rc;
   if ((rc = check_qkv(q, k, v, dtype, block)) || (rc = check_like(dout, q, "dout")) ||
-      (rc = check_like(dk, k, "dk")) || (rc = check_like(dv, v, "dv")) || (rc = check_varlen(vl, q, k)))
+      (rc = check_like(dk, k, "dk")) || (rc = check_like(dv, v, "dv")) || (rc = check_varlen(ex.vl, q, k)) ||
+      (rc = check_mask(ex.mwt, q->shape[2], "transposed mask words")))
     return rc;
+  if (ex.mwt && (block != 0 || ex.vl)) return fail(KFA_ERR_ARG, "a boolean mask excludes block-causal and packed batches");
   if (!stats || !dev_status) return fail(KFA_ERR_ARG, "stats / dev_status: null pointer");
   CUtensorMap mq, mk, mv, mdo;
   if ((rc = make_map(q, dtype, &mq, "q")) || (rc = make_map(k, dtype, &mk, "k")) ||
@@ -316,7 +376,7 @@ int dkdv_impl(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, con
     return rc;
   kfa::BwdParams p;
   fill_bwd_params(p, q, k, stats, scale, block, dev_status);
-  apply_varlen(p, vl);
+  apply_extra(p, ex);
   p.dk = dk->ptr;
   p.dk_sb = dk->stride[0];
   p.dk_sh = dk->stride[1];
@@ -330,11 +390,13 @@ int dkdv_impl(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, con
 }
 
 int dq_impl(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* dout, const float* stats,
-            const KfaTensor4* dq, const Varlen* vl, float scale, int block, int dtype, int* dev_status, void* stream) {
+            const KfaTensor4* dq, const Extra& ex, float scale, int block, int dtype, int* dev_status, void* stream) {
   int rc;
   if ((rc = check_qkv(q, k, v, dtype, block)) || (rc = check_like(dout, q, "dout")) ||
-      (rc = check_like(dq, q, "dq")) || (rc = check_varlen(vl, q, k)))
+      (rc = check_like(dq, q, "dq")) || (rc = check_varlen(ex.vl, q, k)) ||
+      (rc = check_mask(ex.mw, k->shape[2], "mask words")))
     return rc;
+  if (ex.mw && (block != 0 || ex.vl)) return fail(KFA_ERR_ARG, "a boolean mask excludes block-causal and packed batches");
   if (!stats || !dev_status) return fail(KFA_ERR_ARG, "stats / dev_status: null pointer");
   CUtensorMap mq, mk, mv, mdo;
   if ((rc = make_map(q, dtype, &mq, "q")) || (rc = make_map(k, dtype, &mk, "k")) ||
@@ -342,7 +404,7 @@ int dq_impl(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const
     return rc;
   kfa::BwdParams p;
   fill_bwd_params(p, q, k, stats, scale, block, dev_status);
-  apply_varlen(p, vl);
+  apply_extra(p, ex);
   p.dq = dq->ptr;
   p.dq_sb = dq->stride[0];
   p.dq_sh = dq->stride[1];
@@ -365,7 +427,7 @@ int64_t kfa_bwd_stats_bytes(int64_t B, int64_t H, int64_t Sq) {
 
 int kfa_fwd(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* out, float* lse,
             float scale, int block, int dtype, int* dev_status, void* stream) {
-  return fwd_impl(q, k, v, out, lse, nullptr, scale, block, dtype, dev_status, stream);
+  return fwd_impl(q, k, v, out, lse, Extra{}, scale, block, dtype, dev_status, stream);
 }
 
 int kfa_bwd_prepare(const KfaTensor4* out, const KfaTensor4* dout, const float* lse, float* stats, int dtype,
@@ -376,20 +438,45 @@ int kfa_bwd_prepare(const KfaTensor4* out, const KfaTensor4* dout, const float* 
 int kfa_bwd_dkdv(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* dout,
                  const float* stats, const KfaTensor4* dk, const KfaTensor4* dv, float scale, int block, int dtype,
                  int* dev_status, void* stream) {
-  return dkdv_impl(q, k, v, dout, stats, dk, dv, nullptr, scale, block, dtype, dev_status, stream);
+  return dkdv_impl(q, k, v, dout, stats, dk, dv, Extra{}, scale, block, dtype, dev_status, stream);
 }
 
 int kfa_bwd_dq(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* dout,
                const float* stats, const KfaTensor4* dq, float scale, int block, int dtype, int* dev_status,
                void* stream) {
-  return dq_impl(q, k, v, dout, stats, dq, nullptr, scale, block, dtype, dev_status, stream);
+  return dq_impl(q, k, v, dout, stats, dq, Extra{}, scale, block, dtype, dev_status, stream);
 }
 
 int kfa_fwd_varlen(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* out, float* lse,
                    const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, int n_seqs, int max_q, int max_k,
                    float scale, int block, int dtype, int* dev_status, void* stream) {
   const Varlen vl{cu_seqlens_q, cu_seqlens_k, n_seqs, max_q, max_k};
-  return fwd_impl(q, k, v, out, lse, &vl, scale, block, dtype, dev_status, stream);
+  Extra ex;
+  ex.vl = &vl;
+  return fwd_impl(q, k, v, out, lse, ex, scale, block, dtype, dev_status, stream);
+}
+
+int kfa_fwd_masked(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* out, float* lse,
+                   const KfaMaskWords* words, float scale, int dtype, int* dev_status, void* stream) {
+  if (!words) return fail(KFA_ERR_ARG, "kfa_fwd_masked: null mask");
+  Extra ex;
+  ex.mw = words;
+  return fwd_impl(q, k, v, out, lse, ex, scale, 0, dtype, dev_status, stream);
+}
+
+int kfa_bwd_masked(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* out,
+                   const KfaTensor4* dout, const float* lse, float* stats, const KfaTensor4* dq, const KfaTensor4* dk,
+                   const KfaTensor4* dv, const KfaMaskWords* words, const KfaMaskWords* words_t, float scale, int dtype,
+                   int* dev_status, void* stream) {
+  if (!words || !words_t) return fail(KFA_ERR_ARG, "kfa_bwd_masked: null mask");
+  Extra ex;
+  ex.mw = words;
+  ex.mwt = words_t;
+  int rc;
+  if ((rc = check_like(out, q, "out"))) return rc;
+  if ((rc = prepare_impl(out, dout, lse, stats, nullptr, dtype, stream))) return rc;
+  if ((rc = dkdv_impl(q, k, v, dout, stats, dk, dv, ex, scale, 0, dtype, dev_status, stream))) return rc;
+  return dq_impl(q, k, v, dout, stats, dq, ex, scale, 0, dtype, dev_status, stream);
 }
 
 int kfa_bwd_varlen(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* out,
@@ -400,8 +487,10 @@ int kfa_bwd_varlen(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v
   int rc;
   if ((rc = check_like(out, q, "out"))) return rc;
   if ((rc = prepare_impl(out, dout, lse, stats, &vl, dtype, stream))) return rc;
-  if ((rc = dkdv_impl(q, k, v, dout, stats, dk, dv, &vl, scale, block, dtype, dev_status, stream))) return rc;
-  return dq_impl(q, k, v, dout, stats, dq, &vl, scale, block, dtype, dev_status, stream);
+  Extra ex;
+  ex.vl = &vl;
+  if ((rc = dkdv_impl(q, k, v, dout, stats, dk, dv, ex, scale, block, dtype, dev_status, stream))) return rc;
+  return dq_impl(q, k, v, dout, stats, dq, ex, scale, block, dtype, dev_status, stream);
 }
 
 int kfa_bwd(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* out,
@@ -468,6 +557,7 @@ extern "C" int kfa_bwd_static_scratch(const KfaTensor4* q, const KfaTensor4* k, 
 }
 
 #include "kfa_cp.cuh"
+#include "kfa_mask.cuh"
 #include "kfa_selftest.cuh"
 
 #ifdef KFA_PROFILE

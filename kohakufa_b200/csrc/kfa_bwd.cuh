@@ -69,6 +69,16 @@ struct BwdParams {
   // statistics, whose tiles are numbered from each sequence's first row).
   const int* cu_q;
   const int* cu_k;
+  // Boolean mask (kernels instantiated with MASKW), bit set = visible. mw: 32 keys per word along query
+  // rows (row r of (b, h) at mw + b * mw_sb + h * mw_sh + r * mw_row), read by the dQ kernel; mwt: 32
+  // queries per word along key rows, read by the dK / dV kernel. Strides of 0 broadcast; four words per
+  // 128-wide tile; zero bits past the ends.
+  const int* mw;
+  long long mw_sb, mw_sh;
+  int mw_row;
+  const int* mwt;
+  long long mwt_sb, mwt_sh;
+  int mwt_row;
 };
 
 struct PrepParams {
@@ -265,6 +275,26 @@ __device__ __forceinline__ void p_frag(const float2* sv, const float* st, float2
     }
   }
 }
+// The same under a boolean mask: w[e] holds the two words (64 queries of this warpgroup) of key row e;
+// a pair whose bit is clear gets P = 0. col0 = this thread's first column inside every block of 8.
+template <bool BF16>
+__device__ __forceinline__ void p_frag_bits(const float2* sv, const float* st, float2 c2, const uint2* w, int col0,
+                                            float2* pr, uint32_t* pk) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float2 nm = *reinterpret_cast<const float2*>(st + 8 * j);
+    const float2 nl = *reinterpret_cast<const float2*>(st + 128 + 8 * j);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int idx = 16 * (e >> 1) + 2 * j + (e & 1);
+      const float2 x = __ffma2_rn(__fadd2_rn(sv[idx], nm), c2, nl);
+      const uint32_t bits = ((j < 4) ? w[e].x : w[e].y) >> (8 * (j & 3) + col0);
+      const float2 pv = make_float2((bits & 1u) ? ex2(x.x) : 0.f, (bits & 2u) ? ex2(x.y) : 0.f);
+      pr[idx] = pv;
+      pk[idx] = pack16<BF16>(pv.x, pv.y);
+    }
+  }
+}
 // dS = (dP - delta) * P of the same elements, rounded once to 16 bits, unscaled.
 template <bool BF16>
 __device__ __forceinline__ void ds_frag(const float2* dp, const float2* pr, const float* st, uint32_t* dk) {
@@ -295,6 +325,15 @@ __device__ __forceinline__ void p_cols_by_key(const float2* sv, float2 nm, float
     pr[x] = q;
   }
 }
+// Under a boolean mask: bit x of `word` is the key of column x (32 columns).
+__device__ __forceinline__ void p_cols_by_key_bits(const float2* sv, float2 nm, float2 c2, float2 nl, uint32_t word,
+                                                   float2* pr) {
+#pragma unroll
+  for (int x = 0; x < 16; ++x) {
+    const float2 e = __ffma2_rn(__fadd2_rn(sv[x], nm), c2, nl);
+    pr[x] = make_float2(((word >> (2 * x)) & 1u) ? ex2(e.x) : 0.f, ((word >> (2 * x + 1)) & 1u) ? ex2(e.y) : 0.f);
+  }
+}
 template <bool BF16>
 __device__ __forceinline__ void ds_cols_by_key(const float2* dp, const float2* pr, float2 nd, uint32_t* dk) {
 #pragma unroll
@@ -307,7 +346,7 @@ __device__ __forceinline__ void ds_cols_by_key(const float2* dp, const float2* p
 // ---------------------------------------------------------------------------------------
 // dK / dV
 // ---------------------------------------------------------------------------------------
-template <int D, bool BF16>
+template <int D, bool BF16, bool MASKW>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
@@ -514,8 +553,35 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
     const float2 c2 = make_float2(p.c, p.c);
     bool ok = true;
+    // boolean mask: for each of the thread's 4 key rows the two words of this warpgroup's 64 queries,
+    // fetched a step ahead (rows past Skv read as hidden)
+    const int* mkey[4] = {nullptr, nullptr, nullptr, nullptr};
+    uint2 wnext[4];
+    auto mask_fetch = [&](int s) {
+      const int i = first_i + s % n_per;
+      const int head = hk * p.group + s / n_per;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        wnext[e] = make_uint2(0u, 0u);
+        if (mkey[e] != nullptr) wnext[e] = __ldg(reinterpret_cast<const uint2*>(mkey[e] + head * p.mwt_sh + 4 * i + 2 * hq));
+      }
+    };
+    if constexpr (MASKW) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int kr = kv0 + (warp & 3) * 32 + 16 * (e >> 1) + (lane >> 2) + 8 * (e & 1);
+        if (kr < Skv) mkey[e] = p.mwt + bc * p.mwt_sb + static_cast<long long>(kr) * p.mwt_row;
+      }
+      if (n_steps > 0) mask_fetch(0);
+    }
     for (int s = 0; s < n_steps; ++s) {
       KFA_PROF_BEGIN();
+      uint2 wcur[4];
+      if constexpr (MASKW) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) wcur[e] = wnext[e];
+        if (s + 1 < n_steps) mask_fetch(s + 1);
+      }
       const int slot = s % NSL;
       const int i = first_i + s % n_per;
       const int q0 = i * 128 + 64 * hq + col0;  // query of this thread's first column
@@ -537,7 +603,9 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tmem_ld_16x256b_x8(tS + HALF, reinterpret_cast<uint32_t*>(sv + 16));
         tmem_wait_ld();
         uint32_t pk[32];
-        if (masked)
+        if constexpr (MASKW)
+          p_frag_bits<BF16>(sv, st, c2, wcur, col0, pr, pk);
+        else if (masked)
           p_frag<BF16, true>(sv, st, c2, q0, qmin, pr, pk);
         else
           p_frag<BF16, false>(sv, st, c2, q0, qmin, pr, pk);
@@ -617,7 +685,7 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 // ---------------------------------------------------------------------------------------
 // dQ
 // ---------------------------------------------------------------------------------------
-template <int D, bool BF16>
+template <int D, bool BF16, bool MASKW>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
@@ -825,7 +893,19 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     const int my_limit = key_limit(min(row, Sq - 1), p.P, Skv);
     const float2 c2 = make_float2(p.c, p.c);
     bool ok = true;
+    // boolean mask: the two words of this row for the warpgroup's 64 keys of a tile, fetched a tile ahead
+    const uint2* mrow = nullptr;
+    uint2 mnext = make_uint2(0u, 0u);
+    if constexpr (MASKW) {
+      mrow = reinterpret_cast<const uint2*>(p.mw + bc * p.mw_sb + h * p.mw_sh +
+                                            static_cast<long long>(min(row, Sq - 1)) * p.mw_row + 2 * hk);
+      if (n_steps > 0) mnext = __ldg(mrow);
+    }
     for (int j = 0; j < n_steps; ++j) {
+      const uint2 mcur = mnext;
+      if constexpr (MASKW) {
+        if (j + 1 < n_steps) mnext = __ldg(mrow + 2 * (j + 1));
+      }
       ok = mbar_wait_warp(bar(B_S), j & 1, ctl, 7);
       if (!ok) break;
       tc_fence_after();
@@ -841,7 +921,9 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         mbar_arrive(bar(B_SREAD));  // S(j) is in registers: the tensor core may write S(j+1)
 #pragma unroll
         for (int g = 0; g < 2; ++g) {
-          if (j >= n_unmasked)
+          if constexpr (MASKW)
+            p_cols_by_key_bits(sv + 16 * g, nm, c2, nl, g ? mcur.y : mcur.x, pr + 16 * g);
+          else if (j >= n_unmasked)
             p_cols_by_key<true>(sv + 16 * g, nm, c2, nl, lim - 32 * g, pr + 16 * g);
           else
             p_cols_by_key<false>(sv + 16 * g, nm, c2, nl, 32, pr + 16 * g);

@@ -49,6 +49,12 @@ struct FwdParams {
   // the tiles of the longest sequence; CTAs past the end of a shorter one return at once.
   const int* cu_q;
   const int* cu_k;
+  // Boolean mask (kernels instantiated with MASKW): 32 keys per word, bit set = visible; the words of
+  // query row r of (b, h) start at mw + b * mw_sb + h * mw_sh + r * mw_row (a stride of 0 broadcasts),
+  // four words per 128-key tile, zero bits for keys past Skv.
+  const int* mw;
+  long long mw_sb, mw_sh;
+  int mw_row;
 };
 
 constexpr int FWD_THREADS = 320;
@@ -76,7 +82,7 @@ __device__ __forceinline__ int key_limit(int r, int P, int Skv) {
   return lim < Skv ? static_cast<int>(lim) : Skv;
 }
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool MASKW>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
@@ -332,7 +338,21 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     float m = -INFINITY;
     float l = 0.f;
     bool ok = true;
+    // boolean mask: this row's words, one 16-byte load per key tile, fetched a tile ahead
+    const uint4* mrow = nullptr;
+    uint4 mnext = make_uint4(0u, 0u, 0u, 0u);
+    if constexpr (MASKW) {
+      mrow = reinterpret_cast<const uint4*>(p.mw + bc * p.mw_sb + h * p.mw_sh +
+                                            static_cast<long long>(min(row, Sq - 1)) * p.mw_row);
+      if (nt > 0) mnext = __ldg(mrow);
+    }
     for (int j = 0; j < nt; ++j) {
+      uint32_t mbits[4] = {mnext.x, mnext.y, mnext.z, mnext.w};
+      bool apply_bits = false;
+      if constexpr (MASKW) {
+        if (j + 1 < nt) mnext = __ldg(mrow + j + 1);
+        apply_bits = !__all_sync(0xffffffffu, (mbits[0] & mbits[1] & mbits[2] & mbits[3]) == 0xffffffffu);
+      }
       ok = mbar_wait_warp(bar(B_SREADY + hf), j & 1, ctl, 5);
       if (!ok) break;
       tc_fence_after();
@@ -347,7 +367,13 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       tmem_ld32(tS + 64, reinterpret_cast<uint32_t*>(s + 64));
       tmem_ld32(tS + 96, reinterpret_cast<uint32_t*>(s + 96));
       tmem_wait_ld();
-      if (masked) {
+      if constexpr (MASKW) {
+        if (apply_bits) {
+#pragma unroll
+          for (int i = 0; i < 128; ++i)
+            if (!((mbits[i >> 5] >> (i & 31)) & 1u)) s[i] = -INFINITY;
+        }
+      } else if (masked) {
 #pragma unroll
         for (int i = 0; i < 128; ++i)
           if (i >= lim) s[i] = -INFINITY;
@@ -361,8 +387,10 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         mx3 = fmaxf(mx3, fmaxf(s[i + 6], s[i + 7]));
       }
       const float m_new = fmaxf(fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)), m);
+      // A row that has seen no key yet (boolean masks only) shifts by 0: its exponents stay -inf, P = 0.
+      const float m_shift = (MASKW && m_new == -INFINITY) ? 0.f : m_new;
       // Shift first, then scale: the largest exponent of the row is exactly 0.
-      const float alpha = ex2(__fmul_rn(__fsub_rn(m, m_new), c));
+      const float alpha = ex2(__fmul_rn(__fsub_rn(m, m_shift), c));
       m = m_new;
       KFA_PROF_END(7);
       // ---- exact rescale of O whenever any row of this warp moved its max. S_h(j) being ready
@@ -390,12 +418,18 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       tmem_wait_ld();
       KFA_PROF_END(9);
       KFA_PROF_BEGIN();
-      if (masked) {
+      if constexpr (MASKW) {
+        if (apply_bits) {
+#pragma unroll
+          for (int i = 0; i < 128; ++i)
+            if (!((mbits[i >> 5] >> (i & 31)) & 1u)) s[i] = -INFINITY;
+        }
+      } else if (masked) {
 #pragma unroll
         for (int i = 0; i < 128; ++i)
           if (i >= lim) s[i] = -INFINITY;
       }
-      const float2 neg_m = make_float2(-m_new, -m_new);
+      const float2 neg_m = make_float2(-m_shift, -m_shift);
       const float2 c2 = make_float2(c, c);
       float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
       const float2* s2 = reinterpret_cast<const float2*>(s);
@@ -472,7 +506,13 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
     } else if (ok && nt > 0) {
       tc_fence_after();
-      const float inv = 1.0f / l;
+      float inv = 1.0f / l;
+      float log2_l = log2f(l);
+      if (MASKW && l == 0.f) {  // a row with no visible key: output 0, m = +inf, so every P of its backward is 0
+        inv = 0.f;
+        m = INFINITY;
+        log2_l = 0.f;
+      }
       const bool valid = row < Sq;
       uint8_t* orow = reinterpret_cast<uint8_t*>(p.o) +
                       2 * (bc * p.o_sb + h * p.o_sh + static_cast<long long>(q_base + row) * p.o_ss);
@@ -496,7 +536,7 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       if (valid) {
         float* lse = p.lse + (static_cast<long long>(bc) * p.H + h) * 2 * p.Sq + q_base;
         lse[row] = m;
-        lse[p.Sq + row] = log2f(l);
+        lse[p.Sq + row] = log2_l;
       }
     }
   }

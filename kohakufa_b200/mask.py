@@ -1,0 +1,75 @@
+"""Boolean attention masks packed for the kernels: 32 keys per int32 word along each query row (read by
+the forward and the dQ kernel) and 32 queries per word along each key row (read by the dK / dV kernel),
+padded with zero bits to whole 128-wide tiles.
+
+Same interface and word format as the reference's ``PackedMask`` / ``pack_mask`` (KohakuFA
+``src/kohakufa/mask.py:13-128``); the packing is one CUDA kernel of ``libkfa.so`` (``kfa_pack_mask``)
+instead of a Triton kernel, and the reference's tile classes / tile lists are not built (the kernels
+visit every key tile and skip the masking code where a warp's bits are all set).
+"""
+
+import ctypes
+
+import torch
+from torch import Tensor
+
+from kohakufa_b200 import _lib
+
+TILE = 128
+
+
+def normalize(mask: Tensor, batch: int, heads: int, s_q: int, s_kv: int) -> Tensor:
+    """A bool mask broadcastable to ``[B, H, Sq, Skv]`` (True = visible) as 4D with batch / head
+    dimensions of size 1 or B / H (reference mask.py:13-29: same exceptions)."""
+    if mask.dtype != torch.bool:
+        raise TypeError("mask: a boolean tensor (True = the key is visible)")
+    while mask.dim() < 4:
+        mask = mask.unsqueeze(0)
+    if mask.shape[-2:] != (s_q, s_kv) or mask.shape[0] not in (1, batch) or mask.shape[1] not in (1, heads):
+        raise ValueError(f"mask {tuple(mask.shape)} does not broadcast to {(batch, heads, s_q, s_kv)}")
+    return mask
+
+
+def words_per_row(n: int) -> int:
+    """int32 words of a row of ``n`` bits, padded to whole 128-bit tiles."""
+    return 4 * (-(-n // TILE))
+
+
+class PackedMask:
+    """A boolean mask packed once for the kernels (words and transposed words), reusable across calls
+    with the same mask and shape (e.g. every layer of a model)."""
+
+    def __init__(self, mask: Tensor, batch: int, heads: int, s_q: int, s_kv: int) -> None:
+        dense = normalize(mask, batch, heads, s_q, s_kv)
+        if not dense.is_cuda:
+            raise ValueError("mask: a CUDA tensor (there is no CPU path)")
+        self.shape = (batch, heads, s_q, s_kv)
+        bm, hm = dense.shape[:2]
+        self.words = torch.empty(bm, hm, s_q, words_per_row(s_kv), dtype=torch.int32, device=dense.device)
+        self.words_t = torch.empty(bm, hm, s_kv, words_per_row(s_q), dtype=torch.int32, device=dense.device)
+        lib = _lib.load()
+        bytes_ = dense.view(torch.uint8)
+        strides = (ctypes.c_int64 * 4)(*bytes_.stride())
+        with torch.cuda.device(dense.device):
+            rc = lib.kfa_pack_mask(
+                bytes_.data_ptr(), strides, bm, hm, s_q, s_kv, self.words.data_ptr(), self.words_t.data_ptr(),
+                _lib.stream_ptr(dense.device),
+            )  # fmt: skip
+        _lib.check(rc)
+
+
+def pack_mask(mask: Tensor, batch: int, heads: int, s_q: int, s_kv: int) -> PackedMask:
+    """Pack ``mask`` (bool, broadcastable to ``[B, H, Sq, Skv]``, True = visible) once; pass the result
+    as ``attention(..., mask=packed)``."""
+    return PackedMask(mask, batch, heads, s_q, s_kv)
+
+
+def mask_words(words: Tensor, batch: int, heads: int) -> "_lib.KfaMaskWords":
+    """The library's descriptor of ``words [Bm, Hm, rows, row_words]`` (size-1 dimensions broadcast)."""
+    assert words.dtype == torch.int32 and words.dim() == 4 and words.stride(3) == 1
+    d = _lib.KfaMaskWords()
+    d.words = words.data_ptr()
+    d.stride_batch = words.stride(0) if words.shape[0] > 1 else 0
+    d.stride_head = words.stride(1) if words.shape[1] > 1 else 0
+    d.stride_row = words.stride(2)
+    return d

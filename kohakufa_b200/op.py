@@ -147,22 +147,118 @@ def _backward(ctx, dout, dlse):
 attention_fwd_op.register_autograd(_backward, setup_context=_setup_context)
 
 
+# --------------------------------------------------------------------------------------
+# Boolean masks: ops of their own (the reference passes optional word tensors to its one op pair,
+# op.py:58-121); the packed words are saved for the backward.
+# --------------------------------------------------------------------------------------
+
+
+@torch.library.custom_op("kohakufa_b200::sm100_masked_forward", mutates_args=(), device_types="cuda")
+def masked_fwd_op(q: Tensor, k: Tensor, v: Tensor, words: Tensor, words_t: Tensor, scale: float) -> tuple[Tensor, Tensor]:
+    from kohakufa_b200.mask import mask_words
+
+    lib = _lib.load()
+    batch, heads, seq_q, _ = q.shape
+    out = _bshd_like(q)
+    lse = q.new_empty(batch, heads, 2, seq_q, dtype=torch.float32)
+    with torch.cuda.device(q.device):
+        rc = lib.kfa_fwd_masked(
+            *(ctypes.byref(_lib.tensor4(t)) for t in (q, k, v, out)),
+            lse.data_ptr(),
+            ctypes.byref(mask_words(words, batch, heads)),
+            float(scale),
+            _lib.dtype_code(q.dtype),
+            _lib.status_word(q.device).data_ptr(),
+            _lib.stream_ptr(q.device),
+        )
+    _lib.check(rc)
+    return out, lse
+
+
+@masked_fwd_op.register_fake
+def _(q, k, v, words, words_t, scale):
+    batch, heads, seq_q, dim = q.shape
+    return q.new_empty(batch, seq_q, heads, dim).transpose(1, 2), q.new_empty(batch, heads, 2, seq_q, dtype=torch.float32)
+
+
+@torch.library.custom_op("kohakufa_b200::sm100_masked_backward", mutates_args=(), device_types="cuda")
+def masked_bwd_op(
+    q: Tensor, k: Tensor, v: Tensor, out: Tensor, dout: Tensor, lse: Tensor, words: Tensor, words_t: Tensor,
+    scale: float,
+) -> tuple[Tensor, Tensor, Tensor]:  # fmt: skip
+    from kohakufa_b200.mask import mask_words
+
+    lib = _lib.load()
+    batch, heads, seq_q, _ = q.shape
+    dq, dk, dv = _bshd_like(q), _bshd_like(k), _bshd_like(v)
+    stats = q.new_empty(lib.kfa_bwd_stats_bytes(batch, heads, seq_q) // 4, dtype=torch.float32)
+    with torch.cuda.device(q.device):
+        rc = lib.kfa_bwd_masked(
+            *(ctypes.byref(_lib.tensor4(t)) for t in (q, k, v, out, dout)),
+            lse.data_ptr(),
+            stats.data_ptr(),
+            *(ctypes.byref(_lib.tensor4(t)) for t in (dq, dk, dv)),
+            ctypes.byref(mask_words(words, batch, heads)),
+            ctypes.byref(mask_words(words_t, batch, heads)),
+            float(scale),
+            _lib.dtype_code(q.dtype),
+            _lib.status_word(q.device).data_ptr(),
+            _lib.stream_ptr(q.device),
+        )
+    _lib.check(rc)
+    return dq, dk, dv
+
+
+@masked_bwd_op.register_fake
+def _(q, k, v, out, dout, lse, words, words_t, scale):
+    return _bshd_like(q), _bshd_like(k), _bshd_like(v)
+
+
+def _masked_setup(ctx, inputs, output):
+    q, k, v, words, words_t, scale = inputs
+    out, lse = output
+    ctx.save_for_backward(q, k, v, out, lse, words, words_t)
+    ctx.scale = scale
+    ctx.mark_non_differentiable(lse)
+
+
+def _masked_backward(ctx, dout, dlse):
+    q, k, v, out, lse, words, words_t = ctx.saved_tensors
+    if not _strides_ok(dout):
+        dout = dout.contiguous()
+    dq, dk, dv = masked_bwd_op(q, k, v, out, dout, lse, words, words_t, ctx.scale)
+    return dq, dk, dv, None, None, None
+
+
+masked_fwd_op.register_autograd(_masked_backward, setup_context=_masked_setup)
+
+
 def attention(
     q: Tensor,
     k: Tensor,
     v: Tensor,
     scale: float | None = None,
     block_causal: int = 0,
-    mask: Tensor | None = None,
+    mask=None,
 ) -> Tensor:
     """``softmax(scale q k^T) v`` over ``[B, H, S, D]``; ``block_causal > 0``: tokens of block ``i``
-    (``block_causal`` consecutive tokens) see blocks ``0..i`` only. ``mask`` (a boolean mask in the
-    reference, op.py:146-175) is not built."""
-    if mask is not None:
-        raise NotImplementedError("attention: boolean masks are not built yet")
+    (``block_causal`` consecutive tokens) see blocks ``0..i`` only; ``mask``: a bool mask broadcastable
+    to ``[B, H, Sq, Skv]`` (True = visible; a row with no visible key outputs 0) or a ``PackedMask``
+    (reference: op.py:146-175)."""
+    from kohakufa_b200.mask import PackedMask
+
     _check(q, k, v)
     if scale is None:
         scale = q.shape[-1] ** -0.5
+    if mask is not None:
+        if block_causal:
+            raise ValueError("attention: give a mask or block_causal, not both (fold it in)")
+        shape = (q.shape[0], q.shape[1], q.shape[2], k.shape[2])
+        packed = mask if isinstance(mask, PackedMask) else PackedMask(mask, *shape)
+        if packed.shape != shape:
+            raise ValueError(f"packed mask for {packed.shape}, inputs are {shape}")
+        out, _ = masked_fwd_op(q, k, v, packed.words, packed.words_t, float(scale))
+        return out
     out, _ = attention_fwd_op(q, k, v, float(scale), int(block_causal))
     return out
 

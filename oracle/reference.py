@@ -36,19 +36,30 @@ def visible(s_q: int, s_kv: int, block: int, device="cpu"):
     return cols <= rows
 
 
-def attention_fp64(q, k, v, dout, scale, block=0):
+def attention_fp64(q, k, v, dout, scale, block=0, mask=None, groups=1):
     """out, dq, dk, dv in fp64 from the given (already rounded) inputs ``[B, H, S, D]``.
 
     Forward: S = scale q k^T, hidden entries -inf, P = softmax(S), out = P v.
     Backward, written out: dV = P^T dO; dP = dO v^T; delta = rowsum(dO * out);
     dS = P * (dP - delta); dQ = scale dS k; dK = scale dS^T q.
-    Every query row sees key 0 under this mask family, so no row is empty."""
+    ``mask`` (instead of ``block``): bool, broadcastable to the scores, True = visible; a query row
+    with no visible key has P = 0: output 0 and no gradient (KohakuFA tests/reference.py:27-31).
+    ``groups`` > 1: grouped-query attention, each K / V head serves ``groups`` consecutive query heads
+    and its dK / dV sum over them (tests/reference.py:22-24)."""
     q, k, v, dout = (t.detach().to(torch.float64) for t in (q, k, v, dout))
+    kv_heads = k.shape[1]
+    if groups > 1:
+        k, v = (t.repeat_interleave(groups, dim=1) for t in (k, v))
     s = torch.matmul(q, k.transpose(-1, -2)) * scale
-    mask = visible(q.shape[-2], k.shape[-2], block, q.device)
+    if mask is None:
+        mask = visible(q.shape[-2], k.shape[-2], block, q.device)
     if mask is not None:
-        s = s.masked_fill(~mask, float("-inf"))
-    p = torch.softmax(s, dim=-1)
+        mask = mask.expand_as(s)
+        rows = mask.any(-1, keepdim=True)
+        s = torch.where(rows, s.masked_fill(~mask, float("-inf")), torch.zeros_like(s))
+        p = torch.softmax(s, dim=-1) * rows
+    else:
+        p = torch.softmax(s, dim=-1)
     out = torch.matmul(p, v)
     dv = torch.matmul(p.transpose(-1, -2), dout)
     dp = torch.matmul(dout, v.transpose(-1, -2))
@@ -56,6 +67,9 @@ def attention_fp64(q, k, v, dout, scale, block=0):
     ds = p * (dp - delta)
     dq = torch.matmul(ds, k) * scale
     dk = torch.matmul(ds.transpose(-1, -2), q) * scale
+    if groups > 1:
+        shape = (k.shape[0], kv_heads, groups, k.shape[2], k.shape[3])
+        dk, dv = dk.reshape(shape).sum(2), dv.reshape(shape).sum(2)
     return out, dq, dk, dv
 
 

@@ -29,6 +29,37 @@ ATTENTION_CASES = {
     "block24_bf16": (1, 1, 61, 61, 128, "bfloat16", 24, 16, 0.5),
     "dense_cross_bf16": (1, 1, 19, 45, 128, "bfloat16", 0, 17, 1.0),
 }
+# Boolean masks and grouped-query attention: name -> (B, H, Hkv, Sq, Skv, D, dtype, seed, mask kind)
+MASK_CASES = {
+    "mask_random_f16": (2, 2, 2, 37, 45, 64, "float16", 31, "random"),
+    "mask_broadcast_empty_rows_f16": (2, 3, 3, 40, 40, 32, "float16", 32, "empty_rows"),
+    "mask_key_padding_bf16": (2, 2, 2, 30, 50, 64, "bfloat16", 33, "key_padding"),
+    "gqa_causal_f16": (1, 4, 2, 33, 33, 64, "float16", 34, "causal_block"),
+    "mask_gqa_bf16": (1, 4, 1, 29, 41, 64, "bfloat16", 35, "random"),
+}
+
+
+def make_mask_inputs(case):
+    """q, k, v, dout, mask (None for the block-causal GQA case), block."""
+    b, h, hkv, sq, skv, d, dtype, seed, kind = case
+    gen = torch.Generator().manual_seed(seed)
+    dt = getattr(torch, dtype)
+    q = torch.randn(b, h, sq, d, generator=gen).to(dt)
+    k = torch.randn(b, hkv, skv, d, generator=gen).to(dt)
+    v = torch.randn(b, hkv, skv, d, generator=gen).to(dt)
+    dout = torch.randn(b, h, sq, d, generator=gen).to(dt)
+    if kind == "random":
+        return q, k, v, dout, torch.rand(b, h, sq, skv, generator=gen) < 0.4, 0
+    if kind == "empty_rows":  # one mask for every batch and head, rows 5..9 see nothing
+        mask = torch.rand(1, 1, sq, skv, generator=gen) < 0.5
+        mask[:, :, 5:10] = False
+        return q, k, v, dout, mask, 0
+    if kind == "key_padding":  # [B, 1, 1, Skv]: per-batch key lengths
+        lengths = torch.tensor([skv, skv // 3])
+        return q, k, v, dout, (torch.arange(skv)[None, :] < lengths[:, None])[:, None, None, :], 0
+    return q, k, v, dout, None, 1
+
+
 # name -> (B, H, S, D, dtype, seed, magnitude of q and k)
 FLOOR_CASES = {
     "floor_f16": (1, 1, 40, 64, "float16", 21, 1.0),
@@ -82,6 +113,11 @@ def main(ref_root: str) -> None:
         noisy = o + 1e-3 * torch.randn(o.shape, generator=torch.Generator().manual_seed(5), dtype=torch.float64)
         m = ref.metrics(noisy, o)
         out[f"{name}/metrics"] = np.array([m["cos"], m["norm_ratio"], m["rel_err"], m["max_abs_err"], m["max_rel_err"]])
+    for name, case in MASK_CASES.items():
+        q, k, v, dout, mask, block = make_mask_inputs(case)
+        o, dq, dk, dv = ref.reference(q, k, v, dout, case[5] ** -0.5, block=block, groups=case[1] // case[2], mask=mask)
+        for key, val in zip(("out", "dq", "dk", "dv"), (o, dq, dk, dv)):
+            out[f"{name}/{key}"] = val.numpy()
     np.savez_compressed(HERE / "attention_fp64.npz", **out)
 
     sys.path.insert(0, str(root / "benchmarks"))

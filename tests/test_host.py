@@ -74,7 +74,7 @@ def test_mask_with_block_rejected_first():
     q, k, v = qkv()
     with pytest.raises(ValueError, match="mask or causal"):
         api.attention(q, k, v, causal=True, mask=torch.ones(16, 16, dtype=torch.bool))
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(ValueError, match="CUDA tensors only"):  # masks are built; CPU tensors are not
         api.attention(q, k, v, mask=torch.ones(16, 16, dtype=torch.bool))
 
 
@@ -121,9 +121,21 @@ def test_center_keys_is_a_pure_shift():
 
 def test_other_exports_raise():
     assert set(kohakufa_b200.__all__) == {"PackedMask", "attention", "attention_varlen", "pack_mask", "varlen_plan"}
-    for name in ("pack_mask", "PackedMask"):
-        with pytest.raises(NotImplementedError):
-            getattr(kohakufa_b200, name)()
+
+
+def test_mask_normalize_rules():
+    from kohakufa_b200 import mask
+
+    with pytest.raises(TypeError):
+        mask.normalize(torch.ones(3, 3), 1, 1, 3, 3)
+    with pytest.raises(ValueError):
+        mask.normalize(torch.ones(3, 4, dtype=torch.bool), 1, 1, 3, 3)
+    with pytest.raises(ValueError):
+        mask.normalize(torch.ones(2, 1, 3, 3, dtype=torch.bool), 3, 1, 3, 3)
+    assert mask.normalize(torch.ones(3, 3, dtype=torch.bool), 2, 2, 3, 3).shape == (1, 1, 3, 3)
+    assert mask.words_per_row(1) == 4 and mask.words_per_row(128) == 4 and mask.words_per_row(129) == 8
+    with pytest.raises(ValueError, match="CUDA"):
+        kohakufa_b200.pack_mask(torch.ones(3, 3, dtype=torch.bool), 1, 1, 3, 3)
 
 
 def test_varlen_plan_reads_lengths_once_and_validates():

@@ -36,6 +36,27 @@ def test_attention_fp64_matches_reference(name, attention_golden):
         assert float((g - want).abs().max()) < 1e-11, (name, key)
 
 
+@pytest.mark.parametrize("name", sorted(make_golden.MASK_CASES))
+def test_masked_and_grouped_attention_matches_reference(name, attention_golden):
+    """Boolean masks (random, broadcast with empty rows, key padding) and grouped-query attention."""
+    case = make_golden.MASK_CASES[name]
+    q, k, v, dout, mask, block = make_golden.make_mask_inputs(case)
+    got = oracle.attention_fp64(q, k, v, dout, case[5] ** -0.5, block=block, mask=mask, groups=case[1] // case[2])
+    for key, g in zip(("out", "dq", "dk", "dv"), got):
+        want = torch.from_numpy(attention_golden[f"{name}/{key}"])
+        assert g.shape == want.shape, (name, key)
+        assert bool(torch.isfinite(g).all()), (name, key)
+        assert oracle.metrics(g, want)["rel_err"] < 1e-12, (name, key)
+        assert float((g - want).abs().max()) < 1e-11, (name, key)
+
+
+def test_rows_without_visible_keys_are_zero():
+    case = make_golden.MASK_CASES["mask_broadcast_empty_rows_f16"]
+    q, k, v, dout, mask, _ = make_golden.make_mask_inputs(case)
+    out, dq, _, _ = oracle.attention_fp64(q, k, v, dout, case[5] ** -0.5, mask=mask)
+    assert float(out[:, :, 5:10].abs().max()) == 0.0 and float(dq[:, :, 5:10].abs().max()) == 0.0
+
+
 @pytest.mark.parametrize("name", sorted(make_golden.ATTENTION_CASES))
 def test_metrics_match_reference(name, attention_golden):
     want_out = torch.from_numpy(attention_golden[f"{name}/out"])
