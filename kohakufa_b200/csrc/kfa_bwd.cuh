@@ -196,6 +196,19 @@ __device__ __forceinline__ void issue_tmemA_k128(bool lead, uint32_t d_tmem, uin
                  (acc || kk > 0) ? 1u : 0u);
 }
 
+// The same for half of the contraction: k-steps 2 * part, 2 * part + 1 of each warpgroup's piece
+// (the first or the second 32 of its 64 contraction indices).
+template <int D>
+__device__ __forceinline__ void issue_tmemA_k64(bool lead, uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
+                                                uint32_t idesc, bool acc, int part) {
+#pragma unroll
+  for (int x = 0; x < 4; ++x) {
+    const int kk = (x >> 1) * 4 + 2 * part + (x & 1);
+    umma_ts_lead(lead, d_tmem, a_tmem + (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8), b_lo + ((kk * 16 * 128) >> 4), idesc,
+                 (acc || x > 0 || part > 0) ? 1u : 0u);
+  }
+}
+
 // Stores (add = false) or adds (add = true) a row of an fp32 accumulator times mul to fp32 memory.
 __device__ __forceinline__ void store_acc_row_f32(uint32_t taddr, int col0, int ncols, float mul, float* grow,
                                                   bool valid, bool add) {
@@ -254,11 +267,12 @@ __device__ __forceinline__ void store_acc_row(uint32_t taddr, int col0, int ncol
 // 8j + 2(lane % 4), +1 of key row (lane / 4 + 8 * sel) of the warp's 16-lane half `half`.
 //   P = exp2(fma(S - m, c, -log2 l)), kept in fp32 (pr) and packed to 16 bits (pk).
 // MASKED: a pair whose query index is below the key's first visible query (qmin[2 * half + sel]) gets P = 0.
-template <bool BF16, bool MASKED>
+// J0: the four column blocks J0 .. J0 + 3 (32 of the warpgroup's 64 queries) are done per call.
+template <bool BF16, bool MASKED, int J0>
 __device__ __forceinline__ void p_frag(const float2* sv, const float* st, float2 c2, int q_first, const int* qmin,
                                        float2* pr, uint32_t* pk) {
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
+  for (int j = J0; j < J0 + 4; ++j) {
     const float2 nm = *reinterpret_cast<const float2*>(st + 8 * j);
     const float2 nl = *reinterpret_cast<const float2*>(st + 128 + 8 * j);
 #pragma unroll
@@ -277,11 +291,11 @@ __device__ __forceinline__ void p_frag(const float2* sv, const float* st, float2
 }
 // The same under a boolean mask: w[e] holds the two words (64 queries of this warpgroup) of key row e;
 // a pair whose bit is clear gets P = 0. col0 = this thread's first column inside every block of 8.
-template <bool BF16>
+template <bool BF16, int J0>
 __device__ __forceinline__ void p_frag_bits(const float2* sv, const float* st, float2 c2, const uint2* w, int col0,
                                             float2* pr, uint32_t* pk) {
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
+  for (int j = J0; j < J0 + 4; ++j) {
     const float2 nm = *reinterpret_cast<const float2*>(st + 8 * j);
     const float2 nl = *reinterpret_cast<const float2*>(st + 128 + 8 * j);
 #pragma unroll
@@ -371,7 +385,8 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   constexpr int B_DS = 4 + 2 * NSL;       // dS^T(i) stored by both warpgroups
   constexpr int B_ACC = 5 + 2 * NSL;      // dV, dK complete
   constexpr int B_DRAIN = 6 + 2 * NSL;
-  constexpr int N_BARS = 7 + 2 * NSL;
+  constexpr int B_PLO = 7 + 2 * NSL;      // the first 32 queries of P^T(i) stored by both warpgroups
+  constexpr int N_BARS = 8 + 2 * NSL;
   static_assert(N_BARS * 8 + 16 <= 256, "barrier block too small");
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + N_BARS);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
@@ -409,6 +424,7 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     mbar_init(bar(B_S), 1);
     mbar_init(bar(B_DP), 1);
     mbar_init(bar(B_P), 256);
+    mbar_init(bar(B_PLO), 256);
     mbar_init(bar(B_DS), 256);
     mbar_init(bar(B_ACC), 1);
     mbar_init(bar(B_DRAIN), 1);
@@ -501,11 +517,17 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const uint32_t q_n = sSlot + nslot * Cfg::KV_SLOT_BYTES;
         const uint32_t do_n = q_n + Cfg::TILE_BYTES;
         const bool more = s + 1 < n_steps;
-        // dV += P^T(i) dO_i, then S^T(i+1) may overwrite the P^T columns
+        // dV += P^T(i) dO_i in two parts (the first 32 queries of each warpgroup's P^T are signalled
+        // early, so the tensor core starts while the other exponentials are computed), then S^T(i+1)
+        // may overwrite the P^T columns
+        ok = mbar_wait_warp(bar(B_PLO), s & 1, ctl, 4);
+        if (!ok) break;
+        tc_fence_after();
+        issue_tmemA_k64<D>(lead, tDV, tST, sdesc_lo(do_s, TILE_BYTES_64), IDESC_ACC, s > 0, 0);
         ok = mbar_wait_warp(bar(B_P), s & 1, ctl, 4);
         if (!ok) break;
         tc_fence_after();
-        issue_tmemA_k128<D>(lead, tDV, tST, sdesc_lo(do_s, TILE_BYTES_64), IDESC_ACC, s > 0);
+        issue_tmemA_k64<D>(lead, tDV, tST, sdesc_lo(do_s, TILE_BYTES_64), IDESC_ACC, s > 0, 1);
         if (more) {
           ok = mbar_wait_warp(bar(B_QREADY + nslot), ((s + 1) / NSL) & 1, ctl, 5);
           if (!ok) break;
@@ -603,18 +625,33 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tmem_ld_16x256b_x8(tS + HALF, reinterpret_cast<uint32_t*>(sv + 16));
         tmem_wait_ld();
         uint32_t pk[32];
+        // 16-bit P^T goes over the first 32 of the 64 columns this warp has just read (all its lanes),
+        // in two parts of 32 queries (16 packed columns) each
         if constexpr (MASKW)
-          p_frag_bits<BF16>(sv, st, c2, wcur, col0, pr, pk);
+          p_frag_bits<BF16, 0>(sv, st, c2, wcur, col0, pr, pk);
         else if (masked)
-          p_frag<BF16, true>(sv, st, c2, q0, qmin, pr, pk);
+          p_frag<BF16, true, 0>(sv, st, c2, q0, qmin, pr, pk);
         else
-          p_frag<BF16, false>(sv, st, c2, q0, qmin, pr, pk);
-        // 16-bit P^T over the first 32 of the 64 columns this warp has just read (all its lanes)
-        tmem_st_16x128b_x8(tS, pk);
-        tmem_st_16x128b_x8(tS + HALF, pk + 16);
+          p_frag<BF16, false, 0>(sv, st, c2, q0, qmin, pr, pk);
+        tmem_st_16x128b_x4(tS, pk);
+        tmem_st_16x128b_x4(tS + HALF, pk + 16);
+        if constexpr (D == 128) {  // (at D = 64 the dV MMA is too short for the early start to pay)
+          tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive(bar(B_PLO));
+        }
+        if constexpr (MASKW)
+          p_frag_bits<BF16, 4>(sv, st, c2, wcur, col0, pr, pk);
+        else if (masked)
+          p_frag<BF16, true, 4>(sv, st, c2, q0, qmin, pr, pk);
+        else
+          p_frag<BF16, false, 4>(sv, st, c2, q0, qmin, pr, pk);
+        tmem_st_16x128b_x4(tS + 16, pk + 8);
+        tmem_st_16x128b_x4(tS + HALF + 16, pk + 24);
       }
       tmem_wait_st();
       tc_fence_before();
+      if constexpr (D != 128) mbar_arrive(bar(B_PLO));
       mbar_arrive(bar(B_P));
       KFA_PROF_END(3);
       KFA_PROF_BEGIN();

@@ -403,6 +403,14 @@ __device__ __forceinline__ void tmem_st_16x128b_x8(uint32_t taddr, const uint32_
       : "memory");
 }
 
+// st.16x128b.x4: 16 lanes x 16 columns, 8 registers, same element map as the x8 form.
+__device__ __forceinline__ void tmem_st_16x128b_x4(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.16x128b.x4.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+      : "memory");
+}
+
 // ----------------------------------------------------------------------------------
 // Arithmetic helpers
 // ----------------------------------------------------------------------------------
