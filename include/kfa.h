@@ -112,25 +112,38 @@ int kfa_bwd_varlen(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v
  * row. Rows are 4 * ceil(n / 128) words long (whole 128-wide tiles) with zero bits past the end. The words
  * of row r of (batch b, head h) start at words + b * stride_batch + h * stride_head + r * stride_row
  * (in words; multiples of 4; a batch / head stride of 0 broadcasts one mask). A query row with no
- * visible key gets output 0 and zero gradients (its statistics are m = +inf, log2 l = 0). The
- * reference's per-tile classes and tile lists are not used: every key tile is visited. */
+ * visible key gets output 0 and zero gradients (its statistics are m = +inf, log2 l = 0).
+ *
+ * Optional tile table (replaces the reference's tile lists, mask.py:74-122): one int32 per (128 queries x
+ * 128 keys) tile, nonzero = the tile holds a visible pair; tile (qt, kt) of (b, h) at any + b * stride_batch
+ * + h * stride_head + qt * ceil(Skv / 128) + kt. With it the kernels skip tile pairs in which nothing is
+ * visible (each CTA lists the tiles it visits in shared memory; where a list would not fit — more than
+ * 1024 key tiles per row, 768 for the dQ kernel at D = 128, 2048 (query head, query tile) steps per key
+ * tile — every tile is visited). NULL: every tile is visited. */
 typedef struct KfaMaskWords {
   const int32_t* words;
   int64_t stride_batch, stride_head, stride_row;
 } KfaMaskWords;
+typedef struct KfaMaskTiles {
+  const int32_t* any;
+  int64_t stride_batch, stride_head;
+} KfaMaskTiles;
 
 /* mask: bytes, nonzero = visible, element (b, h, r, c) at mask[b * s[0] + h * s[1] + r * s[2] + c * s[3]]
  * with mask_batch x mask_heads x Sq x Skv elements. words: int32[mask_batch * mask_heads * Sq *
- * 4 ceil(Skv / 128)], words_t: int32[mask_batch * mask_heads * Skv * 4 ceil(Sq / 128)], both contiguous. */
+ * 4 ceil(Skv / 128)], words_t: int32[mask_batch * mask_heads * Skv * 4 ceil(Sq / 128)], both contiguous.
+ * tiles (optional): int32[mask_batch * mask_heads * ceil(Sq / 128) * ceil(Skv / 128)], ZEROED by the
+ * caller; the kernel sets the entries of tiles that hold a visible pair. */
 int kfa_pack_mask(const void* mask, const int64_t* mask_stride, int mask_batch, int mask_heads, int Sq,
-                  int Skv, int32_t* words, int32_t* words_t, void* stream);
+                  int Skv, int32_t* words, int32_t* words_t, int32_t* tiles, void* stream);
 int kfa_fwd_masked(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* out,
-                   float* lse, const KfaMaskWords* words, float scale, int dtype, int* dev_status,
-                   void* stream);
+                   float* lse, const KfaMaskWords* words, const KfaMaskTiles* tiles, float scale, int dtype,
+                   int* dev_status, void* stream);
 int kfa_bwd_masked(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* out,
                    const KfaTensor4* dout, const float* lse, float* stats, const KfaTensor4* dq,
                    const KfaTensor4* dk, const KfaTensor4* dv, const KfaMaskWords* words,
-                   const KfaMaskWords* words_t, float scale, int dtype, int* dev_status, void* stream);
+                   const KfaMaskWords* words_t, const KfaMaskTiles* tiles, float scale, int dtype,
+                   int* dev_status, void* stream);
 
 /* Backward without a scratch buffer from the caller. No counterpart in the reference (there the
  * launcher allocates its scratch from torch's caching allocator, bwd.py:1434-1439).

@@ -57,6 +57,10 @@ class KfaMaskWords(ctypes.Structure):
     ]
 
 
+class KfaMaskTiles(ctypes.Structure):
+    _fields_ = [("any", ctypes.c_void_p), ("stride_batch", ctypes.c_int64), ("stride_head", ctypes.c_int64)]
+
+
 class KfaAcc32(ctypes.Structure):
     _fields_ = [("ptr", ctypes.c_void_p), ("head_stride", ctypes.c_int64)]
 
@@ -108,9 +112,10 @@ def load() -> ctypes.CDLL:
         A = ctypes.POINTER(KfaAcc32)
         i64, f32, i32 = ctypes.c_int64, ctypes.c_float, ctypes.c_int
         M = ctypes.POINTER(KfaMaskWords)
-        lib.kfa_pack_mask.argtypes = [vp, ctypes.POINTER(ctypes.c_int64), i32, i32, i32, i32, ip, ip, vp]
-        lib.kfa_fwd_masked.argtypes = [T, T, T, T, fp, M, f32, i32, ip, vp]
-        lib.kfa_bwd_masked.argtypes = [T, T, T, T, T, fp, fp, T, T, T, M, M, f32, i32, ip, vp]
+        MT = ctypes.POINTER(KfaMaskTiles)
+        lib.kfa_pack_mask.argtypes = [vp, ctypes.POINTER(ctypes.c_int64), i32, i32, i32, i32, ip, ip, ip, vp]
+        lib.kfa_fwd_masked.argtypes = [T, T, T, T, fp, M, MT, f32, i32, ip, vp]
+        lib.kfa_bwd_masked.argtypes = [T, T, T, T, T, fp, fp, T, T, T, M, M, MT, f32, i32, ip, vp]
         lib.kfa_fwd_varlen.argtypes = [T, T, T, T, fp, ip, ip, i32, i32, i32, f32, i32, i32, ip, vp]
         lib.kfa_bwd_varlen.argtypes = [T, T, T, T, T, fp, fp, T, T, T, ip, ip, i32, i32, i32, f32, i32, i32, ip, vp]
         lib.kfa_cp_fwd_step.argtypes = [T, T, T, A, fp, i64, i64, i32, f32, i32, i32, ip, vp]

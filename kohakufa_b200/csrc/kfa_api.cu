@@ -123,11 +123,12 @@ template <int D, bool BF16, bool MASKW>
 int launch_fwd_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const kfa::FwdParams& p,
                  cudaStream_t s) {
   auto kern = kfa::kfa_fwd_kernel<D, BF16, MASKW>;
-  int rc = set_smem(kern, kfa::FwdCfg<D>::SMEM_BYTES);
+  constexpr int smem = MASKW ? kfa::FwdCfg<D>::SMEM_BYTES_LIST : kfa::FwdCfg<D>::SMEM_BYTES;
+  int rc = set_smem(kern, smem);
   if (rc) return rc;
   const long long grid = static_cast<long long>(p.B) * p.H * p.n_q_tiles;
   if (grid > 0x7fffffffll) return fail(KFA_ERR_ARG, "too many tiles");
-  kern<<<static_cast<unsigned>(grid), kfa::FWD_THREADS, kfa::FwdCfg<D>::SMEM_BYTES, s>>>(mq, mk, mv, p);
+  kern<<<static_cast<unsigned>(grid), kfa::FWD_THREADS, smem, s>>>(mq, mk, mv, p);
   KFA_CUDA(cudaGetLastError());
   return KFA_OK;
 }
@@ -150,11 +151,12 @@ template <int D, bool BF16, bool MASKW>
 int launch_dkdv_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mdo,
                   const kfa::BwdParams& p, cudaStream_t s) {
   auto kern = kfa::kfa_bwd_dkdv_kernel<D, BF16, MASKW>;
-  int rc = set_smem(kern, kfa::BwdCfg<D>::KV_SMEM_BYTES);
+  constexpr int smem = MASKW ? kfa::BwdCfg<D>::KV_SMEM_BYTES_LIST : kfa::BwdCfg<D>::KV_SMEM_BYTES;
+  int rc = set_smem(kern, smem);
   if (rc) return rc;
   const long long grid = static_cast<long long>(p.B) * p.Hkv * p.n_k128;
   if (grid > 0x7fffffffll) return fail(KFA_ERR_ARG, "too many tiles");
-  kern<<<static_cast<unsigned>(grid), kfa::BWD_THREADS, kfa::BwdCfg<D>::KV_SMEM_BYTES, s>>>(mq, mk, mv, mdo, p);
+  kern<<<static_cast<unsigned>(grid), kfa::BWD_THREADS, smem, s>>>(mq, mk, mv, mdo, p);
   KFA_CUDA(cudaGetLastError());
   return KFA_OK;
 }
@@ -169,11 +171,12 @@ template <int D, bool BF16, bool MASKW>
 int launch_dq_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mdo,
                 const kfa::BwdParams& p, cudaStream_t s) {
   auto kern = kfa::kfa_bwd_dq_kernel<D, BF16, MASKW>;
-  int rc = set_smem(kern, kfa::BwdCfg<D>::Q_SMEM_BYTES);
+  constexpr int smem = MASKW ? kfa::BwdCfg<D>::Q_SMEM_BYTES_LIST : kfa::BwdCfg<D>::Q_SMEM_BYTES;
+  int rc = set_smem(kern, smem);
   if (rc) return rc;
   const long long grid = static_cast<long long>(p.B) * p.H * p.n_q128;
   if (grid > 0x7fffffffll) return fail(KFA_ERR_ARG, "too many tiles");
-  kern<<<static_cast<unsigned>(grid), kfa::BWD_THREADS, kfa::BwdCfg<D>::Q_SMEM_BYTES, s>>>(mq, mk, mv, mdo, p);
+  kern<<<static_cast<unsigned>(grid), kfa::BWD_THREADS, smem, s>>>(mq, mk, mv, mdo, p);
   KFA_CUDA(cudaGetLastError());
   return KFA_OK;
 }
@@ -217,7 +220,14 @@ struct Extra {
   const Varlen* vl = nullptr;
   const KfaMaskWords* mw = nullptr;   // words along query rows
   const KfaMaskWords* mwt = nullptr;  // words along key rows
+  const KfaMaskTiles* mt = nullptr;   // which 128 x 128 tiles hold a visible pair (optional)
 };
+
+int check_tiles(const KfaMaskTiles* t) {
+  if (!t) return KFA_OK;
+  if (!t->any || t->stride_batch < 0 || t->stride_head < 0) return fail(KFA_ERR_ARG, "mask tiles: null table or negative stride");
+  return KFA_OK;
+}
 
 // rows: the rows the words must cover; cols: the bits per row (padded to whole 128-wide tiles)
 int check_mask(const KfaMaskWords* m, int64_t cols, const char* name) {
@@ -272,6 +282,17 @@ void apply_extra(kfa::BwdParams& p, const Extra& ex) {
     p.mwt_sh = ex.mwt->stride_head;
     p.mwt_row = static_cast<int>(ex.mwt->stride_row);
   }
+  if (ex.mt && ex.mt->any) {
+    // the lists of visited tiles live in shared memory: use the table where they fit
+    const bool fits_dkdv = static_cast<long long>(p.group) * p.n_q128 <= kfa::BwdCfg<128>::KV_LIST_CAP;
+    const bool fits_dq = p.n_k128 <= kfa::BwdCfg<128>::Q_LIST_CAP;
+    if (ex.mwt ? fits_dkdv : (ex.mw && fits_dq)) {  // (a call passes the words of ONE of the two kernels)
+      p.mt = ex.mt->any;
+      p.mt_sb = ex.mt->stride_batch;
+      p.mt_sh = ex.mt->stride_head;
+      p.mt_row = p.n_k128;
+    }
+  }
   const Varlen* vl = ex.vl;
   if (!vl) return;
   p.B = vl->n_seqs;
@@ -321,6 +342,14 @@ int fwd_impl(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, cons
     p.mw_sb = ex.mw->stride_batch;
     p.mw_sh = ex.mw->stride_head;
     p.mw_row = static_cast<int>(ex.mw->stride_row);
+    const int n_k128 = (p.Skv + 127) / 128;
+    if ((rc = check_tiles(ex.mt))) return rc;
+    if (ex.mt && n_k128 <= kfa::TILE_LIST_CAP) {  // (longer rows: every key tile is visited)
+      p.mt = ex.mt->any;
+      p.mt_sb = ex.mt->stride_batch;
+      p.mt_sh = ex.mt->stride_head;
+      p.mt_row = n_k128;
+    }
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   KFA_DISPATCH(q->shape[3], dtype, (launch_fwd<KD, KB>(mq, mk, mv, p, s)));
@@ -457,26 +486,29 @@ int kfa_fwd_varlen(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v
 }
 
 int kfa_fwd_masked(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* out, float* lse,
-                   const KfaMaskWords* words, float scale, int dtype, int* dev_status, void* stream) {
+                   const KfaMaskWords* words, const KfaMaskTiles* tiles, float scale, int dtype, int* dev_status,
+                   void* stream) {
   if (!words) return fail(KFA_ERR_ARG, "kfa_fwd_masked: null mask");
   Extra ex;
   ex.mw = words;
+  ex.mt = tiles;
   return fwd_impl(q, k, v, out, lse, ex, scale, 0, dtype, dev_status, stream);
 }
 
 int kfa_bwd_masked(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* out,
                    const KfaTensor4* dout, const float* lse, float* stats, const KfaTensor4* dq, const KfaTensor4* dk,
-                   const KfaTensor4* dv, const KfaMaskWords* words, const KfaMaskWords* words_t, float scale, int dtype,
-                   int* dev_status, void* stream) {
+                   const KfaTensor4* dv, const KfaMaskWords* words, const KfaMaskWords* words_t,
+                   const KfaMaskTiles* tiles, float scale, int dtype, int* dev_status, void* stream) {
   if (!words || !words_t) return fail(KFA_ERR_ARG, "kfa_bwd_masked: null mask");
-  Extra ex;
-  ex.mw = words;
-  ex.mwt = words_t;
+  Extra ex_kv, ex_q;
+  ex_kv.mwt = words_t;
+  ex_q.mw = words;
+  ex_kv.mt = ex_q.mt = tiles;
   int rc;
-  if ((rc = check_like(out, q, "out"))) return rc;
+  if ((rc = check_like(out, q, "out")) || (rc = check_tiles(tiles))) return rc;
   if ((rc = prepare_impl(out, dout, lse, stats, nullptr, dtype, stream))) return rc;
-  if ((rc = dkdv_impl(q, k, v, dout, stats, dk, dv, ex, scale, 0, dtype, dev_status, stream))) return rc;
-  return dq_impl(q, k, v, dout, stats, dq, ex, scale, 0, dtype, dev_status, stream);
+  if ((rc = dkdv_impl(q, k, v, dout, stats, dk, dv, ex_kv, scale, 0, dtype, dev_status, stream))) return rc;
+  return dq_impl(q, k, v, dout, stats, dq, ex_q, scale, 0, dtype, dev_status, stream);
 }
 
 int kfa_bwd_varlen(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* out,

@@ -79,6 +79,11 @@ struct BwdParams {
   const int* mwt;
   long long mwt_sb, mwt_sh;
   int mwt_row;
+  // Optional with a mask: nonzero = some bit of the (128 queries x 128 keys) tile is set; tile (qt, kt) of
+  // (b, h) at mt + b * mt_sb + h * mt_sh + qt * mt_row + kt. Tile pairs without a visible pair are skipped.
+  const int* mt;
+  long long mt_sb, mt_sh;
+  int mt_row;
 };
 
 struct PrepParams {
@@ -161,6 +166,8 @@ struct BwdCfg {
   static constexpr int KV_SLOT_BYTES = 2 * TILE_BYTES + 2048;  // stats padded to keep 1 KB alignment
   static constexpr int KV_SMEM_TILES = 2 * TILE_BYTES + KV_SLOTS * KV_SLOT_BYTES;
   static constexpr int KV_SMEM_BYTES = KV_SMEM_TILES + 1024 + 256;
+  static constexpr int KV_LIST_CAP = 2048;  // (query head, query tile) steps a masked CTA can list
+  static constexpr int KV_SMEM_BYTES_LIST = KV_SMEM_BYTES + 4 * KV_LIST_CAP;
   // dQ kernel: Q, dO resident; K_j and V_j through rings of their own. K_j is read by S(j) and, a step
   // later, by dQ(j); V_j only by dP(j): three K buffers and two V buffers let the copy of tile j + 2
   // start a whole step before it is needed (with K and V sharing two slots it could start only when
@@ -169,6 +176,8 @@ struct BwdCfg {
   static constexpr int NV = (D == 128) ? 2 : 3;
   static constexpr int Q_SMEM_TILES = (2 + NK + NV) * TILE_BYTES;
   static constexpr int Q_SMEM_BYTES = Q_SMEM_TILES + 1024 + 256;
+  static constexpr int Q_LIST_CAP = (D == 128) ? 768 : 1024;  // key tiles a masked CTA can list (what fits)
+  static constexpr int Q_SMEM_BYTES_LIST = Q_SMEM_BYTES + 2 * Q_LIST_CAP;
 };
 
 // Issue helpers for the MMA warp (converged; `lead` is true in the one lane that issues). Operand
@@ -412,8 +421,11 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int first_i = (p.P > 0) ? static_cast<int>((static_cast<long long>(kv0 / p.P) * p.P) / 128) : 0;
   // steps: for every query head of this K / V head's group, the query tiles that see these keys
   const int n_per = max((Sq + 127) / 128 - first_i, 0);
-  const int n_steps = n_per * p.group;
+  int n_steps = n_per * p.group;
   const bool ragged_keys = kv0 + 128 > Skv;
+  // boolean masks with a tile table: the (query head, query tile) steps this CTA runs, in shared memory
+  uint32_t* s_list = reinterpret_cast<uint32_t*>(smem + Cfg::KV_SMEM_TILES + 256);
+  const bool use_list = MASKW && p.mt != nullptr;
 
   if (tid == 0) {
     mbar_init(bar(B_KV), 1);
@@ -435,10 +447,30 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     tmem_alloc(smem_u32(s_tmem), Cfg::TMEM_COLS);
     tmem_relinquish();
   }
+  if constexpr (MASKW) {
+    if (use_list && warp == 1) {
+      int count = 0;
+      for (int g = 0; g < p.group; ++g) {
+        const int* col = p.mt + bc * p.mt_sb + (hk * p.group + g) * p.mt_sh + kt;
+        for (int i0 = 0; i0 < n_per; i0 += 32) {
+          const int i = i0 + lane;
+          const bool seen = i < n_per && __ldg(col + static_cast<long long>(i) * p.mt_row) != 0;
+          const unsigned m = __ballot_sync(0xffffffffu, seen);
+          if (seen) s_list[count + __popc(m & ((1u << lane) - 1u))] = (static_cast<uint32_t>(g) << 16) | static_cast<uint32_t>(i);
+          count += __popc(m);
+        }
+      }
+      if (lane == 0) s_tmem[2] = static_cast<uint32_t>(count);
+    }
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *s_tmem;
+  if (use_list) n_steps = static_cast<int>(s_tmem[2]);
+  // step s -> query tile and query head
+  auto tile_of = [&](int s) { return use_list ? static_cast<int>(s_list[s] & 0xffffu) : first_i + s % n_per; };
+  auto head_of = [&](int s) { return hk * p.group + (use_list ? static_cast<int>(s_list[s] >> 16) : s / n_per); };
 #ifdef KFA_PROFILE
   long long prof_acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
   long long kfa_prof_tb = 0;
@@ -467,10 +499,10 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       int issued = 0;
       for (int s = 0; s < n_steps; ++s) {
         const int slot = s % NSL, use = s / NSL;
-        if (use > 0) ok = mbar_wait(bar(B_QFREE + slot), (use - 1) & 1, ctl, 1);
+        if (use > 0) ok = mbar_wait(bar(B_QFREE + slot), (use - 1) & 1, ctl, 11);
         if (!ok) break;
-        const int i = first_i + s % n_per;
-        const int head = hk * p.group + s / n_per;
+        const int i = tile_of(s);
+        const int head = head_of(s);
         const uint32_t base = sSlot + slot * Cfg::KV_SLOT_BYTES;
         mbar_expect_tx(bar(B_QREADY + slot), 2 * Cfg::TILE_BYTES + STATS_BYTES);
         for (int ch = 0; ch < CH; ++ch) {
@@ -500,8 +532,8 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const uint32_t tST = tmem + Cfg::TM_S, tDP = tmem + Cfg::TM_DP;
       const uint32_t tDV = tmem + Cfg::TM_ACC0, tDK = tmem + Cfg::TM_ACC1;
       const uint32_t k_lo = sdesc_lo(sK, 16), v_lo = sdesc_lo(sV, 16);
-      bool ok = mbar_wait_warp(bar(B_KV), 0, ctl, 2);
-      if (ok) ok = mbar_wait_warp(bar(B_QREADY + 0), 0, ctl, 3);
+      bool ok = mbar_wait_warp(bar(B_KV), 0, ctl, 12);
+      if (ok) ok = mbar_wait_warp(bar(B_QREADY + 0), 0, ctl, 13);
       if (ok) {
         tc_fence_after();
         issue_kmajor_n128<D>(lead, tST, k_lo, sdesc_lo(sSlot, 16), IDESC_S);
@@ -520,22 +552,22 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         // dV += P^T(i) dO_i in two parts (the first 32 queries of each warpgroup's P^T are signalled
         // early, so the tensor core starts while the other exponentials are computed), then S^T(i+1)
         // may overwrite the P^T columns
-        ok = mbar_wait_warp(bar(B_PLO), s & 1, ctl, 4);
+        ok = mbar_wait_warp(bar(B_PLO), s & 1, ctl, 14);
         if (!ok) break;
         tc_fence_after();
         issue_tmemA_k64<D>(lead, tDV, tST, sdesc_lo(do_s, TILE_BYTES_64), IDESC_ACC, s > 0, 0);
-        ok = mbar_wait_warp(bar(B_P), s & 1, ctl, 4);
+        ok = mbar_wait_warp(bar(B_P), s & 1, ctl, 14);
         if (!ok) break;
         tc_fence_after();
         issue_tmemA_k64<D>(lead, tDV, tST, sdesc_lo(do_s, TILE_BYTES_64), IDESC_ACC, s > 0, 1);
         if (more) {
-          ok = mbar_wait_warp(bar(B_QREADY + nslot), ((s + 1) / NSL) & 1, ctl, 5);
+          ok = mbar_wait_warp(bar(B_QREADY + nslot), ((s + 1) / NSL) & 1, ctl, 15);
           if (!ok) break;
           issue_kmajor_n128<D>(lead, tST, k_lo, sdesc_lo(q_n, 16), IDESC_S);
           umma_commit_lead(lead, bar(B_S));
         }
         // dK += dS^T(i) Q_i, then dP^T(i+1) may overwrite the dS^T columns
-        ok = mbar_wait_warp(bar(B_DS), s & 1, ctl, 6);
+        ok = mbar_wait_warp(bar(B_DS), s & 1, ctl, 16);
         if (!ok) break;
         tc_fence_after();
         issue_tmemA_k128<D>(lead, tDK, tDP, sdesc_lo(q_s, TILE_BYTES_64), IDESC_ACC, s > 0);
@@ -580,8 +612,8 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const int* mkey[4] = {nullptr, nullptr, nullptr, nullptr};
     uint2 wnext[4];
     auto mask_fetch = [&](int s) {
-      const int i = first_i + s % n_per;
-      const int head = hk * p.group + s / n_per;
+      const int i = tile_of(s);
+      const int head = head_of(s);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         wnext[e] = make_uint2(0u, 0u);
@@ -605,12 +637,12 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (s + 1 < n_steps) mask_fetch(s + 1);
       }
       const int slot = s % NSL;
-      const int i = first_i + s % n_per;
+      const int i = tile_of(s);
       const int q0 = i * 128 + 64 * hq + col0;  // query of this thread's first column
       // masked step: some (key, query) pair of this tile pair is hidden, or keys are padded
       const bool masked = ragged_keys || (p.P > 0 && key_limit(i * 128, p.P, Skv) < kv0 + 128);
-      ok = mbar_wait_warp(bar(B_QREADY + slot), (s / NSL) & 1, ctl, 7);  // stats of this step
-      if (ok) ok = mbar_wait_warp(bar(B_S), s & 1, ctl, 8);
+      ok = mbar_wait_warp(bar(B_QREADY + slot), (s / NSL) & 1, ctl, 17);  // stats of this step
+      if (ok) ok = mbar_wait_warp(bar(B_S), s & 1, ctl, 18);
       if (!ok) break;
       tc_fence_after();
       const float* st =
@@ -655,7 +687,7 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       mbar_arrive(bar(B_P));
       KFA_PROF_END(3);
       KFA_PROF_BEGIN();
-      ok = mbar_wait_warp(bar(B_DP), s & 1, ctl, 9);
+      ok = mbar_wait_warp(bar(B_DP), s & 1, ctl, 19);
       if (!ok) break;
       tc_fence_after();
       KFA_PROF_END(6);
@@ -694,7 +726,7 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       if (valid && p.acc_mode == 1)
         for (int cc = 0; cc < D; cc += 4) *reinterpret_cast<float4*>(grow32 + cc) = make_float4(0.f, 0.f, 0.f, 0.f);
     } else {
-      ok = mbar_wait_warp(bar(B_ACC), 0, ctl, 9) && ok;
+      ok = mbar_wait_warp(bar(B_ACC), 0, ctl, 19) && ok;
       if (ok) {
         tc_fence_after();
         const uint32_t tacc = tmem + (hq ? Cfg::TM_ACC1 : Cfg::TM_ACC0) + lane_base;
@@ -774,8 +806,11 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     if (row0 >= Sq || Skv <= 0) return;  // the whole CTA, before anything is set up
   }
   const int last = min(row0 + 127, Sq - 1);
-  const int n_steps = (key_limit(last, p.P, Skv) + 127) / 128;
+  int n_steps = (key_limit(last, p.P, Skv) + 127) / 128;
   const int n_unmasked = key_limit(row0, p.P, Skv) / 128;
+  // boolean masks with a tile table: the key tiles this CTA visits, in shared memory
+  uint16_t* s_list = reinterpret_cast<uint16_t*>(smem + Cfg::Q_SMEM_TILES + 256);
+  const bool use_list = MASKW && p.mt != nullptr;
 
   if (tid == 0) {
     mbar_init(bar(B_Q), 1);
@@ -800,10 +835,30 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     tmem_alloc(smem_u32(s_tmem), Cfg::TMEM_COLS);
     tmem_relinquish();
   }
+  if constexpr (MASKW) {
+    if (use_list && warp == 1) {
+      const int* trow = p.mt + bc * p.mt_sb + h * p.mt_sh + static_cast<long long>(qt) * p.mt_row;
+      int count = 0;
+      for (int j0 = 0; j0 < n_steps; j0 += 32) {
+        const int j = j0 + lane;
+        const bool seen = j < n_steps && __ldg(trow + j) != 0;
+        const unsigned m = __ballot_sync(0xffffffffu, seen);
+        if (seen) s_list[count + __popc(m & ((1u << lane) - 1u))] = static_cast<uint16_t>(j);
+        count += __popc(m);
+      }
+      if (count == 0) {  // nothing visible: one tile still runs, so that the rows get their zeros
+        if (lane == 0) s_list[0] = 0;
+        count = 1;
+      }
+      if (lane == 0) s_tmem[2] = static_cast<uint32_t>(count);
+    }
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *s_tmem;
+  if (use_list) n_steps = static_cast<int>(s_tmem[2]);
+  auto tile_of = [&](int it) { return use_list ? static_cast<int>(s_list[it]) : it; };
 #ifdef KFA_PROFILE
   long long prof_acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
   long long kfa_prof_tb = 0;
@@ -831,19 +886,19 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       int issued_k = 0, issued_v = 0;
       for (int j = 0; j < n_steps; ++j) {
         const int ks = j % NK, vs = j % NV;
-        if (j >= NK) ok = mbar_wait(bar(B_KFREE + ks), (j / NK - 1) & 1, ctl, 1);
+        if (j >= NK) ok = mbar_wait(bar(B_KFREE + ks), (j / NK - 1) & 1, ctl, 21);
         if (!ok) break;
         mbar_expect_tx(bar(B_KREADY + ks), Cfg::TILE_BYTES);
         for (int ch = 0; ch < CH; ++ch)
           tma_load_4d(sKr + ks * Cfg::TILE_BYTES + ch * TILE_BYTES_64, &tmK, bar(B_KREADY + ks), ch * 64,
-                      k_base + j * 128, h / p.group, bc);
+                      k_base + tile_of(j) * 128, h / p.group, bc);
         issued_k = j + 1;
-        if (j >= NV) ok = mbar_wait(bar(B_VFREE + vs), (j / NV - 1) & 1, ctl, 1);
+        if (j >= NV) ok = mbar_wait(bar(B_VFREE + vs), (j / NV - 1) & 1, ctl, 21);
         if (!ok) break;
         mbar_expect_tx(bar(B_VREADY + vs), Cfg::TILE_BYTES);
         for (int ch = 0; ch < CH; ++ch)
           tma_load_4d(sVr + vs * Cfg::TILE_BYTES + ch * TILE_BYTES_64, &tmV, bar(B_VREADY + vs), ch * 64,
-                      k_base + j * 128, h / p.group, bc);
+                      k_base + tile_of(j) * 128, h / p.group, bc);
         issued_v = j + 1;
       }
       if (!ok) {  // aborting: let the copies in flight land before the CTA gives up its shared memory
@@ -867,13 +922,13 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       constexpr uint32_t IDESC_ACC = make_idesc(BF16, true, 128, D);
       const uint32_t tS = tmem + Cfg::TM_S, tDP = tmem + Cfg::TM_DP, tDQ = tmem + Cfg::TM_ACC0;
       const uint32_t q_lo = sdesc_lo(sQ, 16), do_lo = sdesc_lo(sDO, 16);
-      bool ok = mbar_wait_warp(bar(B_Q), 0, ctl, 2);
-      if (ok) ok = mbar_wait_warp(bar(B_KREADY + 0), 0, ctl, 3);
+      bool ok = mbar_wait_warp(bar(B_Q), 0, ctl, 22);
+      if (ok) ok = mbar_wait_warp(bar(B_KREADY + 0), 0, ctl, 23);
       if (ok) {
         tc_fence_after();
         issue_kmajor_n128<D>(lead, tS, q_lo, sdesc_lo(sKr, 16), IDESC_S);
         umma_commit_lead(lead, bar(B_S));
-        ok = mbar_wait_warp(bar(B_VREADY + 0), 0, ctl, 3);
+        ok = mbar_wait_warp(bar(B_VREADY + 0), 0, ctl, 23);
       }
       if (ok) {
         tc_fence_after();
@@ -886,21 +941,21 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         const int nk = (j + 1) % NK, nv = (j + 1) % NV;
         const bool more = j + 1 < n_steps;
         if (more) {  // S(j+1) as soon as the warpgroups hold S(j) in registers
-          ok = mbar_wait_warp(bar(B_KREADY + nk), ((j + 1) / NK) & 1, ctl, 4);
-          if (ok) ok = mbar_wait_warp(bar(B_SREAD), j & 1, ctl, 5);
+          ok = mbar_wait_warp(bar(B_KREADY + nk), ((j + 1) / NK) & 1, ctl, 24);
+          if (ok) ok = mbar_wait_warp(bar(B_SREAD), j & 1, ctl, 25);
           if (!ok) break;
           tc_fence_after();
           issue_kmajor_n128<D>(lead, tS, q_lo, sdesc_lo(sKr + nk * Cfg::TILE_BYTES, 16), IDESC_S);
           umma_commit_lead(lead, bar(B_S));
         }
         // dQ += dS(j) K_j, then dP(j+1) may overwrite the dS columns
-        ok = mbar_wait_warp(bar(B_DS), j & 1, ctl, 6);
+        ok = mbar_wait_warp(bar(B_DS), j & 1, ctl, 26);
         if (!ok) break;
         tc_fence_after();
         issue_tmemA_k128<D>(lead, tDQ, tDP, sdesc_lo(k_s, TILE_BYTES_64), IDESC_ACC, j > 0);
         umma_commit_lead(lead, bar(B_KFREE + j % NK));
         if (more) {
-          ok = mbar_wait_warp(bar(B_VREADY + nv), ((j + 1) / NV) & 1, ctl, 4);
+          ok = mbar_wait_warp(bar(B_VREADY + nv), ((j + 1) / NV) & 1, ctl, 24);
           if (!ok) break;
           tc_fence_after();
           issue_kmajor_n128<D>(lead, tDP, do_lo, sdesc_lo(sVr + nv * Cfg::TILE_BYTES, 16), IDESC_S);
@@ -936,14 +991,14 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     if constexpr (MASKW) {
       mrow = reinterpret_cast<const uint2*>(p.mw + bc * p.mw_sb + h * p.mw_sh +
                                             static_cast<long long>(min(row, Sq - 1)) * p.mw_row + 2 * hk);
-      if (n_steps > 0) mnext = __ldg(mrow);
+      if (n_steps > 0) mnext = __ldg(mrow + 2 * tile_of(0));
     }
-    for (int j = 0; j < n_steps; ++j) {
+    for (int j = 0; j < n_steps; ++j) {  // j counts visited tiles (tile_of(j) is the key tile)
       const uint2 mcur = mnext;
       if constexpr (MASKW) {
-        if (j + 1 < n_steps) mnext = __ldg(mrow + 2 * (j + 1));
+        if (j + 1 < n_steps) mnext = __ldg(mrow + 2 * tile_of(j + 1));
       }
-      ok = mbar_wait_warp(bar(B_S), j & 1, ctl, 7);
+      ok = mbar_wait_warp(bar(B_S), j & 1, ctl, 27);
       if (!ok) break;
       tc_fence_after();
       const int lim = my_limit - j * 128 - 64 * hk;  // visible columns of this warpgroup (masked tiles)
@@ -967,7 +1022,7 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
       }
       KFA_PROF_END(3);
-      ok = mbar_wait_warp(bar(B_DP), j & 1, ctl, 8);
+      ok = mbar_wait_warp(bar(B_DP), j & 1, ctl, 28);
       if (!ok) break;
       tc_fence_after();
       KFA_PROF_BEGIN();
@@ -988,7 +1043,7 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       mbar_arrive(bar(B_DS));
       KFA_PROF_END(4);
     }
-    ok = mbar_wait_warp(bar(B_ACC), 0, ctl, 9) && ok;
+    ok = mbar_wait_warp(bar(B_ACC), 0, ctl, 29) && ok;
     if (ok) {
       tc_fence_after();
       if (p.acc_mode == 0) {

@@ -55,7 +55,16 @@ struct FwdParams {
   const int* mw;
   long long mw_sb, mw_sh;
   int mw_row;
+  // Optional with a mask: one int per (128 queries x 128 keys) tile, nonzero = some bit of the tile is set;
+  // tile (qt, kt) of (b, h) at mt + b * mt_sb + h * mt_sh + qt * mt_row + kt. Key tiles in which neither
+  // half of the CTA sees anything are skipped by every role (nullptr: all key tiles are visited).
+  const int* mt;
+  long long mt_sb, mt_sh;
+  int mt_row;
 };
+
+// Longest list of visited tiles a CTA keeps in shared memory (masks with more tiles per row visit all).
+constexpr int TILE_LIST_CAP = 1024;
 
 constexpr int FWD_THREADS = 320;
 constexpr int TILE_BYTES_64 = 128 * 64 * 2;  // one 128-row x 64-column 16-bit box = 16 KB
@@ -71,6 +80,7 @@ struct FwdCfg {
 #endif
   static constexpr int SMEM_TILES = 2 * TILE_BYTES + STAGES * TILE_BYTES;
   static constexpr int SMEM_BYTES = SMEM_TILES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int SMEM_BYTES_LIST = SMEM_BYTES + 2 * TILE_LIST_CAP;  // + the list of visited key tiles
   static constexpr uint32_t TMEM_COLS = 512;
   static constexpr uint32_t TM_S0 = 0, TM_S1 = 128, TM_O0 = 256, TM_O1 = 256 + D;
 };
@@ -146,7 +156,10 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       n_unmasked[hf] = 0;
     }
   }
-  const int n_max = max(n_tiles[0], n_tiles[1]);
+  int n_max = max(n_tiles[0], n_tiles[1]);
+  // boolean masks with a tile table: the key tiles this CTA visits, in shared memory
+  uint16_t* s_list = reinterpret_cast<uint16_t*>(smem + Cfg::SMEM_TILES + 256);
+  const bool use_list = MASKW && p.mt != nullptr;
 
   // ---- setup ----
   if (tid == 0) {
@@ -171,10 +184,36 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     tmem_alloc(smem_u32(s_tmem), Cfg::TMEM_COLS);
     tmem_relinquish();
   }
+  if constexpr (MASKW) {
+    if (use_list && warp == 1) {  // (warp 0 allocates tensor memory meanwhile)
+      const int* t0 = p.mt + bc * p.mt_sb + h * p.mt_sh + static_cast<long long>(2 * q_tile) * p.mt_row;
+      const bool two = row0 + 128 < Sq;
+      int count = 0;
+      for (int j0 = 0; j0 < n_max; j0 += 32) {
+        const int j = j0 + lane;
+        bool seen = false;
+        if (j < n_max) seen = (__ldg(t0 + j) | (two ? __ldg(t0 + p.mt_row + j) : 0)) != 0;
+        const unsigned m = __ballot_sync(0xffffffffu, seen);
+        if (seen) s_list[count + __popc(m & ((1u << lane) - 1u))] = static_cast<uint16_t>(j);
+        count += __popc(m);
+      }
+      if (count == 0) {  // nothing visible at all: one tile still runs, so that the rows get their zeros
+        if (lane == 0) s_list[0] = 0;
+        count = 1;
+      }
+      if (lane == 0) s_tmem[2] = static_cast<uint32_t>(count);
+    }
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *s_tmem;
+  if (use_list) {
+    n_max = static_cast<int>(s_tmem[2]);
+    n_tiles[0] = n_tiles[0] > 0 ? n_max : 0;
+    n_tiles[1] = n_tiles[1] > 0 ? n_max : 0;
+  }
+  auto tile_of = [&](int it) { return use_list ? static_cast<int>(s_list[it]) : it; };
 #ifdef KFA_PROFILE
   long long prof_acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
   long long kfa_prof_tb = 0;
@@ -205,7 +244,7 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       for (int i = 0; i < NS; ++i) armed[i] = -1;
       bool ok = true;
       for (int idx = 0; idx < 2 * n_max && ok; ++idx) {
-        const int j = idx >> 1;
+        const int j = tile_of(idx >> 1);
         const int stage = idx % NS;
         const int use = idx / NS;
         if (use > 0) ok = mbar_wait(bar(B_KVFREE + stage), (use - 1) & 1, ctl, 1);
@@ -344,13 +383,13 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     if constexpr (MASKW) {
       mrow = reinterpret_cast<const uint4*>(p.mw + bc * p.mw_sb + h * p.mw_sh +
                                             static_cast<long long>(min(row, Sq - 1)) * p.mw_row);
-      if (nt > 0) mnext = __ldg(mrow);
+      if (nt > 0) mnext = __ldg(mrow + tile_of(0));
     }
-    for (int j = 0; j < nt; ++j) {
+    for (int j = 0; j < nt; ++j) {  // j counts visited tiles (tile_of(j) is the key tile)
       uint32_t mbits[4] = {mnext.x, mnext.y, mnext.z, mnext.w};
       bool apply_bits = false;
       if constexpr (MASKW) {
-        if (j + 1 < nt) mnext = __ldg(mrow + j + 1);
+        if (j + 1 < nt) mnext = __ldg(mrow + tile_of(j + 1));
         apply_bits = !__all_sync(0xffffffffu, (mbits[0] & mbits[1] & mbits[2] & mbits[3]) == 0xffffffffu);
       }
       ok = mbar_wait_warp(bar(B_SREADY + hf), j & 1, ctl, 5);

@@ -3,9 +3,11 @@
 // along each key row (`words_t`, read by the dK / dV kernel, whose threads own key rows). Bit c % 32 of
 // word c / 32 is key (query) c; rows are padded with zero bits to whole 128-wide tiles, so a tile's four
 // words never run past a row and padded keys / queries are hidden without a length check.
-// Same word format as the reference's packing (src/kohakufa/mask.py:32-72); the reference's per-tile
-// any / all classes and tile lists (mask.py:74-122) are not built: every key tile is visited, and a
-// warp whose 128 x 32 bits are all set skips the masking code.
+// Same word format as the reference's packing (src/kohakufa/mask.py:32-72). Instead of the reference's
+// per-tile any / all classes and host-built tile lists (mask.py:74-122) the packing marks, in one int per
+// (128 queries x 128 keys) tile, whether the tile holds any visible pair; every CTA builds the list of
+// tiles it visits from that table in shared memory, and a warp whose bits are all set skips the masking
+// code.
 // Included at the end of kfa_api.cu (uses its helpers).
 #pragma once
 
@@ -16,7 +18,7 @@ namespace kfa {
 __global__ void __launch_bounds__(128) kfa_pack_mask_kernel(const uint8_t* mask, long long m_sb, long long m_sh,
                                                             long long m_sr, long long m_sc, int Hm, int Sq, int Skv,
                                                             int* words, int wq /*ints per row of words*/, int* words_t,
-                                                            int wk /*ints per row of words_t*/) {
+                                                            int wk /*ints per row of words_t*/, int* tiles) {
   __shared__ uint8_t tile[4][32][33];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int cb = blockIdx.x * 4 + warp;  // 32-key block
@@ -37,6 +39,12 @@ __global__ void __launch_bounds__(128) kfa_pack_mask_kernel(const uint8_t* mask,
     }
   }
   __syncwarp();
+  if (live && tiles != nullptr) {  // any bit set in this 32 x 32 block: mark its 128 x 128 tile
+    bool some = false;
+    for (int r = 0; r < 32; ++r) some |= tile[warp][r][lane] != 0;
+    if (__any_sync(0xffffffffu, some) && lane == 0)
+      atomicOr(tiles + (static_cast<long long>(slice) * (wk / 4) + rb / 4) * (wq / 4) + cb / 4, 1);
+  }
   if (live) {
     for (int c = 0; c < 32; ++c) {
       const int key = cb * 32 + c;
@@ -58,7 +66,7 @@ __global__ void kfa_zero_words_kernel(int* words, long long rows, int width, int
 }  // namespace kfa
 
 extern "C" int kfa_pack_mask(const void* mask, const int64_t* mask_stride, int mask_batch, int mask_heads, int Sq,
-                             int Skv, int32_t* words, int32_t* words_t, void* stream) {
+                             int Skv, int32_t* words, int32_t* words_t, int32_t* tiles, void* stream) {
   if (!mask || !mask_stride || !words || !words_t) return fail(KFA_ERR_ARG, "kfa_pack_mask: null pointer");
   if (mask_batch < 1 || mask_heads < 1 || Sq < 1 || Skv < 1) return fail(KFA_ERR_ARG, "kfa_pack_mask: empty mask");
   const int wq = 4 * ((Skv + 127) / 128), wk = 4 * ((Sq + 127) / 128);
@@ -68,7 +76,7 @@ extern "C" int kfa_pack_mask(const void* mask, const int64_t* mask_stride, int m
   dim3 grid((wq + 3) / 4, (Sq + 31) / 32, slices);
   kfa::kfa_pack_mask_kernel<<<grid, 128, 0, s>>>(static_cast<const uint8_t*>(mask), mask_stride[0], mask_stride[1],
                                                  mask_stride[2], mask_stride[3], mask_heads, Sq, Skv, words, wq,
-                                                 words_t, wk);
+                                                 words_t, wk, tiles);
   KFA_CUDA(cudaGetLastError());
   const int written = (Sq + 31) / 32;
   if (wk > written) {

@@ -19,7 +19,7 @@ namespace kfa {
 // Status codes written to the device status word (first failure wins).
 enum : int {
   KFA_DEV_OK = 0,
-  KFA_DEV_TIMEOUT_BASE = 100,  // 100 + id of the wait site that gave up
+  KFA_DEV_TIMEOUT_BASE = 100,  // 100 + id of the wait site that gave up: 1-9 forward, 11-19 dK/dV, 21-29 dQ kernel
 };
 
 #ifndef KFA_WAIT_CYCLES

@@ -4,8 +4,9 @@ padded with zero bits to whole 128-wide tiles.
 
 Same interface and word format as the reference's ``PackedMask`` / ``pack_mask`` (KohakuFA
 ``src/kohakufa/mask.py:13-128``); the packing is one CUDA kernel of ``libkfa.so`` (``kfa_pack_mask``)
-instead of a Triton kernel, and the reference's tile classes / tile lists are not built (the kernels
-visit every key tile and skip the masking code where a warp's bits are all set).
+instead of a Triton kernel. In place of the reference's tile classes and host-built tile lists
+(mask.py:74-122) the packing fills a table with one int per (128 queries x 128 keys) tile, nonzero where
+the tile holds a visible pair; the kernels list the tiles they visit from it and skip the rest.
 """
 
 import ctypes
@@ -36,8 +37,8 @@ def words_per_row(n: int) -> int:
 
 
 class PackedMask:
-    """A boolean mask packed once for the kernels (words and transposed words), reusable across calls
-    with the same mask and shape (e.g. every layer of a model)."""
+    """A boolean mask packed once for the kernels (words, transposed words, table of non-empty tiles),
+    reusable across calls with the same mask and shape (e.g. every layer of a model)."""
 
     def __init__(self, mask: Tensor, batch: int, heads: int, s_q: int, s_kv: int) -> None:
         dense = normalize(mask, batch, heads, s_q, s_kv)
@@ -47,13 +48,14 @@ class PackedMask:
         bm, hm = dense.shape[:2]
         self.words = torch.empty(bm, hm, s_q, words_per_row(s_kv), dtype=torch.int32, device=dense.device)
         self.words_t = torch.empty(bm, hm, s_kv, words_per_row(s_q), dtype=torch.int32, device=dense.device)
+        self.tiles = torch.zeros(bm, hm, -(-s_q // TILE), -(-s_kv // TILE), dtype=torch.int32, device=dense.device)
         lib = _lib.load()
         bytes_ = dense.view(torch.uint8)
         strides = (ctypes.c_int64 * 4)(*bytes_.stride())
         with torch.cuda.device(dense.device):
             rc = lib.kfa_pack_mask(
                 bytes_.data_ptr(), strides, bm, hm, s_q, s_kv, self.words.data_ptr(), self.words_t.data_ptr(),
-                _lib.stream_ptr(dense.device),
+                self.tiles.data_ptr(), _lib.stream_ptr(dense.device),
             )  # fmt: skip
         _lib.check(rc)
 
@@ -72,4 +74,14 @@ def mask_words(words: Tensor, batch: int, heads: int) -> "_lib.KfaMaskWords":
     d.stride_batch = words.stride(0) if words.shape[0] > 1 else 0
     d.stride_head = words.stride(1) if words.shape[1] > 1 else 0
     d.stride_row = words.stride(2)
+    return d
+
+
+def mask_tiles(tiles: Tensor) -> "_lib.KfaMaskTiles":
+    """The library's descriptor of the tile table ``[Bm, Hm, ceil(Sq / 128), ceil(Skv / 128)]``."""
+    assert tiles.dtype == torch.int32 and tiles.dim() == 4 and tiles.is_contiguous()
+    d = _lib.KfaMaskTiles()
+    d.any = tiles.data_ptr()
+    d.stride_batch = tiles.stride(0) if tiles.shape[0] > 1 else 0
+    d.stride_head = tiles.stride(1) if tiles.shape[1] > 1 else 0
     return d

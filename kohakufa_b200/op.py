@@ -154,8 +154,10 @@ attention_fwd_op.register_autograd(_backward, setup_context=_setup_context)
 
 
 @torch.library.custom_op("kohakufa_b200::sm100_masked_forward", mutates_args=(), device_types="cuda")
-def masked_fwd_op(q: Tensor, k: Tensor, v: Tensor, words: Tensor, words_t: Tensor, scale: float) -> tuple[Tensor, Tensor]:
-    from kohakufa_b200.mask import mask_words
+def masked_fwd_op(
+    q: Tensor, k: Tensor, v: Tensor, words: Tensor, words_t: Tensor, tiles: Tensor, scale: float
+) -> tuple[Tensor, Tensor]:
+    from kohakufa_b200.mask import mask_tiles, mask_words
 
     lib = _lib.load()
     batch, heads, seq_q, _ = q.shape
@@ -166,6 +168,7 @@ def masked_fwd_op(q: Tensor, k: Tensor, v: Tensor, words: Tensor, words_t: Tenso
             *(ctypes.byref(_lib.tensor4(t)) for t in (q, k, v, out)),
             lse.data_ptr(),
             ctypes.byref(mask_words(words, batch, heads)),
+            ctypes.byref(mask_tiles(tiles)),
             float(scale),
             _lib.dtype_code(q.dtype),
             _lib.status_word(q.device).data_ptr(),
@@ -176,7 +179,7 @@ def masked_fwd_op(q: Tensor, k: Tensor, v: Tensor, words: Tensor, words_t: Tenso
 
 
 @masked_fwd_op.register_fake
-def _(q, k, v, words, words_t, scale):
+def _(q, k, v, words, words_t, tiles, scale):
     batch, heads, seq_q, dim = q.shape
     return q.new_empty(batch, seq_q, heads, dim).transpose(1, 2), q.new_empty(batch, heads, 2, seq_q, dtype=torch.float32)
 
@@ -184,9 +187,9 @@ def _(q, k, v, words, words_t, scale):
 @torch.library.custom_op("kohakufa_b200::sm100_masked_backward", mutates_args=(), device_types="cuda")
 def masked_bwd_op(
     q: Tensor, k: Tensor, v: Tensor, out: Tensor, dout: Tensor, lse: Tensor, words: Tensor, words_t: Tensor,
-    scale: float,
+    tiles: Tensor, scale: float,
 ) -> tuple[Tensor, Tensor, Tensor]:  # fmt: skip
-    from kohakufa_b200.mask import mask_words
+    from kohakufa_b200.mask import mask_tiles, mask_words
 
     lib = _lib.load()
     batch, heads, seq_q, _ = q.shape
@@ -200,6 +203,7 @@ def masked_bwd_op(
             *(ctypes.byref(_lib.tensor4(t)) for t in (dq, dk, dv)),
             ctypes.byref(mask_words(words, batch, heads)),
             ctypes.byref(mask_words(words_t, batch, heads)),
+            ctypes.byref(mask_tiles(tiles)),
             float(scale),
             _lib.dtype_code(q.dtype),
             _lib.status_word(q.device).data_ptr(),
@@ -210,24 +214,24 @@ def masked_bwd_op(
 
 
 @masked_bwd_op.register_fake
-def _(q, k, v, out, dout, lse, words, words_t, scale):
+def _(q, k, v, out, dout, lse, words, words_t, tiles, scale):
     return _bshd_like(q), _bshd_like(k), _bshd_like(v)
 
 
 def _masked_setup(ctx, inputs, output):
-    q, k, v, words, words_t, scale = inputs
+    q, k, v, words, words_t, tiles, scale = inputs
     out, lse = output
-    ctx.save_for_backward(q, k, v, out, lse, words, words_t)
+    ctx.save_for_backward(q, k, v, out, lse, words, words_t, tiles)
     ctx.scale = scale
     ctx.mark_non_differentiable(lse)
 
 
 def _masked_backward(ctx, dout, dlse):
-    q, k, v, out, lse, words, words_t = ctx.saved_tensors
+    q, k, v, out, lse, words, words_t, tiles = ctx.saved_tensors
     if not _strides_ok(dout):
         dout = dout.contiguous()
-    dq, dk, dv = masked_bwd_op(q, k, v, out, dout, lse, words, words_t, ctx.scale)
-    return dq, dk, dv, None, None, None
+    dq, dk, dv = masked_bwd_op(q, k, v, out, dout, lse, words, words_t, tiles, ctx.scale)
+    return dq, dk, dv, None, None, None, None
 
 
 masked_fwd_op.register_autograd(_masked_backward, setup_context=_masked_setup)
@@ -257,7 +261,7 @@ def attention(
         packed = mask if isinstance(mask, PackedMask) else PackedMask(mask, *shape)
         if packed.shape != shape:
             raise ValueError(f"packed mask for {packed.shape}, inputs are {shape}")
-        out, _ = masked_fwd_op(q, k, v, packed.words, packed.words_t, float(scale))
+        out, _ = masked_fwd_op(q, k, v, packed.words, packed.words_t, packed.tiles, float(scale))
         return out
     out, _ = attention_fwd_op(q, k, v, float(scale), int(block_causal))
     return out

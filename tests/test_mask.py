@@ -62,6 +62,51 @@ def test_pack_mask_words():
 
     assert torch.equal(unpack(packed.words, 517), mask)
     assert torch.equal(unpack(packed.words_t, 269), mask.transpose(-1, -2))
+    assert packed.tiles.shape == (2, 3, 3, 5) and bool((packed.tiles != 0).all())  # dense random mask: no empty tile
+
+
+def structured_mask(kind, s_q, s_kv):
+    r = torch.arange(s_q, device="cuda")[:, None]
+    c = torch.arange(s_kv, device="cuda")[None, :]
+    if kind == "window":  # sliding window of 200 keys behind the diagonal
+        return (c <= r) & (c > r - 200)
+    if kind == "block_diagonal":  # documents of 300 tokens
+        return (r // 300) == (c // 300)
+    if kind == "prefix":  # everybody sees the first 100 keys, plus its own 128-block
+        return (c < 100) | ((r // 128) == (c // 128))
+    if kind == "last_rows_blind":  # the last 300 query rows see nothing
+        return (r < s_q - 300) & (c <= r)
+    raise ValueError(kind)
+
+
+@pytest.mark.parametrize("kind", ["window", "block_diagonal", "prefix", "last_rows_blind"])
+@pytest.mark.parametrize("dim,heads,kv_heads", [(64, 2, 2), (128, 4, 2)])
+def test_mask_with_empty_tiles(kind, dim, heads, kv_heads):
+    """Masks with whole 128 x 128 tiles hidden: the kernels skip them (table of non-empty tiles) and give
+    the same result as the oracle, which sees the dense mask."""
+    s_q, s_kv = 1100, 1300
+    mask = structured_mask(kind, s_q, s_kv)
+    packed = pack_mask(mask, 1, heads, s_q, s_kv)
+    dense_any = torch.nn.functional.pad(mask, (0, -s_kv % 128, 0, -s_q % 128)).reshape(9, 128, 11, 128).any(3).any(1)
+    assert torch.equal(packed.tiles[0, 0] != 0, dense_any) and not bool(dense_any.all())
+    q, k, v, dout = inputs(1, heads, s_q, s_kv, dim=dim, kv_heads=kv_heads)
+    got = run(q, k, v, dout, mask=packed)
+    check(got, oracle.attention_fp64(q, k, v, dout, dim**-0.5, mask=mask, groups=heads // kv_heads))
+    if kind == "last_rows_blind":
+        assert float(got[0].detach()[:, :, -300:].abs().max()) == 0.0 and float(got[1][:, :, -300:].abs().max()) == 0.0
+
+
+def test_skipping_tiles_does_not_change_the_bits():
+    """The same mask with and without the tile table: identical results (hidden tiles contribute exact
+    zeros when they are visited)."""
+    mask = structured_mask("window", 1100, 1300)
+    q, k, v, dout = inputs(2, 2, 1100, 1300)
+    packed = pack_mask(mask, 2, 2, 1100, 1300)
+    a = run(q, k, v, dout, mask=packed)
+    packed.tiles.fill_(1)  # visit everything
+    b = run(q, k, v, dout, mask=packed)
+    for name, x, y in zip(("out", "dq", "dk", "dv"), a, b):
+        assert torch.equal(x, y), name
 
 
 @pytest.mark.parametrize(
