@@ -36,6 +36,34 @@ def words_per_row(n: int) -> int:
     return 4 * (-(-n // TILE))
 
 
+@torch.library.custom_op("kohakufa_b200::pack_mask", mutates_args=(), device_types="cuda")
+def pack_mask_op(mask: Tensor, s_q: int, s_kv: int) -> tuple[Tensor, Tensor, Tensor]:
+    """words, words_t, tiles of a ``[Bm, Hm, Sq, Skv]`` bool mask (True = visible), any strides."""
+    mask_bytes = mask.view(torch.uint8)
+    bm, hm = mask_bytes.shape[:2]
+    dev = mask_bytes.device
+    words = torch.empty(bm, hm, s_q, words_per_row(s_kv), dtype=torch.int32, device=dev)
+    words_t = torch.empty(bm, hm, s_kv, words_per_row(s_q), dtype=torch.int32, device=dev)
+    tiles = torch.zeros(bm, hm, -(-s_q // TILE), -(-s_kv // TILE), dtype=torch.int32, device=dev)
+    lib = _lib.load()
+    strides = (ctypes.c_int64 * 4)(*mask_bytes.stride())
+    with torch.cuda.device(dev):
+        rc = lib.kfa_pack_mask(
+            mask_bytes.data_ptr(), strides, bm, hm, s_q, s_kv, words.data_ptr(), words_t.data_ptr(),
+            tiles.data_ptr(), _lib.stream_ptr(dev),
+        )  # fmt: skip
+    _lib.check(rc)
+    return words, words_t, tiles
+
+
+@pack_mask_op.register_fake
+def _(mask, s_q, s_kv):
+    bm, hm = mask.shape[:2]
+    new = lambda *shape: mask.new_empty(*shape, dtype=torch.int32)  # noqa: E731
+    return (new(bm, hm, s_q, words_per_row(s_kv)), new(bm, hm, s_kv, words_per_row(s_q)),
+            new(bm, hm, -(-s_q // TILE), -(-s_kv // TILE)))  # fmt: skip
+
+
 class PackedMask:
     """A boolean mask packed once for the kernels (words, transposed words, table of non-empty tiles),
     reusable across calls with the same mask and shape (e.g. every layer of a model)."""
@@ -45,19 +73,7 @@ class PackedMask:
         if not dense.is_cuda:
             raise ValueError("mask: a CUDA tensor (there is no CPU path)")
         self.shape = (batch, heads, s_q, s_kv)
-        bm, hm = dense.shape[:2]
-        self.words = torch.empty(bm, hm, s_q, words_per_row(s_kv), dtype=torch.int32, device=dense.device)
-        self.words_t = torch.empty(bm, hm, s_kv, words_per_row(s_q), dtype=torch.int32, device=dense.device)
-        self.tiles = torch.zeros(bm, hm, -(-s_q // TILE), -(-s_kv // TILE), dtype=torch.int32, device=dense.device)
-        lib = _lib.load()
-        bytes_ = dense.view(torch.uint8)
-        strides = (ctypes.c_int64 * 4)(*bytes_.stride())
-        with torch.cuda.device(dense.device):
-            rc = lib.kfa_pack_mask(
-                bytes_.data_ptr(), strides, bm, hm, s_q, s_kv, self.words.data_ptr(), self.words_t.data_ptr(),
-                self.tiles.data_ptr(), _lib.stream_ptr(dense.device),
-            )  # fmt: skip
-        _lib.check(rc)
+        self.words, self.words_t, self.tiles = pack_mask_op(dense, s_q, s_kv)
 
 
 def pack_mask(mask: Tensor, batch: int, heads: int, s_q: int, s_kv: int) -> PackedMask:

@@ -208,3 +208,7 @@ def test_mask_compiled_and_all_visible_equals_dense():
         assert torch.equal(a, b)
     fn = torch.compile(lambda q, k, v: attention(q, k, v, mask=packed), fullgraph=True)
     assert torch.equal(fn(q, k, v), masked[0])
+    # a bool mask given directly: the packing is a custom op too, so this traces as well
+    ones = torch.ones(300, 300, dtype=torch.bool, device="cuda")
+    fn2 = torch.compile(lambda q, k, v, m: attention(q, k, v, mask=m), fullgraph=True)
+    assert torch.equal(fn2(q, k, v, ones), masked[0])
