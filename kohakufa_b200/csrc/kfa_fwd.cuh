@@ -12,7 +12,12 @@
 //   warp  9     TMA producer (one thread): Q halves once, K_j / V_j through a ring
 //
 //   TMEM columns: S0 [0,128)  S1 [128,256)  O0 [256,256+D)  O1 [256+D,256+2D).
-//   P_h (16-bit) overwrites the first 64 columns of S_h and is the A operand of O_h += P V.
+//   A key tile's 128 score columns are produced and consumed as two parts of 64 keys: S_h part p sits in
+//   columns 64p..64p+63 of S_h, its P (16-bit) overwrites the first 32 of them and is the A operand of
+//   O_h += P V for those 64 keys. As soon as that MMA is issued the next tile's scores of the same part
+//   follow into the same columns, while the softmax warpgroup works on the other part: neither waits for
+//   a whole tile of the other. (The 64-column score MMAs run at 2/3 of the tensor core's rate, because both
+//   operands stream from shared memory; the key loop was bound by the hand-offs, not by the tensor core.)
 //
 // Numerics kept from the reference (docs/precision.md:17-114; fwd.py:785-790, 905-924, 1029-1038):
 //   * the exponent is shift-then-scale, exp2((S - m) * c): the row's largest P is exactly 1;
@@ -110,12 +115,12 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   constexpr int B_QREADY = 0;             // 2
   constexpr int B_KVREADY = 2;            // NS
   constexpr int B_KVFREE = 2 + NS;        // NS
-  constexpr int B_SREADY = 2 + 2 * NS;    // 2
-  constexpr int B_PREADY = 4 + 2 * NS;    // 2
-  constexpr int B_OFINAL = 6 + 2 * NS;    // 2
-  constexpr int B_DRAIN = 8 + 2 * NS;     // 1
-  constexpr int B_PLO = 9 + 2 * NS;       // 2: first 64 keys of P_h stored, O_h rescaled
-  constexpr int N_BARS = 11 + 2 * NS;
+  constexpr int B_SREADY = 2 + 2 * NS;    // 4: [half][part] the 64 score columns of that part are in TMEM
+  constexpr int B_PREADY = 6 + 2 * NS;    // 4: [half][part] the 64 keys of P_h of that part stored, O_h rescaled
+  constexpr int B_OFINAL = 10 + 2 * NS;   // 2
+  constexpr int B_DRAIN = 12 + 2 * NS;    // 1
+  constexpr int B_PVDONE = 13 + 2 * NS;   // 4: [half][part] that part of O_h += P V has retired
+  constexpr int N_BARS = 17 + 2 * NS;
   static_assert(N_BARS * 8 + 16 <= 256, "barrier block too small");
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + N_BARS);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
@@ -169,12 +174,12 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       mbar_init(bar(B_KVREADY + i), 1);
       mbar_init(bar(B_KVFREE + i), 1);
     }
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < 4; ++i) {
       mbar_init(bar(B_SREADY + i), 1);
       mbar_init(bar(B_PREADY + i), 128);
-      mbar_init(bar(B_OFINAL + i), 1);
-      mbar_init(bar(B_PLO + i), 128);
     }
+    for (int i = 0; i < 2; ++i) mbar_init(bar(B_OFINAL + i), 1);
+    for (int i = 0; i < 4; ++i) mbar_init(bar(B_PVDONE + i), 1);
     mbar_init(bar(B_DRAIN), 1);
     // An earlier failure (status word already set): allocate, skip the work, free.
     *s_abort = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
@@ -271,27 +276,29 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     // The whole warp runs this role converged; one elected lane issues the tcgen05 instructions.
     {
       const bool lead = elect_one();
-      constexpr uint32_t IDESC_S = make_idesc(BF16, false, 128, 128);
+      constexpr uint32_t IDESC_S = make_idesc(BF16, false, 128, 64);
       constexpr uint32_t IDESC_O = make_idesc(BF16, true, 128, D);
       const uint32_t tmS[2] = {tmem + Cfg::TM_S0, tmem + Cfg::TM_S1};
       const uint32_t tmO[2] = {tmem + Cfg::TM_O0, tmem + Cfg::TM_O1};
       const uint32_t q_lo[2] = {sdesc_lo(sQ, 16), sdesc_lo(sQ + Cfg::TILE_BYTES, 16)};
       bool ok = true;
 
-      auto issue_S = [&](int hf, int stage) {
-        const uint32_t k_lo = sdesc_lo(sKV + stage * Cfg::TILE_BYTES, 16);
+      // S_h of the 64 keys of one part (rows 64 part .. of the K tile) into columns 64 part .. of S_h
+      auto issue_S = [&](int hf, int stage, int part) {
+        const uint32_t k_lo = sdesc_lo(sKV + stage * Cfg::TILE_BYTES + part * (TILE_BYTES_64 / 2), 16);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = ((kk >> 2) * TILE_BYTES_64 + (kk & 3) * 32) >> 4;
-          umma_ss_lead(lead, tmS[hf], q_lo[hf] + off, k_lo + off, IDESC_S, kk > 0 ? 1u : 0u);
+          umma_ss_lead(lead, tmS[hf] + 64 * part, q_lo[hf] + off, k_lo + off, IDESC_S, kk > 0 ? 1u : 0u);
         }
       };
-      auto issue_PV = [&](int hf, int stage, bool acc, int part) {  // part: keys [64 part, 64 part + 64)
+      // O_h += P V over the 64 keys of one part; its 16-bit P sits in the first 32 columns of the part
+      auto issue_PV = [&](int hf, int stage, bool acc, int part) {
         const uint32_t v_lo = sdesc_lo(sKV + stage * Cfg::TILE_BYTES, TILE_BYTES_64);
 #pragma unroll
         for (int k4 = 0; k4 < 4; ++k4) {
           const int kk = part * 4 + k4;
-          umma_ts_lead(lead, tmO[hf], tmS[hf] + kk * 8, v_lo + ((kk * 2048) >> 4), IDESC_O,
+          umma_ts_lead(lead, tmO[hf], tmS[hf] + 64 * part + k4 * 8, v_lo + ((kk * 2048) >> 4), IDESC_O,
                        (acc || kk > 0) ? 1u : 0u);
         }
       };
@@ -299,58 +306,60 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         return mbar_wait_warp(bar(B_KVREADY + idx % NS), (idx / NS) & 1, ctl, 2);
       };
 
-      // S(0) for both halves
+      // S(0), both parts, for both halves
       ok = kv_wait(0);
       for (int hf = 0; hf < 2 && ok; ++hf) {
         if (n_tiles[hf] == 0) continue;
         ok = mbar_wait_warp(bar(B_QREADY + hf), 0, ctl, 3);
         if (!ok) break;
         tc_fence_after();
-        KFA_PROF_BEGIN();
-        issue_S(hf, 0);
-        KFA_PROF_END(7);
-        umma_commit_lead(lead, bar(B_SREADY + hf));
+        for (int part = 0; part < 2; ++part) {
+          issue_S(hf, 0, part);
+          umma_commit_lead(lead, bar(B_SREADY + 2 * hf + part));
+        }
       }
       if (ok) umma_commit_lead(lead, bar(B_KVFREE + 0));
 
+      // Per key tile and 64-key part, for each half: O_h += P V of the part, then the next tile's
+      // scores of the same part overwrite it. The other part of S_h is untouched meanwhile, so the
+      // softmax of one part runs while the tensor core works on the other.
       for (int j = 0; j < n_max && ok; ++j) {
         const int iv = 2 * j + 1;  // V_j
         const int ik = 2 * j + 2;  // K_{j+1}
         const bool more = (j + 1 < n_max);
+        KFA_PROF_BEGIN();
         ok = kv_wait(iv);
         if (!ok) break;
         if (more) {
           ok = kv_wait(ik);
           if (!ok) break;
         }
-        for (int hf = 0; hf < 2 && ok; ++hf) {
-          if (j < n_tiles[hf]) {
-            ok = mbar_wait_warp(bar(B_PLO + hf), j & 1, ctl, 4);
-            if (!ok) break;
-            tc_fence_after();
-            issue_PV(hf, iv % NS, j > 0, 0);
-            ok = mbar_wait_warp(bar(B_PREADY + hf), j & 1, ctl, 4);
-            if (!ok) break;
-            tc_fence_after();
-            issue_PV(hf, iv % NS, j > 0, 1);
-            KFA_PROF_BEGIN();
-            if (j == n_tiles[hf] - 1) umma_commit_lead(lead, bar(B_OFINAL + hf));
-            KFA_PROF_END(5);
+        KFA_PROF_END(5);
+        for (int part = 0; part < 2 && ok; ++part) {
+          for (int hf = 0; hf < 2 && ok; ++hf) {
+            if (j < n_tiles[hf]) {
+              KFA_PROF_BEGIN();
+              ok = mbar_wait_warp(bar(B_PREADY + 2 * hf + part), j & 1, ctl, 4);
+              if (!ok) break;
+              tc_fence_after();
+              KFA_PROF_END(3);
+              KFA_PROF_BEGIN();
+              issue_PV(hf, iv % NS, j > 0, part);
+              umma_commit_lead(lead, bar(B_PVDONE + 2 * hf + part));
+              if (part == 1 && j == n_tiles[hf] - 1) umma_commit_lead(lead, bar(B_OFINAL + hf));
+              KFA_PROF_END(7);
+            }
+            if (more && j + 1 < n_tiles[hf]) {
+              KFA_PROF_BEGIN();
+              issue_S(hf, ik % NS, part);
+              umma_commit_lead(lead, bar(B_SREADY + 2 * hf + part));
+              KFA_PROF_END(6);
+            }
           }
-          KFA_PROF_BEGIN();
-          if (hf == 1) umma_commit_lead(lead, bar(B_KVFREE + iv % NS));
-          KFA_PROF_END(5);
-          if (more && j + 1 < n_tiles[hf]) {
-            KFA_PROF_BEGIN();
-            issue_S(hf, ik % NS);
-            KFA_PROF_END(7);
-            KFA_PROF_BEGIN();
-            umma_commit_lead(lead, bar(B_SREADY + hf));
-            KFA_PROF_END(6);
-          }
-          KFA_PROF_BEGIN();
-          if (more && hf == 1) umma_commit_lead(lead, bar(B_KVFREE + ik % NS));
-          KFA_PROF_END(6);
+        }
+        if (ok) {
+          umma_commit_lead(lead, bar(B_KVFREE + iv % NS));
+          if (more) umma_commit_lead(lead, bar(B_KVFREE + ik % NS));
         }
       }
       // Everything issued has to retire before TMEM is freed.
@@ -385,6 +394,14 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                                             static_cast<long long>(min(row, Sq - 1)) * p.mw_row);
       if (nt > 0) mnext = __ldg(mrow + tile_of(0));
     }
+#ifdef KFA_FWD_STAGGER
+    if (hf == 1) {  // start the second half later, so that the halves' exponent phases alternate
+      const long long ts = clock64();
+      while (clock64() - ts < KFA_FWD_STAGGER) {
+      }
+      __syncwarp();
+    }
+#endif
     for (int j = 0; j < nt; ++j) {  // j counts visited tiles (tile_of(j) is the key tile)
       uint32_t mbits[4] = {mnext.x, mnext.y, mnext.z, mnext.w};
       bool apply_bits = false;
@@ -392,93 +409,60 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         if (j + 1 < nt) mnext = __ldg(mrow + tile_of(j + 1));
         apply_bits = !__all_sync(0xffffffffu, (mbits[0] & mbits[1] & mbits[2] & mbits[3]) == 0xffffffffu);
       }
-      ok = mbar_wait_warp(bar(B_SREADY + hf), j & 1, ctl, 5);
-      if (!ok) break;
-      tc_fence_after();
       const bool masked = (j >= nu);
-      const int lim = my_limit - j * 128;
-      float s[128];
-      // ---- pass 1: row max (the values are read again below, which keeps the registers free
-      //      for the O rescale in between; TMEM reads are cheap) ----
-      KFA_PROF_BEGIN();
-      tmem_ld32(tS + 0, reinterpret_cast<uint32_t*>(s));
-      tmem_ld32(tS + 32, reinterpret_cast<uint32_t*>(s + 32));
-      tmem_ld32(tS + 64, reinterpret_cast<uint32_t*>(s + 64));
-      tmem_ld32(tS + 96, reinterpret_cast<uint32_t*>(s + 96));
-      tmem_wait_ld();
-      if constexpr (MASKW) {
-        if (apply_bits) {
+      // The tile's 128 keys are handled as two parts of 64 with their own score columns, so that the
+      // tensor core refills one part while this thread works on the other.
 #pragma unroll
-          for (int i = 0; i < 128; ++i)
-            if (!((mbits[i >> 5] >> (i & 31)) & 1u)) s[i] = -INFINITY;
+      for (int part = 0; part < 2; ++part) {
+        KFA_PROF_BEGIN();
+        ok = mbar_wait_warp(bar(B_SREADY + 2 * hf + part), j & 1, ctl, 5);
+        if (!ok) break;
+        tc_fence_after();
+        KFA_PROF_END(6);
+        const uint32_t tSp = tS + 64 * part;
+        const int lim = my_limit - j * 128 - 64 * part;
+        float s[64];
+        KFA_PROF_BEGIN();
+        tmem_ld32(tSp, reinterpret_cast<uint32_t*>(s));
+        tmem_ld32(tSp + 32, reinterpret_cast<uint32_t*>(s + 32));
+        tmem_wait_ld();
+        if constexpr (MASKW) {
+          if (apply_bits) {
+#pragma unroll
+            for (int i = 0; i < 64; ++i)
+              if (!((mbits[2 * part + (i >> 5)] >> (i & 31)) & 1u)) s[i] = -INFINITY;
+          }
+        } else if (masked) {
+#pragma unroll
+          for (int i = 0; i < 64; ++i)
+            if (i >= lim) s[i] = -INFINITY;
         }
-      } else if (masked) {
+        float mx0 = fmaxf(s[0], s[1]), mx1 = fmaxf(s[2], s[3]), mx2 = fmaxf(s[4], s[5]), mx3 = fmaxf(s[6], s[7]);
 #pragma unroll
-        for (int i = 0; i < 128; ++i)
-          if (i >= lim) s[i] = -INFINITY;
-      }
-      float mx0 = fmaxf(s[0], s[1]), mx1 = fmaxf(s[2], s[3]), mx2 = fmaxf(s[4], s[5]), mx3 = fmaxf(s[6], s[7]);
-#pragma unroll
-      for (int i = 8; i < 128; i += 8) {  // pairs of maxima: three-input max instructions
-        mx0 = fmaxf(mx0, fmaxf(s[i], s[i + 1]));
-        mx1 = fmaxf(mx1, fmaxf(s[i + 2], s[i + 3]));
-        mx2 = fmaxf(mx2, fmaxf(s[i + 4], s[i + 5]));
-        mx3 = fmaxf(mx3, fmaxf(s[i + 6], s[i + 7]));
-      }
-      const float m_new = fmaxf(fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)), m);
-      // A row that has seen no key yet (boolean masks only) shifts by 0: its exponents stay -inf, P = 0.
-      const float m_shift = (MASKW && m_new == -INFINITY) ? 0.f : m_new;
-      // Shift first, then scale: the largest exponent of the row is exactly 0.
-      const float alpha = ex2(__fmul_rn(__fsub_rn(m, m_shift), c));
-      m = m_new;
-      KFA_PROF_END(7);
-      // ---- exact rescale of O whenever any row of this warp moved its max. S_h(j) being ready
-      //      implies O_h += P V of tile j-1 has retired (commits cover all earlier MMAs). ----
-      KFA_PROF_BEGIN();
-      if (j > 0 && !__all_sync(0xffffffffu, alpha == 1.0f)) {
-        const float2 a2 = make_float2(alpha, alpha);
-#pragma unroll
-        for (int c0 = 0; c0 < D; c0 += 64) {
-          float2 o[32];
-          tmem_ld32(tO + c0, reinterpret_cast<uint32_t*>(o));
-          tmem_ld32(tO + c0 + 32, reinterpret_cast<uint32_t*>(o + 16));
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __fmul2_rn(o[i], a2);
-          tmem_st32(tO + c0, reinterpret_cast<const uint32_t*>(o));
-          tmem_st32(tO + c0 + 32, reinterpret_cast<const uint32_t*>(o + 16));
+        for (int i = 8; i < 64; i += 8) {  // pairs of maxima: three-input max instructions
+          mx0 = fmaxf(mx0, fmaxf(s[i], s[i + 1]));
+          mx1 = fmaxf(mx1, fmaxf(s[i + 2], s[i + 3]));
+          mx2 = fmaxf(mx2, fmaxf(s[i + 4], s[i + 5]));
+          mx3 = fmaxf(mx3, fmaxf(s[i + 6], s[i + 7]));
         }
-      }
-      // ---- pass 2: the exponentials ----
-      tmem_ld32(tS + 0, reinterpret_cast<uint32_t*>(s));
-      tmem_ld32(tS + 32, reinterpret_cast<uint32_t*>(s + 32));
-      tmem_ld32(tS + 64, reinterpret_cast<uint32_t*>(s + 64));
-      tmem_ld32(tS + 96, reinterpret_cast<uint32_t*>(s + 96));
-      tmem_wait_ld();
-      KFA_PROF_END(9);
-      KFA_PROF_BEGIN();
-      if constexpr (MASKW) {
-        if (apply_bits) {
+        const float m_new = fmaxf(fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)), m);
+        // A row that has seen no key yet (boolean masks only) shifts by 0: its exponents stay -inf, P = 0.
+        const float m_shift = (MASKW && m_new == -INFINITY) ? 0.f : m_new;
+        // Shift first, then scale: the largest exponent of the row is exactly 0.
+        const float alpha = ex2(__fmul_rn(__fsub_rn(m, m_shift), c));
+        m = m_new;
+        KFA_PROF_END(7);
+        // ---- the exponentials ----
+        KFA_PROF_BEGIN();
+        const float2 neg_m = make_float2(-m_shift, -m_shift);
+        const float2 c2 = make_float2(c, c);
+        float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
+        const float2* s2 = reinterpret_cast<const float2*>(s);
+        uint32_t pk[32];
 #pragma unroll
-          for (int i = 0; i < 128; ++i)
-            if (!((mbits[i >> 5] >> (i & 31)) & 1u)) s[i] = -INFINITY;
-        }
-      } else if (masked) {
-#pragma unroll
-        for (int i = 0; i < 128; ++i)
-          if (i >= lim) s[i] = -INFINITY;
-      }
-      const float2 neg_m = make_float2(-m_shift, -m_shift);
-      const float2 c2 = make_float2(c, c);
-      float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
-      const float2* s2 = reinterpret_cast<const float2*>(s);
-#pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; i += 2) {
-          const float2 x0 = __fmul2_rn(__fadd2_rn(s2[g * 16 + i], neg_m), c2);
-          const float2 x1 = __fmul2_rn(__fadd2_rn(s2[g * 16 + i + 1], neg_m), c2);
+        for (int i = 0; i < 32; i += 2) {
+          const float2 x0 = __fmul2_rn(__fadd2_rn(s2[i], neg_m), c2);
+          const float2 x1 = __fmul2_rn(__fadd2_rn(s2[i + 1], neg_m), c2);
           const float2 p0 = make_float2(ex2(x0.x), ex2(x0.y));
           const float2 p1 = make_float2(ex2(x1.x), ex2(x1.y));
           la = __fadd2_rn(la, p0);
@@ -486,18 +470,39 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           pk[i] = pack16<BF16>(p0.x, p0.y);
           pk[i + 1] = pack16<BF16>(p1.x, p1.y);
         }
-        tmem_st16(tS + g * 16, pk);  // P over the S columns already read
-        if (g == 1) {  // the first 64 keys of P (and the rescaled O) are in place: O += P V may start
-          tmem_wait_st();
-          tc_fence_before();
-          mbar_arrive(bar(B_PLO + hf));
+        tmem_st32(tSp, pk);  // P of this part over its own score columns, already in registers
+        KFA_PROF_END(8);
+        // ---- exact rescale of O whenever any row of this warp moved its max; every part of
+        //      O_h += P V issued so far has to have retired first (they had the exponent loop's
+        //      time to do so: the wait is normally over at once) ----
+        KFA_PROF_BEGIN();
+        // (Only a warp that rescales waits: the barrier of the previous part cannot run two phases
+        //  ahead of this thread, since the part after the next needs this thread's P.)
+        if ((j > 0 || part > 0) && !__all_sync(0xffffffffu, alpha == 1.0f)) {
+          const int prev = 2 * j + part - 1;  // the part issued before this one
+          ok = mbar_wait_warp(bar(B_PVDONE + 2 * hf + (prev & 1)), (prev >> 1) & 1, ctl, 7);
+          if (!ok) break;
+          tc_fence_after();
+          {
+            const float2 a2 = make_float2(alpha, alpha);
+#pragma unroll
+            for (int c0 = 0; c0 < D; c0 += 32) {  // (32 columns at a time: the scores stay in registers)
+              float2 o[16];
+              tmem_ld32(tO + c0, reinterpret_cast<uint32_t*>(o));
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 16; ++i) o[i] = __fmul2_rn(o[i], a2);
+              tmem_st32(tO + c0, reinterpret_cast<const uint32_t*>(o));
+            }
+          }
         }
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar(B_PREADY + 2 * hf + part));
+        l = l * alpha + ((la.x + la.y) + (lb.x + lb.y));
+        KFA_PROF_END(9);
       }
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(bar(B_PREADY + hf));
-      l = l * alpha + ((la.x + la.y) + (lb.x + lb.y));
-      KFA_PROF_END(8);
+      if (!ok) break;
     }
     // ---- epilogue ----
     if (nt > 0) ok = mbar_wait_warp(bar(B_OFINAL + hf), 0, ctl, 6) && ok;
