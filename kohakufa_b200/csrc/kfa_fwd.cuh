@@ -394,14 +394,6 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                                             static_cast<long long>(min(row, Sq - 1)) * p.mw_row);
       if (nt > 0) mnext = __ldg(mrow + tile_of(0));
     }
-#ifdef KFA_FWD_STAGGER
-    if (hf == 1) {  // start the second half later, so that the halves' exponent phases alternate
-      const long long ts = clock64();
-      while (clock64() - ts < KFA_FWD_STAGGER) {
-      }
-      __syncwarp();
-    }
-#endif
     for (int j = 0; j < nt; ++j) {  // j counts visited tiles (tile_of(j) is the key tile)
       uint32_t mbits[4] = {mnext.x, mnext.y, mnext.z, mnext.w};
       bool apply_bits = false;
