@@ -193,8 +193,21 @@ def config_dict(cfg, n_gpus):
             if cfg.name.startswith("C5") and n_gpus > 1
             else f"batch x heads sharding over {n_gpus} GPU(s), no communication"
         ),
-        "l2": "inputs larger than L2 (4 x 268 MB per step at C3); no flush needed",
+        "l2": l2_note(cfg),
     }
+
+
+def l2_note(cfg):
+    """How the timed steps relate to the 126 MB L2 (inputs of one step: q, k, v, dout)."""
+    mb = 4 * cfg.batch * cfg.heads * cfg.seq * cfg.dim * 2 / 1e6
+    if mb > 126:
+        return f"inputs larger than L2 (4 tensors, {mb:.0f} MB per step); no flush needed"
+    return f"inputs {mb:.1f} MB per step fit in L2 and are not flushed: a launch-bound parity configuration, not a roofline one"
+
+
+# The reference's own published fwd+bwd TFLOP/s for a configuration's exact shape, where there is one
+# (on B300, its only published hardware: benchmarks/results/speed.csv:202-203).
+PUBLISHED = {"C4": 763.0}
 
 
 def main():
@@ -331,7 +344,7 @@ def main():
         "ms_per_step": ms_per_step,
         "higher_is_better": True,
         "scaling": "strong" if ring_mode else "weak",
-        "vs_baseline": None,
+        "vs_baseline": (value / world / PUBLISHED[cfg.name]) if cfg.name in PUBLISHED else None,
         "dtype": "bf16" if cfg.dtype == torch.bfloat16 else "fp16",
         "data": "synthetic",
         "config": config_dict(cfg, world),
