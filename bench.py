@@ -58,8 +58,22 @@ class ClockSampler:
         self.index = index
         self.rows = []
         self.proc = None
+        self.first = 0  # rows before this index were sampled before the timed region began
+
+    def wait_running(self, timeout=5.0):
+        """Blocks until nvidia-smi has delivered its first row (it can take longer to start than a short
+        timed region lasts), then marks where the region's own samples begin."""
+        t0 = time.perf_counter()
+        while self.proc is not None and not self.rows and time.perf_counter() - t0 < timeout:
+            time.sleep(0.02)
+        self.first = len(self.rows)
+
+    def samples_under_load(self):
+        return len(self.rows) - self.first
 
     def __enter__(self):
+        if self.index < 0:  # only rank 0 samples (its own GPU)
+            return self
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
@@ -89,7 +103,7 @@ class ClockSampler:
     def summary(self):
         clocks, reasons, max_mhz = [], set(), None
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for row in self.rows:
+        for row in self.rows[self.first :]:
             if len(row) < 7:
                 continue
             try:
@@ -289,7 +303,8 @@ def main():
 
     # ---- timed region: exactly K steps, device time, max over ranks ----
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as sampler:
+    with ClockSampler(local if rank == 0 else -1) as sampler:
+        sampler.wait_running()
         barrier()
         start.record()
         for _ in range(args.steps):
@@ -298,6 +313,12 @@ def main():
         barrier()
         # per-kernel device times, same workload, still inside the sampled region
         kernel_ms = time_kernels(cfg, q, k, v, dout, args.steps)
+        # a short timed region can end before nvidia-smi's next sample: keep the same load running
+        # (untimed) until three samples under load exist, for at most 1.5 s
+        t_extra = time.perf_counter()
+        while rank == 0 and not ring_mode and sampler.samples_under_load() < 3 and time.perf_counter() - t_extra < 1.5:
+            step()
+            torch.cuda.synchronize()
     ms = start.elapsed_time(stop)
     if world > 1:
         t = torch.tensor([ms], device=dev)

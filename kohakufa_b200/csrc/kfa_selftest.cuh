@@ -211,10 +211,120 @@ int selftest_one(std::string& rep) {
 
 }  // namespace
 
+namespace kfa {
+
+// The fragment-shaped TMEM accesses of the dK / dV kernel against the one-lane-per-thread shape:
+// a pattern stored with st.32x32b is read back with ld.16x256b.x8, and a pattern stored with
+// st.16x128b.x8 / .x4 is read back with ld.32x32b. The host checks the documented element maps.
+__global__ void __launch_bounds__(128, 1) kfa_selftest_frag_kernel(uint32_t* out_ld, uint32_t* out_st) {
+  __shared__ uint32_t s_tmem;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (warp == 0) {
+    tmem_alloc(smem_u32(&s_tmem), 128);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s_tmem;
+  const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+  uint32_t v[32];
+  for (int c0 = 0; c0 < 64; c0 += 32) {  // lane = tid, columns 0..63: value = lane * 1000 + column
+    for (int i = 0; i < 32; ++i) v[i] = tid * 1000 + c0 + i;
+    tmem_st32(tmem + lane_base + c0, v);
+  }
+  tmem_wait_st();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  for (int half = 0; half < 2; ++half) {
+    tmem_ld_16x256b_x8(tmem + lane_base + (static_cast<uint32_t>(16 * half) << 16), v);
+    tmem_wait_ld();
+    for (int i = 0; i < 32; ++i) out_ld[((warp * 2 + half) * 32 + lane) * 32 + i] = v[i];
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  for (int half = 0; half < 2; ++half) {  // columns 64..95 by one x8 store, 96..127 by two x4 stores
+    uint32_t w[16];
+    for (int i = 0; i < 16; ++i) w[i] = (half << 16) | (lane << 8) | i;
+    const uint32_t base = tmem + lane_base + (static_cast<uint32_t>(16 * half) << 16);
+    tmem_st_16x128b_x8(base + 64, w);
+    tmem_st_16x128b_x4(base + 96, w);
+    tmem_st_16x128b_x4(base + 112, w + 8);
+  }
+  tmem_wait_st();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  for (int c0 = 64; c0 < 128; c0 += 32) {
+    tmem_ld32(tmem + lane_base + c0, v);
+    tmem_wait_ld();
+    for (int i = 0; i < 32; ++i) out_st[tid * 64 + (c0 - 64) + i] = v[i];
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 128);
+  }
+}
+
+}  // namespace kfa
+
+namespace {
+
+int selftest_frag(std::string& rep) {
+  uint32_t *d_ld = nullptr, *d_st = nullptr;
+  const size_t n_ld = 4 * 2 * 32 * 32, n_st = 128 * 64;
+  if (cudaMalloc(&d_ld, n_ld * 4) != cudaSuccess || cudaMalloc(&d_st, n_st * 4) != cudaSuccess) {
+    cudaFree(d_ld);
+    return fail(KFA_ERR_CUDA, "selftest: cudaMalloc failed");
+  }
+  kfa::kfa_selftest_frag_kernel<<<1, 128>>>(d_ld, d_st);
+  std::vector<uint32_t> h_ld(n_ld), h_st(n_st);
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaMemcpy(h_ld.data(), d_ld, n_ld * 4, cudaMemcpyDeviceToHost);
+  if (e == cudaSuccess) e = cudaMemcpy(h_st.data(), d_st, n_st * 4, cudaMemcpyDeviceToHost);
+  cudaFree(d_ld);
+  cudaFree(d_st);
+  if (e != cudaSuccess) return fail(KFA_ERR_CUDA, "selftest fragments: %s", cudaGetErrorString(e));
+  int bad_ld = 0, bad_st = 0;
+  // ld.16x256b.x8: r[4j + q] = (lane l/4 + 8 (q >= 2), column 8j + 2 (l % 4) + (q & 1))
+  for (int w = 0; w < 4; ++w)
+    for (int half = 0; half < 2; ++half)
+      for (int l = 0; l < 32; ++l)
+        for (int i = 0; i < 32; ++i) {
+          const int j = i / 4, q = i % 4;
+          const uint32_t row = w * 32 + half * 16 + l / 4 + (q >= 2 ? 8 : 0), col = 8 * j + 2 * (l % 4) + (q & 1);
+          bad_ld += h_ld[((w * 2 + half) * 32 + l) * 32 + i] != row * 1000 + col;
+        }
+  // st.16x128b: r[2j + s] -> (lane l/4 + 8 s, column 4j + l % 4), columns counted from the store's address
+  for (int t = 0; t < 128; ++t)
+    for (int c = 0; c < 64; ++c) {
+      const int half = (t % 32) / 16, r16 = t % 16;
+      const int cc = c < 32 ? c : (c < 48 ? c - 32 : c - 48);  // column inside its store
+      const int reg0 = c < 32 ? 0 : (c < 48 ? 0 : 8);          // first register of its store
+      const uint32_t want = (half << 16) | (((r16 % 8) * 4 + cc % 4) << 8) | (reg0 + 2 * (cc / 4) + (r16 >= 8 ? 1 : 0));
+      bad_st += h_st[t * 64 + c] != want;
+    }
+  char line[160];
+  snprintf(line, sizeof(line), "tmem fragments: ld.16x256b %s, st.16x128b %s\n", bad_ld ? "differ" : "exact",
+           bad_st ? "differ" : "exact");
+  rep += line;
+  return (bad_ld || bad_st) ? KFA_ERR_SELFTEST : KFA_OK;
+}
+
+}  // namespace
+
 extern "C" int kfa_selftest(char* report, int report_len) {
   std::string rep;
   const int r1 = selftest_one<false>(rep);
-  const int r2 = (r1 == KFA_ERR_CUDA) ? r1 : selftest_one<true>(rep);
+  int r2 = (r1 == KFA_ERR_CUDA) ? r1 : selftest_one<true>(rep);
+  if (r2 != KFA_ERR_CUDA) {
+    const int r3 = selftest_frag(rep);
+    if (r3) r2 = r3;
+  }
   if (report && report_len > 0) {
     std::strncpy(report, rep.c_str(), report_len - 1);
     report[report_len - 1] = 0;
