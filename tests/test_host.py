@@ -184,3 +184,46 @@ def test_fake_kernels_infer_layouts():
         assert lse.shape == (2, 3, 2, 10) and lse.dtype == torch.float32
         dq, dk, dv = torch.ops.kohakufa_b200.sm100_backward(q, k, k, out, out, lse, 0.125, 0)
         assert dq.shape == q.shape and dk.shape == k.shape and dv.stride() == k.stride()
+
+
+def test_bench_clock_sampler_with_a_fake_nvidia_smi(tmp_path, monkeypatch):
+    """ClockSampler parses nvidia-smi rows, keeps only the rows sampled after wait_running(), and reports
+    throttle reasons; nvidia-smi is replaced by a script that prints rows like the real one."""
+    import importlib
+    import os
+    import stat
+    import time
+
+    fake = tmp_path / "nvidia-smi"
+    fake.write_text(
+        "#!/bin/sh\n"
+        "echo '1965, 1965, 150.0, Not Active, Not Active, Not Active, Not Active'\n"
+        "sleep 0.3\n"
+        "while true; do echo '1700, 1965, 990.0, Not Active, Not Active, Not Active, Active'; sleep 0.05; done\n"
+    )
+    fake.chmod(fake.stat().st_mode | stat.S_IEXEC)
+    monkeypatch.setenv("PATH", f"{tmp_path}{os.pathsep}{os.environ['PATH']}")
+    bench = importlib.import_module("bench")
+    with bench.ClockSampler(0) as sampler:
+        sampler.wait_running()
+        assert sampler.first == 1  # the idle row came before the timed region
+        t0 = time.perf_counter()
+        while sampler.samples_under_load() < 3 and time.perf_counter() - t0 < 5:
+            time.sleep(0.05)
+    out = sampler.summary()
+    assert out["sm_mhz"] == 1700.0 and out["sm_max_mhz"] == 1965.0 and out["reasons"] == ["sw_power_cap"]
+    assert out["samples"] >= 3
+    assert bench.ClockSampler(-1).summary()["samples"] == 0
+
+
+def test_bench_notes():
+    import importlib
+
+    bench = importlib.import_module("bench")
+    from kohakufa_b200 import workloads
+
+    assert "larger than L2" in bench.l2_note(workloads.CONFIGS["C3"])
+    assert "fit in L2" in bench.l2_note(workloads.CONFIGS["C1"])
+    assert set(bench.PUBLISHED) == {"C4"}
+    d = bench.config_dict(workloads.CONFIGS["C5"], 8)
+    assert "ring over 8 GPUs" in d["parallelism"] and d["global_batch"] == 1
