@@ -159,7 +159,7 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, co
 }
 
 // ----------------------------------------------------------------------------------
-// TMA (tiled tensor loads, plain bulk loads). No multicast anywhere.
+// TMA (tiled tensor loads, plain bulk loads), each into this CTA's own shared memory only.
 // ----------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
                                             int c0, int c1, int c2, int c3) {
