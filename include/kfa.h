@@ -83,6 +83,22 @@ int kfa_bwd(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const
             const KfaTensor4* dk, const KfaTensor4* dv, float scale, int block, int dtype,
             int* dev_status, void* stream);
 
+/* Backward as ONE main kernel (dK, dV and dQ from one P and one dS per tile pair, five matrix products
+ * instead of the seven of kfa_bwd), the way the reference's backward works: replaces
+ * attention_backward (bwd.py:1413-1482) with its fp32 dQ accumulator (bwd.py:1135-1232 reduce partition,
+ * 1391-1410 _dq_convert_kernel). Three launches in stream order: statistics + zero-fill of the
+ * accumulator, the fused kernel (dQ tiles are added to the accumulator with fp32 reduce-adds), conversion
+ * of the accumulator to 16-bit dq. dK and dV are bit-identical to kfa_bwd's; dQ is identical up to the
+ * order of its fp32 additions, which varies from run to run (use kfa_bwd where bit-reproducible
+ * gradients are required).
+ * `stats`: kfa_bwd_stats_bytes(B, H, Sq) bytes; `dq_acc`: kfa_bwd_dq_acc_bytes(B, H, Sq, D) bytes
+ * (fp32, whole 128-row tiles: 4 * D bytes per padded query row), 16-byte aligned; both are scratch. */
+int64_t kfa_bwd_dq_acc_bytes(int64_t B, int64_t H, int64_t Sq, int64_t D);
+int kfa_bwd_fused(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* out,
+                  const KfaTensor4* dout, const float* lse, float* stats, float* dq_acc, const KfaTensor4* dq,
+                  const KfaTensor4* dk, const KfaTensor4* dv, float scale, int block, int dtype,
+                  int* dev_status, void* stream);
+
 /* Packed variable-length batches. Replace attention_forward_varlen (fwd.py:1277-1320) and
  * attention_backward_varlen (bwd.py:1591-1647); the reference's host-built tile tables (fwd.py:1265-1274,
  * bwd.py:1559-1588) are not needed: the kernels read the sequence boundaries themselves.
@@ -210,6 +226,16 @@ int kfa_cp_bwd_dq_step(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor
 
 /* grad = acc rounded to 16 bits. */
 int kfa_cp_grad_finalize(const KfaAcc32* acc, const KfaTensor4* grad, int dtype, void* stream);
+
+/* Diagnostic: the raw scores Q K^T (unscaled, unmasked) as fp32 [B, H, Sq, Skv] (contiguous), produced by
+ * the same tensor-core instruction sequence the attention kernels use (one fp32-accumulating MMA per 16
+ * elements of the head dim, in ascending order). What comes out is NOT the correctly rounded dot
+ * product: the tensor core sums the products of a step with a truncating adder, a few units in the last
+ * place away. tests/ use it to compute the accuracy floor of a kernel whose scores come from this
+ * hardware. No counterpart in the reference, whose emulation assumes correctly rounded fp32 scores
+ * (benchmarks/dinov3_backward.py:236). k may have fewer heads than q (grouped-query attention). */
+int kfa_scores(const KfaTensor4* q, const KfaTensor4* k, float* scores, int dtype, int* dev_status,
+               void* stream);
 
 /* Hardware self-check of the building blocks (TMA tile load, MMA from shared memory, MMA with a
  * tensor-memory operand, tensor-memory loads / stores) on small fixed matrices. Synchronises.

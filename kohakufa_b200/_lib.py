@@ -25,6 +25,8 @@ SYMBOLS = (
     "kfa_bwd_dkdv",
     "kfa_bwd_dq",
     "kfa_bwd",
+    "kfa_bwd_dq_acc_bytes",
+    "kfa_bwd_fused",
     "kfa_bwd_static_scratch",
     "kfa_fwd_varlen",
     "kfa_bwd_varlen",
@@ -36,6 +38,7 @@ SYMBOLS = (
     "kfa_cp_bwd_dkdv_step",
     "kfa_cp_bwd_dq_step",
     "kfa_cp_grad_finalize",
+    "kfa_scores",
     "kfa_selftest",
 )
 
@@ -108,6 +111,9 @@ def load() -> ctypes.CDLL:
         lib.kfa_bwd_dkdv.argtypes = [T, T, T, T, fp, T, T, ctypes.c_float, ctypes.c_int, ctypes.c_int, ip, vp]
         lib.kfa_bwd_dq.argtypes = [T, T, T, T, fp, T, ctypes.c_float, ctypes.c_int, ctypes.c_int, ip, vp]
         lib.kfa_bwd.argtypes = [T, T, T, T, T, fp, fp, T, T, T, ctypes.c_float, ctypes.c_int, ctypes.c_int, ip, vp]
+        lib.kfa_bwd_dq_acc_bytes.restype = ctypes.c_int64
+        lib.kfa_bwd_dq_acc_bytes.argtypes = [ctypes.c_int64] * 4
+        lib.kfa_bwd_fused.argtypes = [T, T, T, T, T, fp, fp, fp, T, T, T, ctypes.c_float, ctypes.c_int, ctypes.c_int, ip, vp]
         lib.kfa_bwd_static_scratch.argtypes = [T, T, T, T, T, fp, T, T, T, ctypes.c_float, ctypes.c_int, ctypes.c_int, ip, vp]
         A = ctypes.POINTER(KfaAcc32)
         i64, f32, i32 = ctypes.c_int64, ctypes.c_float, ctypes.c_int
@@ -123,9 +129,11 @@ def load() -> ctypes.CDLL:
         lib.kfa_cp_bwd_dkdv_step.argtypes = [T, T, T, T, fp, i64, A, A, i32, f32, i32, i32, ip, vp]
         lib.kfa_cp_bwd_dq_step.argtypes = [T, T, T, T, fp, i64, A, i32, f32, i32, i32, ip, vp]
         lib.kfa_cp_grad_finalize.argtypes = [A, T, i32, vp]
+        lib.kfa_scores.argtypes = [T, T, fp, i32, ip, vp]
         lib.kfa_selftest.argtypes = [ctypes.c_char_p, ctypes.c_int]
-        for name in SYMBOLS[3:]:
-            getattr(lib, name).restype = ctypes.c_int
+        for name in SYMBOLS:
+            if name not in ("kfa_abi_version", "kfa_last_error", "kfa_bwd_stats_bytes", "kfa_bwd_dq_acc_bytes"):
+                getattr(lib, name).restype = ctypes.c_int
         if lib.kfa_abi_version() != ABI_VERSION:
             raise KfaError(f"libkfa ABI {lib.kfa_abi_version()} != expected {ABI_VERSION}: rebuild")
         _lib = lib
@@ -178,6 +186,46 @@ def device_status(device=None) -> int:
 def reset_device_status(device=None) -> None:
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     status_word(device).zero_()
+
+
+def check_status(device=None) -> None:
+    """Raises ``KfaError`` if a kernel on ``device`` (default: the current one) gave up on an internal
+    wait since the last ``reset_status``.
+
+    The kernels never hang: a wait that exceeds its (seconds-long) limit makes the CTA fill the output
+    rows it owns with NaN, record ``100 + wait id`` in a per-device status word and leave; every later
+    launch on that device then skips its work and leaves its outputs as NaN as well. Nothing on the
+    launch path reads the word back (that would synchronise), so call this where the program
+    synchronises anyway, e.g. after ``loss.item()`` or the optimizer step: NaN gradients plus a nonzero
+    status mean "a kernel timed out", not "the model diverged". Reads one int from the device."""
+    code = device_status(device)
+    if code != 0:
+        raise KfaError(
+            f"a libkfa kernel timed out waiting on its pipeline (status {code} = 100 + wait id); outputs since then "
+            "are NaN. Call reset_status() to re-enable the kernels"
+        )
+
+
+def reset_status(device=None) -> None:
+    """Clears the device's status word (see ``check_status``) so that later launches do their work again."""
+    reset_device_status(device)
+
+
+def raw_scores(q: torch.Tensor, k: torch.Tensor) -> torch.Tensor:
+    """``q k^T`` (unscaled, unmasked) as fp32 ``[B, H, Sq, Skv]``, straight from the tensor-core instruction
+    sequence the attention kernels use (``kfa_scores``): a diagnostic for accuracy studies."""
+    out = torch.empty(q.shape[0], q.shape[1], q.shape[2], k.shape[2], dtype=torch.float32, device=q.device)
+    with torch.cuda.device(q.device):
+        rc = load().kfa_scores(
+            ctypes.byref(tensor4(q)),
+            ctypes.byref(tensor4(k)),
+            out.data_ptr(),
+            dtype_code(q.dtype),
+            status_word(q.device).data_ptr(),
+            stream_ptr(q.device),
+        )
+    check(rc)
+    return out
 
 
 def stream_ptr(device: torch.device) -> int:

@@ -1,56 +1,64 @@
-"""Public entry point: argument handling and dispatch to the kernels.
+"""``attention`` and ``attention_varlen``: the calls a user of the package makes.
 
-Same signature, defaults, casts and exceptions as the reference's ``kohakufa.attention``
-(KohakuFA ``src/kohakufa/api.py:56-111``); the compute behind it is ``libkfa.so``.
+They take the arguments, defaults and error conditions of the reference's entry points
+(KohakuFA ``src/kohakufa/api.py:56-146``), turn them into what the kernels understand (a frame size,
+a 16-bit compute dtype, a head dim the kernels are built for) and hand over to the custom ops in
+``kohakufa_b200.op``, which launch ``libkfa.so``. Nothing is computed here except the optional
+key centring, which is a handful of fp32 torch reductions.
 """
 
 import torch
 from torch import Tensor
 
-from kohakufa_b200.op import KERNEL_DIMS, MAX_KERNEL_DIM
-from kohakufa_b200.op import attention as _sm100_attention
-from kohakufa_b200.op import attention_varlen as _sm100_attention_varlen
-from kohakufa_b200.op import varlen_plan  # noqa: F401 (re-exported)
+from kohakufa_b200 import op as _op
+from kohakufa_b200.op import varlen_plan  # noqa: F401  (part of the public surface)
 
 COMPUTE_DTYPES = (torch.float16, torch.bfloat16)
-MAX_HEAD_DIM = MAX_KERNEL_DIM
+MAX_HEAD_DIM = _op.MAX_KERNEL_DIM
 
 
-def _pad_head_dim(q: Tensor, k: Tensor, v: Tensor) -> tuple[Tensor, Tensor, Tensor]:
-    """Any head dim up to MAX_HEAD_DIM: the kernels are built for 64 and 128, so pad the last dim
-    up to one with zeros (zero columns change neither q . k nor the output's first D columns; the
-    caller keeps the scale of the real D and slices the output). The reference pads to multiples
-    of 16 (api.py:18-29); the rule is the same, the granularity coarser."""
-    dim = q.shape[-1]
-    if dim > MAX_HEAD_DIM or dim < 1:
+def _frame_size(causal: bool, block_causal: int) -> int:
+    """The one integer the kernels mask by: 0 dense, 1 token-causal, P frames of P tokens."""
+    if causal and block_causal not in (0, 1):
+        raise ValueError("causal is block_causal=1: give one of them")
+    return 1 if causal else int(block_causal)
+
+
+def _fit_head_dim(*tensors: Tensor) -> tuple[Tensor, ...]:
+    """Zero-extends the last dimension to the next head dim a kernel exists for.
+
+    Added zero columns contribute nothing to ``q . k``, and the output columns they produce are
+    sliced away by the caller, which also keeps the softmax scale of the true head dim, so the
+    result is exact (the reference widens the same way, api.py:18-29)."""
+    dim = tensors[0].shape[-1]
+    if not 1 <= dim <= MAX_HEAD_DIM:
         raise ValueError(f"head_dim {dim}: 1 .. {MAX_HEAD_DIM} supported")
-    if dim in KERNEL_DIMS:
-        return q, k, v
-    padded = min(d for d in KERNEL_DIMS if d >= dim)
-    return tuple(torch.nn.functional.pad(t, (0, padded - dim)) for t in (q, k, v))
+    target = _op.kernel_dim_for(dim)
+    if target == dim:
+        return tensors
+    return tuple(torch.nn.functional.pad(t, (0, target - dim)) for t in tensors)
 
 
-def _centered(k: Tensor, mean: Tensor, dtype: torch.dtype) -> Tensor:
-    """``k - mean`` in fp32, rounded once to ``dtype``."""
-    return (k.float() - mean).to(dtype)
+def _remove_key_mean(k: Tensor, dtype: torch.dtype, cu_seqlens: Tensor | None = None) -> Tensor:
+    """``k`` minus the average key of its sequence, computed in fp32 and rounded once to ``dtype``.
 
+    Every score of a query row then moves by one common amount, which softmax ignores, so outputs
+    are unchanged while the large component all keys share never reaches the 16-bit rounding;
+    autograd routes ``-mean(dK)`` back (reference api.py:32-53).
 
-def _center_keys(k: Tensor, dtype: torch.dtype) -> Tensor:
-    """Subtracts the fp32 mean over keys of each (batch, K / V head) (reference api.py:37-43).
-    Exact: every logit of a query row moves by the same amount, which the softmax drops, and dK
-    picks up ``- mean(dK')`` through autograd."""
-    return _centered(k, k.float().mean(-2, keepdim=True), dtype)
-
-
-def _center_keys_varlen(k: Tensor, cu_seqlens_k: Tensor) -> Tensor:
-    """``_center_keys`` per packed sequence (``k [Tk, Hkv, D]``), without host syncs (reference
-    api.py:46-53): the fp32 mean of each sequence's keys is subtracted from them."""
-    rows = torch.arange(k.shape[0], device=k.device)
-    seq = torch.searchsorted(cu_seqlens_k[1:].contiguous(), rows, right=True)
+    Dense input ``[B, Hkv, Skv, D]``: one average per (batch, head), over dim -2. Packed input
+    ``[Tk, Hkv, D]`` with ``cu_seqlens``: one average per (sequence, head); sequence membership of a
+    row is derived on the device, so no length is read back to the host."""
     k32 = k.float()
-    sums = k32.new_zeros(cu_seqlens_k.numel() - 1, *k.shape[1:]).index_add_(0, seq, k32)
-    counts = (cu_seqlens_k[1:] - cu_seqlens_k[:-1]).clamp(min=1).float()
-    return _centered(k, (sums / counts[:, None, None])[seq], k.dtype)
+    if cu_seqlens is None:
+        return (k32 - k32.mean(dim=-2, keepdim=True)).to(dtype)
+    lengths = cu_seqlens[1:] - cu_seqlens[:-1]
+    owner = torch.repeat_interleave(
+        torch.arange(lengths.numel(), device=k.device), lengths.long(), output_size=k.shape[0]
+    )
+    totals = k32.new_zeros(lengths.numel(), *k.shape[1:]).index_add_(0, owner, k32)
+    mean = totals / lengths.clamp(min=1).to(torch.float32).view(-1, 1, 1)
+    return (k32 - mean[owner]).to(dtype)
 
 
 def attention(
@@ -65,44 +73,44 @@ def attention(
     compute_dtype: torch.dtype | None = None,
     center_keys: bool = False,
 ) -> Tensor:
-    """``softmax(scale q k^T) v``.
+    """Scaled dot-product attention, forward and (through autograd) backward, on the B200 kernels.
 
-    Args:
-        q: ``[B, H, Sq, D]``; k, v: ``[B, H, Skv, D]``. Views of ``[B, S, H, D]`` projections are
-            fine (any strides, contiguous last dim, 16-byte aligned).
-        causal: query ``r`` sees keys ``0..r`` (top-left aligned when ``Sq != Skv``).
-        block_causal: frame size ``P > 0``: query ``r`` sees keys of frames up to its own,
-            ``c // P <= r // P``. ``causal`` is ``block_causal=1``.
-        scale: softmax scale, ``D ** -0.5`` by default.
-        mask: bool, broadcastable to ``[B, H, Sq, Skv]``, True = visible, or a ``pack_mask(...)``
-            result to reuse one packing across calls (exclusive with ``causal`` / ``block_causal``:
-            fold them into the mask). A query row with no visible key outputs 0.
-        compute_dtype: tensor-core operand dtype; inputs of another dtype (e.g. fp32) are cast.
-            Defaults to the inputs' dtype if it is fp16 / bf16, else fp16.
-        center_keys: subtract the mean key (over keys, per batch and head, in fp32) before the
-            single cast to ``compute_dtype``. Exact (softmax is shift-invariant per row).
+    ``q`` is ``[B, H, Sq, D]``; ``k`` and ``v`` are ``[B, Hkv, Skv, D]`` where ``Hkv`` divides ``H``
+    (each K / V head serves ``H // Hkv`` consecutive query heads). Transposed views of
+    ``[B, S, H, D]`` projections are taken as they are: only the last dim must be contiguous and
+    the other strides 16-byte multiples.
 
-    Returns ``[B, H, Sq, D]`` in the inputs' dtype (a view of ``[B, Sq, H, D]`` storage).
+    Visibility, one of:
+      * nothing: every query sees every key;
+      * ``causal=True``: query ``r`` sees keys ``0 .. r`` (rows and columns both count from 0 when
+        ``Sq != Skv``);
+      * ``block_causal=P``: tokens come in frames of ``P``; a query sees the keys of its own and of
+        earlier frames (``c // P <= r // P``). ``causal`` is the case ``P = 1``;
+      * ``mask``: a bool tensor that broadcasts to ``[B, H, Sq, Skv]`` (True = visible), or the result
+        of ``pack_mask`` to pay for the packing once. Cannot be combined with the two above. A query
+        with no visible key gets a zero output row and zero gradients.
+
+    ``scale`` defaults to ``D ** -0.5`` of the head dim passed in. ``compute_dtype`` is the 16-bit
+    dtype the tensor cores see; inputs of another dtype are cast to it (fp16 unless they already are
+    fp16 / bf16) and the result is cast back. ``center_keys`` subtracts each (batch, head)'s mean key
+    in fp32 before that cast (see ``_remove_key_mean``): same function, better conditioned.
+
+    Returns ``[B, H, Sq, D]`` in the dtype of ``q``, laid out as ``[B, Sq, H, D]`` in memory.
     """
-    if causal and block_causal not in (0, 1):
-        raise ValueError("causal is block_causal=1: give one of them")
-    block = 1 if causal else int(block_causal)
+    frame = _frame_size(causal, block_causal)
     if compute_dtype is None:
         compute_dtype = q.dtype if q.dtype in COMPUTE_DTYPES else torch.float16
     if compute_dtype not in COMPUTE_DTYPES:
         raise TypeError(f"compute_dtype {compute_dtype}: one of {COMPUTE_DTYPES}")
-    in_dtype = q.dtype
+    result_dtype, head_dim = q.dtype, q.shape[-1]
     if center_keys:
-        k = _center_keys(k, compute_dtype)
-    q, k, v = (t.to(compute_dtype) for t in (q, k, v))
-    dim = q.shape[-1]
-    if scale is None:
-        scale = dim**-0.5
-    q, k, v = _pad_head_dim(q, k, v)
-    if mask is not None and block:
+        k = _remove_key_mean(k, compute_dtype)
+    q, k, v = _fit_head_dim(*(t.to(compute_dtype) for t in (q, k, v)))
+    if mask is not None and frame:
         raise ValueError("give a mask or causal / block_causal, not both (fold them in)")
-    out = _sm100_attention(q, k, v, scale, block, mask)[..., :dim]
-    return out if out.dtype == in_dtype else out.to(in_dtype)
+    softmax_scale = head_dim**-0.5 if scale is None else scale
+    out = _op.attention(q, k, v, softmax_scale, frame, mask)[..., :head_dim]
+    return out.to(result_dtype) if out.dtype != result_dtype else out
 
 
 def attention_varlen(
@@ -118,21 +126,28 @@ def attention_varlen(
     plan: tuple | None = None,
     center_keys: bool = False,
 ) -> Tensor:
-    """Variable-length attention over packed sequences, each its own problem (no padding computed):
-    ``q [Tq, H, D]``, ``k / v [Tk, Hkv, D]`` (fp16 / bf16), sequence ``b`` at rows
-    ``cu_seqlens[b] : cu_seqlens[b + 1]`` (int32 [B + 1]). ``causal`` / ``block_causal`` apply within
-    each sequence. ``plan``: ``varlen_plan(cu_seqlens_q, cu_seqlens_k, H, Hkv, block)``, built once per
-    batch of lengths (it reads the lengths on the host), e.g. to keep the call free of host syncs
-    inside a CUDA graph. ``center_keys``: as in ``attention``, with the mean taken per sequence.
-    Same signature and exceptions as the reference's (api.py:114-146)."""
-    if causal and block_causal not in (0, 1):
-        raise ValueError("causal is block_causal=1: give one of them")
-    block = 1 if causal else int(block_causal)
-    dim = q.shape[-1]
-    if scale is None:
-        scale = dim**-0.5
+    """Attention over a packed batch: sequences of different lengths stored back to back, each
+    attended to on its own, with no padding rows computed (reference api.py:114-146).
+
+    ``q`` is ``[Tq, H, D]``, ``k`` / ``v`` are ``[Tk, Hkv, D]`` (fp16 or bf16); int32 ``cu_seqlens_*``
+    of length ``B + 1`` give the row range ``[cu[b], cu[b + 1])`` of sequence ``b``. ``causal`` and
+    ``block_causal`` are applied inside every sequence. ``plan`` is what ``varlen_plan`` returned for
+    these lengths; passing it keeps this call free of device-to-host reads (needed under CUDA-graph
+    capture), otherwise it is built here. ``center_keys`` removes each sequence's own mean key.
+    """
+    frame = _frame_size(causal, block_causal)
+    head_dim = q.shape[-1]
     if center_keys:
-        k = _center_keys_varlen(k, cu_seqlens_k)
-    q, k, v = _pad_head_dim(q, k, v)
-    out = _sm100_attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, scale=scale, block_causal=block, plan=plan)
-    return out[..., :dim]
+        k = _remove_key_mean(k, k.dtype, cu_seqlens_k)
+    q, k, v = _fit_head_dim(q, k, v)
+    out = _op.attention_varlen(
+        q,
+        k,
+        v,
+        cu_seqlens_q,
+        cu_seqlens_k,
+        scale=head_dim**-0.5 if scale is None else scale,
+        block_causal=frame,
+        plan=plan,
+    )
+    return out[..., :head_dim]

@@ -21,9 +21,11 @@ HEADERS = [
     CSRC / "kfa_ptx.cuh",
     CSRC / "kfa_fwd.cuh",
     CSRC / "kfa_bwd.cuh",
+    CSRC / "kfa_bwd_fused.cuh",
     CSRC / "kfa_selftest.cuh",
     CSRC / "kfa_cp.cuh",
     CSRC / "kfa_mask.cuh",
+    CSRC / "kfa_scores.cuh",
     PKG.parent / "include" / "kfa.h",
 ]
 NVCC_FLAGS = [

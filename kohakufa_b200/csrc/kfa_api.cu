@@ -14,6 +14,7 @@
 
 #include "../../include/kfa.h"
 #include "kfa_bwd.cuh"
+#include "kfa_bwd_fused.cuh"
 #include "kfa_fwd.cuh"
 
 namespace {
@@ -356,7 +357,7 @@ int fwd_impl(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, cons
 }
 
 int prepare_impl(const KfaTensor4* out, const KfaTensor4* dout, const float* lse, float* stats, const Varlen* vl,
-                 int dtype, void* stream) {
+                 int dtype, void* stream, float* dq_acc = nullptr) {
   int rc;
   if ((rc = check_tensor(out, "out")) || (rc = check_like(dout, out, "dout"))) return rc;
   if (!lse || !stats) return fail(KFA_ERR_ARG, "lse / stats: null pointer");
@@ -375,6 +376,7 @@ int prepare_impl(const KfaTensor4* out, const KfaTensor4* dout, const float* lse
   p.do_ss = dout->stride[2];
   p.lse = lse;
   p.stats = stats;
+  p.dq_acc = dq_acc;
   p.B = static_cast<int>(out->shape[0]);
   p.H = static_cast<int>(out->shape[1]);
   p.Sq = static_cast<int>(out->shape[2]);
@@ -440,6 +442,56 @@ int dq_impl(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const
   p.dq_ss = dq->stride[2];
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   KFA_DISPATCH(q->shape[3], dtype, (launch_dq<KD, KB>(mq, mk, mv, mdo, p, s)));
+}
+
+
+template <int D, bool BF16>
+int launch_fused(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mdo,
+                 const kfa::BwdParams& p, float* dq_acc, cudaStream_t s) {
+  auto kern = kfa::kfa_bwd_fused_kernel<D, BF16>;
+  constexpr int smem = kfa::FusedCfg<D>::SMEM_BYTES;
+  int rc = set_smem(kern, smem);
+  if (rc) return rc;
+  const long long grid = static_cast<long long>(p.B) * p.Hkv * p.n_k128;
+  if (grid > 0x7fffffffll) return fail(KFA_ERR_ARG, "too many tiles");
+  kern<<<static_cast<unsigned>(grid), kfa::FUSED_THREADS, smem, s>>>(mq, mk, mv, mdo, p, dq_acc);
+  KFA_CUDA(cudaGetLastError());
+  auto conv = kfa::kfa_bwd_dq_convert_kernel<D, BF16>;
+  conv<<<dim3(p.n_q128, p.B * p.H), 256, 0, s>>>(dq_acc, p.dq, p.dq_sb, p.dq_sh, p.dq_ss, p.H, p.Sq, p.scale);
+  KFA_CUDA(cudaGetLastError());
+  return KFA_OK;
+}
+
+int fused_impl(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* dout,
+               const float* stats, float* dq_acc, const KfaTensor4* dq, const KfaTensor4* dk, const KfaTensor4* dv,
+               float scale, int block, int dtype, int* dev_status, void* stream) {
+  int rc;
+  if ((rc = check_qkv(q, k, v, dtype, block)) || (rc = check_like(dout, q, "dout")) || (rc = check_like(dq, q, "dq")) ||
+      (rc = check_like(dk, k, "dk")) || (rc = check_like(dv, v, "dv")))
+    return rc;
+  if (!stats || !dq_acc || !dev_status) return fail(KFA_ERR_ARG, "stats / dq_acc / dev_status: null pointer");
+  if (reinterpret_cast<uintptr_t>(dq_acc) % 16) return fail(KFA_ERR_ARG, "dq_acc: not 16-byte aligned");
+  CUtensorMap mq, mk, mv, mdo;
+  if ((rc = make_map(q, dtype, &mq, "q")) || (rc = make_map(k, dtype, &mk, "k")) ||
+      (rc = make_map(v, dtype, &mv, "v")) || (rc = make_map(dout, dtype, &mdo, "dout")))
+    return rc;
+  kfa::BwdParams p;
+  fill_bwd_params(p, q, k, stats, scale, block, dev_status);
+  if (static_cast<long long>(p.B) * p.H > 65535) return fail(KFA_ERR_ARG, "B * H > 65535");
+  p.dq = dq->ptr;
+  p.dq_sb = dq->stride[0];
+  p.dq_sh = dq->stride[1];
+  p.dq_ss = dq->stride[2];
+  p.dk = dk->ptr;
+  p.dk_sb = dk->stride[0];
+  p.dk_sh = dk->stride[1];
+  p.dk_ss = dk->stride[2];
+  p.dv = dv->ptr;
+  p.dv_sb = dv->stride[0];
+  p.dv_sh = dv->stride[1];
+  p.dv_ss = dv->stride[2];
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  KFA_DISPATCH(q->shape[3], dtype, (launch_fused<KD, KB>(mq, mk, mv, mdo, p, dq_acc, s)));
 }
 
 }  // namespace
@@ -535,6 +587,21 @@ int kfa_bwd(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const
   return kfa_bwd_dq(q, k, v, dout, stats, dq, scale, block, dtype, dev_status, stream);
 }
 
+int64_t kfa_bwd_dq_acc_bytes(int64_t B, int64_t H, int64_t Sq, int64_t D) {
+  return B * H * ((Sq + 127) / 128) * 128 * D * 4;
+}
+
+int kfa_bwd_fused(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* out,
+                  const KfaTensor4* dout, const float* lse, float* stats, float* dq_acc, const KfaTensor4* dq,
+                  const KfaTensor4* dk, const KfaTensor4* dv, float scale, int block, int dtype, int* dev_status,
+                  void* stream) {
+  int rc;
+  if ((rc = check_like(out, q, "out"))) return rc;
+  if (!dq_acc) return fail(KFA_ERR_ARG, "dq_acc: null pointer");
+  if ((rc = prepare_impl(out, dout, lse, stats, nullptr, dtype, stream, dq_acc))) return rc;
+  return fused_impl(q, k, v, dout, stats, dq_acc, dq, dk, dv, scale, block, dtype, dev_status, stream);
+}
+
 }  // extern "C"
 
 // ---------------------------------------------------------------------------------------------
@@ -590,6 +657,7 @@ extern "C" int kfa_bwd_static_scratch(const KfaTensor4* q, const KfaTensor4* k, 
 
 #include "kfa_cp.cuh"
 #include "kfa_mask.cuh"
+#include "kfa_scores.cuh"
 #include "kfa_selftest.cuh"
 
 #ifdef KFA_PROFILE

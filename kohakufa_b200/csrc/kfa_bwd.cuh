@@ -95,6 +95,9 @@ struct PrepParams {
   float* stats;      // [B*H, n_q128, 3, 128]
   int B, H, Sq, n_q128;
   const int* cu_q;  // packed variable-length batches: see BwdParams
+  // Fused backward only (else nullptr): the fp32 dQ accumulator, whole 128-row tiles of D floats per
+  // (batch, head); every CTA zero-fills the tile of its rows.
+  float* dq_acc;
 };
 
 // ---------------------------------------------------------------------------------------
@@ -120,6 +123,11 @@ __global__ void __launch_bounds__(128) kfa_bwd_prepare_kernel(const PrepParams p
   const uint8_t* gb = reinterpret_cast<const uint8_t*>(p.dout) + 2 * (bc * p.do_sb + h * p.do_sh + q_base * p.do_ss);
   float* st = p.stats + (static_cast<long long>(bh) * p.n_q128 + tile) * 384;
   const float* lse = p.lse + (static_cast<long long>(bc) * p.H + h) * 2 * p.Sq + q_base;
+  if (p.dq_acc != nullptr) {
+    float4* acc = reinterpret_cast<float4*>(p.dq_acc + (static_cast<long long>(bh) * p.n_q128 + tile) * (128 * D));
+#pragma unroll 4
+    for (int i = threadIdx.x; i < 128 * D / 4; i += 128) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
   for (int r0 = warp * 32; r0 < warp * 32 + 32; r0 += RPW) {
     const int r_in = r0 + sub;
     const int row = tile * 128 + r_in;

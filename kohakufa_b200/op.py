@@ -25,8 +25,35 @@ from torch import Tensor
 
 from kohakufa_b200 import _lib
 
+import os
+
 KERNEL_DIMS = (64, 128)  # head dims the kernels are built for; the API zero-pads up to one
 MAX_KERNEL_DIM = 128
+
+
+def kernel_dim_for(dim: int) -> int:
+    """The smallest head dim a kernel is built for that holds ``dim``."""
+    return min(d for d in KERNEL_DIMS if d >= dim)
+
+
+# Which backward runs. The fused kernel (one P and one dS per tile pair, dQ accumulated with fp32
+# reduce-adds) is the fast one; its dQ varies in the last bits from run to run because the order of
+# those adds does. The split kernels (dK / dV kernel + dQ kernel that recomputes S and dP) give
+# bit-identical gradients every run at about 1.4x the backward time.
+_deterministic = os.environ.get("KFA_DETERMINISTIC", "0") not in ("", "0")
+
+
+def set_deterministic(flag: bool) -> None:
+    """``True``: every later backward uses the split, bit-reproducible kernels; ``False`` (the default,
+    unless the environment variable ``KFA_DETERMINISTIC`` is set to something other than 0): the fused
+    kernel. Applies to dense / causal / block-causal ``attention``; masks and packed batches always
+    run the split kernels."""
+    global _deterministic
+    _deterministic = bool(flag)
+
+
+def is_deterministic() -> bool:
+    return _deterministic
 
 
 def _strides_ok(t: Tensor) -> bool:
@@ -97,27 +124,25 @@ def attention_bwd_op(
     q: Tensor, k: Tensor, v: Tensor, out: Tensor, dout: Tensor, lse: Tensor, scale: float, block: int
 ) -> tuple[Tensor, Tensor, Tensor]:
     lib = _lib.load()
-    batch, heads, seq_q, _ = q.shape
+    batch, heads, seq_q, dim = q.shape
     dq, dk, dv = _bshd_like(q), _bshd_like(k), _bshd_like(v)
     stats = q.new_empty(lib.kfa_bwd_stats_bytes(batch, heads, seq_q) // 4, dtype=torch.float32)
+    tensors = [ctypes.byref(_lib.tensor4(t)) for t in (q, k, v, out, dout, dq, dk, dv)]
+    tail = (
+        float(scale),
+        int(block),
+        _lib.dtype_code(q.dtype),
+        _lib.status_word(q.device).data_ptr(),
+        _lib.stream_ptr(q.device),
+    )
     with torch.cuda.device(q.device):
-        rc = lib.kfa_bwd(
-            ctypes.byref(_lib.tensor4(q)),
-            ctypes.byref(_lib.tensor4(k)),
-            ctypes.byref(_lib.tensor4(v)),
-            ctypes.byref(_lib.tensor4(out)),
-            ctypes.byref(_lib.tensor4(dout)),
-            lse.data_ptr(),
-            stats.data_ptr(),
-            ctypes.byref(_lib.tensor4(dq)),
-            ctypes.byref(_lib.tensor4(dk)),
-            ctypes.byref(_lib.tensor4(dv)),
-            float(scale),
-            int(block),
-            _lib.dtype_code(q.dtype),
-            _lib.status_word(q.device).data_ptr(),
-            _lib.stream_ptr(q.device),
-        )
+        if _deterministic or batch * heads > 65535:
+            rc = lib.kfa_bwd(*tensors[:5], lse.data_ptr(), stats.data_ptr(), *tensors[5:], *tail)
+        else:
+            dq_acc = q.new_empty(lib.kfa_bwd_dq_acc_bytes(batch, heads, seq_q, dim) // 4, dtype=torch.float32)
+            rc = lib.kfa_bwd_fused(
+                *tensors[:5], lse.data_ptr(), stats.data_ptr(), dq_acc.data_ptr(), *tensors[5:], *tail
+            )
     _lib.check(rc)
     return dq, dk, dv
 

@@ -7,8 +7,13 @@ Run once where the reference checkout is available:
 It imports the reference's ``tests/reference.py`` (fp64 attention + metrics) and
 ``benchmarks/dinov3_backward.py`` (``emulated_grads``, the correct-kernel rounding floor and its
 bug variants), runs them on small seeded CPU inputs and stores inputs' recipe + outputs in
-``tests/golden/*.npz``. The fixtures travel with the repository; the reference does not.
+``tests/golden/*.npz``, plus ``floor_large_logit.json``: the error of the reference's emulated floor
+against the reference's fp64 gradients on the large-logit workloads of ``kohakufa_b200.workloads`` (only
+the error norms are stored, the tensors are regenerated from their seeds by the tests). The fixtures
+travel with the repository; the reference does not.
 """
+
+import json
 
 import importlib.util
 import sys
@@ -68,6 +73,25 @@ FLOOR_CASES = {
     "floor_large_bf16": (1, 1, 40, 64, "bfloat16", 24, 30.0),
 }
 BUG_SETS = {"floor": (), "scale_ds": ("scale*dS",), "single_lse": ("single lse",), "scale_shift": ("scale-shift",)}
+# The large-logit workloads the GPU floor tests run: name -> (generator, arguments)
+LARGE_LOGIT_CASES = {
+    "C2": ("config", "C2", 4),
+    "C2-bf16": ("config", "C2-bf16", 4),
+    "balanced-f16": ("balanced", "float16"),
+    "balanced-bf16": ("balanced", "bfloat16"),
+}
+
+
+def make_large_logit_inputs(name):
+    """q, k, v, dout ([B, H, S, D], CPU, already rounded) and the softmax scale of a LARGE_LOGIT_CASES entry."""
+    sys.path.insert(0, str(HERE.parent.parent))
+    from kohakufa_b200 import workloads
+
+    case = LARGE_LOGIT_CASES[name]
+    if case[0] == "config":
+        cfg = workloads.CONFIGS[case[1]]
+        return workloads.make_inputs(cfg, batch=case[2], heads=cfg.heads), cfg.scale
+    return workloads.balanced_large_logit_inputs(1, 4, 512, 64, getattr(torch, case[1])), 64**-0.5
 
 
 def make_attention_inputs(case):
@@ -131,7 +155,26 @@ def main(ref_root: str) -> None:
             for key, val in zip(("dq", "dk", "dv"), (dq, dk, dv)):
                 out[f"{name}/{tag}/{key}"] = val.numpy()
     np.savez_compressed(HERE / "floor_emulation.npz", **out)
-    print("wrote", HERE / "attention_fp64.npz", HERE / "floor_emulation.npz")
+
+    def rel_l2(got, want):
+        return float((got.double() - want.double()).norm() / want.double().norm())
+
+    floors = {}
+    for name in LARGE_LOGIT_CASES:
+        (q, k, v, dout), scale = make_large_logit_inputs(name)
+        want = ref.reference(q, k, v, dout, scale)[1:]
+        inputs = {"q": q, "k": k, "v": v, "dout": dout, "scale": scale}
+        entry = {}
+        for tag, bugs in BUG_SETS.items():
+            got = emu.emulated_grads(inputs, set(bugs))
+            entry[tag] = {key: rel_l2(g, w) for key, g, w in zip(("dq", "dk", "dv"), got, want)}
+            if tag == "floor":  # the same with the gradients themselves rounded to the 16-bit output dtype
+                entry["floor_rounded_outputs"] = {
+                    key: rel_l2(g.to(q.dtype), w) for key, g, w in zip(("dq", "dk", "dv"), got, want)
+                }
+        floors[name] = entry
+    (HERE / "floor_large_logit.json").write_text(json.dumps(floors, indent=1) + "\n")
+    print("wrote", HERE / "attention_fp64.npz", HERE / "floor_emulation.npz", HERE / "floor_large_logit.json")
 
 
 if __name__ == "__main__":

@@ -53,26 +53,6 @@ def want_for(q, k, v, dout, block=0, scale=None):
     return oracle.attention_fp64(q, k, v, dout, scale, block=block)
 
 
-def tensor_core_scores(q, k):
-    """q k^T with fp32 accumulation on the GPU's tensor cores (a library GEMM with 16-bit inputs and
-    fp32 output): the raw scores as any tensor-core kernel gets them, a few fp32 units in the last
-    place away from the correctly rounded product."""
-    b, h, sq, d = q.shape
-    qq = q.detach().reshape(b * h, sq, d).contiguous()
-    kk = k.detach().reshape(b * h, k.shape[2], d).contiguous()
-    return torch.bmm(qq, kk.transpose(1, 2), out_dtype=torch.float32).reshape(b, h, sq, k.shape[2])
-
-
-def rounded_floor(q, k, v, dout, scale, block=0, hardware_scores=False):
-    """The correct-kernel rounding floor INCLUDING the rounding of dq, dk, dv themselves to the
-    16-bit output dtype, which the reference's emulation leaves out (it returns fp64) and which no
-    kernel with 16-bit outputs can avoid. ``hardware_scores``: start from the tensor core's fp32
-    scores instead of the correctly rounded ones (see ``oracle.floor_grads``)."""
-    scores = tensor_core_scores(q, k) if hardware_scores else None
-    floor = oracle.floor_grads(q.detach(), k.detach(), v.detach(), dout, scale, block, scores=scores)
-    return tuple(g.to(q.dtype).double() for g in floor)
-
-
 def test_selftest():
     report = _lib.selftest()
     assert "exact" in report and "differ" not in report, report
@@ -253,58 +233,6 @@ def test_huge_logits(causal, dim, mag):
     want = want_for(q, k, v, dout, block=int(causal))
     for name, g, w, bound in zip(("dk", "dv"), got[2:], want[2:], (0.995, 0.9999)):
         assert oracle.metrics(g, w)["cos"] > bound, name
-
-
-def floor_ratios(got, want, q, k, v, dout, scale):
-    """kernel error / floor error for dq, dk, dv: against the emulated floor with 16-bit outputs
-    ("ideal", correctly rounded fp32 scores) and against the same floor started from the tensor
-    core's scores ("hardware")."""
-    ideal = rounded_floor(q, k, v, dout, scale)
-    hardware = rounded_floor(q, k, v, dout, scale, hardware_scores=True)
-    rows = {}
-    for idx, key in ((1, "dq"), (2, "dk"), (3, "dv")):
-        err = oracle.rel_l2(got[idx], want[idx])
-        rows[key] = (
-            err,
-            err / oracle.rel_l2(ideal[idx - 1], want[idx]),
-            err / oracle.rel_l2(hardware[idx - 1], want[idx]),
-        )
-    print({k_: tuple(f"{x:.3e}" for x in v_) for k_, v_ in rows.items()})
-    return rows
-
-
-@pytest.mark.parametrize("name", ["C2", "C2-bf16"])
-def test_config2_large_logit_floor(name):
-    """C2 (max logit ~1e5, runner-up within ~1e1): dQ, dK, dV within 1.1x the correct-kernel
-    rounding floor, fp16 and bf16. The floor is the reference's emulation plus two things every
-    tensor-core kernel with 16-bit outputs pays and the emulation leaves out: the rounding of the
-    gradients themselves, and raw scores that come out of the tensor core's truncating fp32
-    accumulation instead of a correctly rounded product (at these logits one fp32 unit in the last
-    place of a score is ~1% of a neighbouring P). Against the idealised floor the same results sit
-    at 1.0-1.3x; both ratios are printed."""
-    cfg = workloads.CONFIGS[name]
-    q, k, v, dout = (t.cuda() for t in workloads.make_inputs(cfg, batch=4, heads=cfg.heads))
-    q, k, v = (t.requires_grad_() for t in (q, k, v))
-    got = run(q, k, v, dout)
-    want = want_for(q, k, v, dout)
-    out_tol = TOL if cfg.dtype == torch.float16 else BF16_TOL
-    assert oracle.metrics(got[0], want[0])["rel_err"] < out_tol
-    for key, (err, ideal, hardware) in floor_ratios(got, want, q, k, v, dout, cfg.scale).items():
-        assert hardware <= 1.1, f"{key}: kernel {err:.3e}, {hardware:.3f}x the floor ({ideal:.3f}x the idealised one)"
-        assert ideal <= 1.5, f"{key}: {ideal:.3f}x the idealised floor"
-
-
-@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-def test_balanced_large_logits(dtype):
-    """The reference's own large-logit generator (magnitude split between q and k, max logit 1e5):
-    all three gradients within 1.1x the floor (defined as in the C2 test)."""
-    q, k, v, dout = (t.cuda() for t in workloads.balanced_large_logit_inputs(1, 4, 512, 64, dtype))
-    q, k, v = (t.requires_grad_() for t in (q, k, v))
-    got = run(q, k, v, dout)
-    want = want_for(q, k, v, dout)
-    for key, (err, ideal, hardware) in floor_ratios(got, want, q, k, v, dout, 64**-0.5).items():
-        assert hardware <= 1.1, f"{key}: kernel {err:.3e}, {hardware:.3f}x the floor ({ideal:.3f}x the idealised one)"
-        assert ideal <= 1.5, f"{key}: {ideal:.3f}x the idealised floor"
 
 
 def test_largest_p_is_exactly_one():

@@ -104,23 +104,25 @@ def test_stride_rule():
 
 def test_pad_head_dim():
     q, k, v = qkv(d=40)
-    pq, pk, pv = api._pad_head_dim(q, k, v)
+    pq, pk, pv = api._fit_head_dim(q, k, v)
     assert pq.shape[-1] == pk.shape[-1] == pv.shape[-1] == 64
     q, k, v = qkv(d=72)
-    assert api._pad_head_dim(q, k, v)[0].shape[-1] == 128
+    assert api._fit_head_dim(q, k, v)[0].shape[-1] == 128
     q, k, v = qkv(d=128)
-    assert api._pad_head_dim(q, k, v)[0] is q
+    assert api._fit_head_dim(q, k, v)[0] is q
 
 
 def test_center_keys_is_a_pure_shift():
     k = torch.randn(2, 3, 10, 8)
-    c = api._center_keys(k, torch.float16)
+    c = api._remove_key_mean(k, torch.float16)
     assert c.dtype == torch.float16
     assert float(c.float().mean(-2).abs().max()) < 1e-3
 
 
 def test_other_exports_raise():
-    assert set(kohakufa_b200.__all__) == {"PackedMask", "attention", "attention_varlen", "pack_mask", "varlen_plan"}
+    reference_exports = {"PackedMask", "attention", "attention_varlen", "pack_mask", "varlen_plan"}
+    own = {"check_status", "reset_status", "set_deterministic", "is_deterministic"}
+    assert set(kohakufa_b200.__all__) == reference_exports | own
 
 
 def test_mask_normalize_rules():
@@ -164,11 +166,11 @@ def test_varlen_fake_kernels_infer_layouts():
 
 
 def test_center_keys_varlen_subtracts_each_sequence_mean():
-    from kohakufa_b200.api import _center_keys_varlen
+    from kohakufa_b200.api import _remove_key_mean
 
     k = torch.randn(12, 2, 8) + 3.0
     cu = torch.tensor([0, 5, 5, 12], dtype=torch.int32)
-    c = _center_keys_varlen(k, cu)
+    c = _remove_key_mean(k, k.dtype, cu)
     assert float(c[:5].mean(0).abs().max()) < 1e-5 and float(c[5:].mean(0).abs().max()) < 1e-5
 
 
