@@ -12,7 +12,14 @@ Rank 0 prints ONE JSON line: the metric (fwd+bwd TFLOP/s, algorithmic FLOPs in t
 convention), the end-to-end number through ``kohakufa_b200.attention`` with host buffers, the
 tensor-core roofline of the dominant kernel from CUDA-event timings of each kernel inside the timed
 steps, the CPU baseline (the fp64 oracle on the host cores, on a bounded sample), and the clocks
-sampled during the timed region.
+sampled during the timed region. Configurations whose step lasts microseconds (C1, C2) are timed as
+one CUDA graph of the K steps, as the reference's benchmark does (benchmarks/speed.py:29-61): eager
+launches would measure the host's launch rate instead of the kernels.
+
+With N > 1 GPUs the line also carries a ``ring`` record: the context-parallel C5 problem (one causal
+sequence of 131072 tokens spread over the N GPUs, strong scaling) timed the same way, with the share of
+the step the compute stream spent waiting for NCCL, the ring's results against the single-GPU kernels
+at S = 16384, and fp64 spot checks of rows of the full-length result.
 
 ``--impl reference`` times the reference's CPU path (its fp64 oracle, restated in oracle/) on the
 host cores instead, on a bounded sample of the same configuration.
@@ -124,32 +131,39 @@ class ClockSampler:
         }
 
 
-def cpu_baseline(cfg, threads=None, target_seconds=12.0):
-    """The fp64 oracle (forward + backward) on the host cores on a bounded sample of ``cfg``: one
-    (batch, head) slice at the configuration's length capped so that the fp64 score matrices fit
-    comfortably; repeated until about ``target_seconds`` have passed."""
+def reference_sample(cfg):
+    """The bounded sample of ``cfg`` both CPU measurements run: 1 batch x 2 heads at the configuration's
+    length capped at 2048 (fp64 score matrices of a longer slice would not be a few seconds of work)."""
     from kohakufa_b200 import workloads
+
+    seq = min(cfg.seq, 2048)
+    inputs = workloads.make_inputs(cfg, batch=1, heads=2, seq=seq)
+    flops = workloads.attention_flops(1, 2, seq, seq, cfg.dim, cfg.block)
+    return inputs, flops, f"fp64 oracle, fwd+bwd, 1 batch x 2 heads of {cfg.name} at S={seq}"
+
+
+def cpu_baseline(cfg, threads=None, target_seconds=12.0):
+    """The fp64 oracle (forward + backward) on the host cores on the bounded sample of ``cfg``, repeated
+    until about ``target_seconds`` have passed."""
     from oracle import reference as oracle
 
     threads = threads or os.cpu_count() or 1
     torch.set_num_threads(threads)
-    seq = min(cfg.seq, 4096)
-    q, k, v, dout = workloads.make_inputs(cfg, batch=1, heads=1, seq=seq)
-    flops = workloads.attention_flops(1, 1, seq, seq, cfg.dim, cfg.block)
+    (q, k, v, dout), flops, sample = reference_sample(cfg)
     oracle.attention_fp64(q, k, v, dout, cfg.scale, cfg.block)  # warm-up
     reps, t0 = 0, time.perf_counter()
     while True:
         oracle.attention_fp64(q, k, v, dout, cfg.scale, cfg.block)
         reps += 1
         elapsed = time.perf_counter() - t0
-        if elapsed > target_seconds or reps >= 50:
+        if elapsed > target_seconds or reps >= 200:
             break
     return {
         "value": flops * reps / elapsed / 1e12,
         "unit": UNIT,
         "cores": threads,
         "kind": "port",
-        "sample": f"fp64 oracle, fwd+bwd, 1 batch x 1 head of {cfg.name} at S={seq}, {reps} repetitions in {elapsed:.1f} s",
+        "sample": f"{sample}, {reps} repetitions in {elapsed:.1f} s",
     }
 
 
@@ -159,14 +173,12 @@ def run_reference(args, cfg):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    from kohakufa_b200 import workloads
     from oracle import reference as oracle
 
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
-    seq = min(cfg.seq, 2048)
-    q, k, v, dout = workloads.make_inputs(cfg, batch=1, heads=2, seq=seq)
-    flops = workloads.attention_flops(1, 2, seq, seq, cfg.dim, cfg.block)
+    (q, k, v, dout), flops, sample = reference_sample(cfg)
+    sample += " per step"
     for _ in range(args.warmup):
         oracle.attention_fp64(q, k, v, dout, cfg.scale, cfg.block)
     t0 = time.perf_counter()
@@ -174,7 +186,6 @@ def run_reference(args, cfg):
         oracle.attention_fp64(q, k, v, dout, cfg.scale, cfg.block)
     elapsed = time.perf_counter() - t0
     value = flops * args.steps / elapsed / 1e12
-    sample = f"fp64 oracle, fwd+bwd, 1 batch x 2 heads of {cfg.name} at S={seq} per step"
     line = {
         "impl": "reference",
         "metric": METRIC,
@@ -189,7 +200,7 @@ def run_reference(args, cfg):
         "vs_baseline": None,
         "dtype": "f64",
         "data": "synthetic",
-        "config": config_dict(cfg, 1) | {"sample": sample},
+        "config": config_dict(cfg, args.gpus),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -233,8 +244,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=None, help="override the configuration's batch (profiling a small case)")
     ap.add_argument("--heads", type=int, default=None, help="override the configuration's head count")
+    ap.add_argument("--deterministic", action="store_true", help="time the split, bit-reproducible backward kernels")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-ring", action="store_true", help="N > 1: skip the context-parallel C5 record")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -251,14 +264,16 @@ def main():
 
     import torch.distributed as dist
 
-    from kohakufa_b200 import _lib, attention
+    from kohakufa_b200 import _lib, attention, set_deterministic
     from kohakufa_b200.op import attention_bwd_op, attention_fwd_op
 
+    set_deterministic(args.deterministic)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    affinity = bind_to_gpu_cpus(local)  # before any pinned allocation: first touch places the pages
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
@@ -275,7 +290,6 @@ def main():
     q, k, v, dout = (t.to(dev, non_blocking=True).transpose(1, 2) for t in host)
     torch.cuda.synchronize()
     flops = workloads.attention_flops(cfg.batch, cfg.heads, cfg.seq, cfg.seq, cfg.dim, cfg.block)
-    fwd_flops = flops / 3.5
     scale, block = cfg.scale, cfg.block
 
     if ring_mode:
@@ -301,18 +315,37 @@ def main():
     barrier()
     assert _lib.device_status(dev) == 0, "a kernel wait timed out during warm-up"
 
+    # A step of a few hundred microseconds is launch-bound when issued eagerly: such configurations are
+    # timed as ONE CUDA graph holding the K steps (the reference's method, benchmarks/speed.py:29-61).
+    use_graph = (not ring_mode) and flops < 1e11
+    graph = None
+    if use_graph:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(args.steps):
+                    step()
+        torch.cuda.current_stream().wait_stream(side)
+        graph.replay()  # one untimed replay
+        barrier()
+
     # ---- timed region: exactly K steps, device time, max over ranks ----
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local if rank == 0 else -1) as sampler:
         sampler.wait_running()
         barrier()
         start.record()
-        for _ in range(args.steps):
-            step()
+        if graph is not None:
+            graph.replay()
+        else:
+            for _ in range(args.steps):
+                step()
         stop.record()
         barrier()
         # per-kernel device times, same workload, still inside the sampled region
-        kernel_ms = time_kernels(cfg, q, k, v, dout, args.steps)
+        kernel_ms = time_kernels(cfg, q, k, v, dout, args.steps, args.deterministic)
         # a short timed region can end before nvidia-smi's next sample: keep the same load running
         # (untimed) until three samples under load exist, for at most 1.5 s
         t_extra = time.perf_counter()
@@ -337,6 +370,14 @@ def main():
             e2e = end_to_end(cfg, host, dev, attn, 1, flops, max(2, args.steps // 4), barrier, reduce_max=True)
         else:
             e2e = end_to_end(cfg, host, dev, attention, world, flops, max(3, args.steps // 4), barrier)
+        e2e["cpu_affinity"] = affinity
+
+    # ---- N > 1: the context-parallel ring on C5, under the same launch ----
+    ring_rec = None
+    if world > 1 and not ring_mode and not args.no_ring:
+        del q, k, v, dout, host
+        torch.cuda.empty_cache()
+        ring_rec = ring_record(rank, world, dev, barrier)
 
     if rank != 0:
         if world > 1:
@@ -344,17 +385,18 @@ def main():
         return
 
     peaks, peak_kind = measured_peaks()
-    units = {"fwd": 2, "dkdv": 4, "dq": 1}  # matmuls of the algorithmic count each kernel delivers
-    dominant = max(("fwd", "dkdv", "dq"), key=lambda n: kernel_ms[n])
+    # matmuls of the algorithmic count (2 forward + 5 backward) each kernel delivers; the split dQ kernel's
+    # S and dP are recomputation and count for nothing
+    units = {"fwd": 2, "fused": 5, "dkdv": 4, "dq": 1}
+    names = {"fwd": "kfa_fwd_kernel", "fused": "kfa_bwd_fused_kernel", "dkdv": "kfa_bwd_dkdv_kernel", "dq": "kfa_bwd_dq_kernel"}
+    dominant = max((n for n in units if n in kernel_ms), key=lambda n: kernel_ms[n])
     # the kernels were timed on this rank's local tensors (the whole problem unless ring mode)
-    local_fwd_flops = workloads.attention_flops(q.shape[0], q.shape[1], q.shape[2], q.shape[2], cfg.dim, cfg.block, backward=False)
+    local_rows = cfg.seq // world if ring_mode else cfg.seq
+    local_fwd_flops = workloads.attention_flops(cfg.batch, cfg.heads, local_rows, local_rows, cfg.dim, cfg.block, backward=False)
     achieved = units[dominant] * (local_fwd_flops / 2) / (kernel_ms[dominant] * 1e-3) / 1e12
-    peak = peaks["bf16_tflops_sustained"]
-    # DRAM traffic of the dK/dV kernel from the ncu capture of the same shape at 16 heads
-    # (profiles/attention_kernels_c3_b1h16_ncu.md), scaled by the number of heads (it grows in proportion)
-    traffic = None
-    if dominant == "dkdv" and (cfg.seq, cfg.dim, cfg.block) == (8192, 128, 1) and not ring_mode:
-        traffic = 176.8e6 / 16 * q.shape[0] * q.shape[1]
+    clocks = sampler.summary()
+    # 4096 multiply-adds per clock and SM at the clock the GPU actually ran the timed region at
+    clock_peak = 4096 * 2 * 148 * clocks["sm_mhz"] * 1e6 / 1e12 if clocks.get("sm_mhz") else None
     line = {
         "metric": METRIC,
         "value": value,
@@ -368,28 +410,37 @@ def main():
         "vs_baseline": (value / world / PUBLISHED[cfg.name]) if cfg.name in PUBLISHED else None,
         "dtype": "bf16" if cfg.dtype == torch.bfloat16 else "fp16",
         "data": "synthetic",
-        "config": config_dict(cfg, world),
+        "config": config_dict(cfg, world)
+        | {"timing": f"one CUDA graph of {args.steps} steps" if use_graph else "eager launches, CUDA events"}
+        | {"backward": "split kernels (deterministic)" if args.deterministic else "fused kernel"},
         "pct_of_peak": {
-            "of_measured_sustained": value / world / peaks["bf16_tflops_sustained"],
             "of_measured_burst": value / world / peaks["bf16_tflops"],
+            "of_measured_sustained": value / world / peaks["bf16_tflops_sustained"],
             "of_nominal_2250": value / world / 2250.0,
             "peaks": peak_kind,
         },
         "kernel_ms": kernel_ms,
         "roofline": {
             "bound": "tensor",
-            "kernel": {"fwd": "kfa_fwd_kernel", "dkdv": "kfa_bwd_dkdv_kernel", "dq": "kfa_bwd_dq_kernel"}[dominant],
+            "kernel": names[dominant],
             "achieved": achieved,
-            "peak": peak,
+            "peak": peaks["bf16_tflops"],
             "unit": "TFLOP/s",
-            "frac": achieved / peak,
-            "traffic": traffic,
-            "note": f"algorithmic matmuls counted for this kernel: {units[dominant]} of 7; peak = {peak_kind} sustained cuBLAS bf16",
+            "frac": achieved / peaks["bf16_tflops"],
+            "frac_of_sustained_peak": achieved / peaks["bf16_tflops_sustained"],
+            "frac_of_clock_normalised_peak": achieved / clock_peak if clock_peak else None,
+            "traffic": ncu_traffic(dominant, cfg, q_heads=cfg.batch * cfg.heads) if not ring_mode else None,
+            "note": f"algorithmic matmuls counted for this kernel: {units[dominant]} of 7; peak = {peak_kind} burst cuBLAS bf16 "
+            "(the timed region lasts a fraction of a second); sustained = the same GEMM in a seconds-long loop; "
+            "clock-normalised = 4096 MAC x 2 x 148 SMs x the median SM clock sampled during the timed region; "
+            "traffic = DRAM bytes of one launch from an ncu capture of a 16-head case, scaled by the head count",
         },
         "gpu_launches": (3 * world + 5 if ring_mode else 4) * args.steps,
-        "clocks": sampler.summary(),
+        "clocks": clocks,
         "e2e": e2e,
     }
+    if ring_rec is not None:
+        line["ring"] = ring_rec
     if not args.no_cpu_baseline and world == 1:
         line["cpu_baseline"] = cpu_baseline(cfg)
     print(json.dumps(line), flush=True)
@@ -397,7 +448,41 @@ def main():
         dist.destroy_process_group()
 
 
-def time_kernels(cfg, q, k, v, dout, reps):
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of the named kernel at B=1, H=16 of
+# a configuration, from ncu captures of that small case; a launch's traffic grows in proportion to the
+# number of (batch, head) pairs, so the full launch is this times heads / 16.
+NCU_DRAM_BYTES_16_HEADS = {
+    ("dkdv", 8192, 128, 1): 176.8e6,
+}
+
+
+def ncu_traffic(kernel, cfg, q_heads):
+    per16 = NCU_DRAM_BYTES_16_HEADS.get((kernel, cfg.seq, cfg.dim, cfg.block))
+    return None if per16 is None else per16 / 16 * q_heads
+
+
+def bind_to_gpu_cpus(index):
+    """Pins this process to the CPU cores the driver reports as local to GPU ``index`` (NVML, read-only),
+    so that the pinned host buffers allocated afterwards are placed on that NUMA node. Returns what was
+    done, for the record."""
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (os.cpu_count() + 63) // 64)
+        cpus = {64 * w + b for w, word in enumerate(words) for b in range(64) if (word >> b) & 1}
+        allowed = os.sched_getaffinity(0)
+        use = sorted(cpus & allowed)
+        if use and len(use) < len(allowed):
+            os.sched_setaffinity(0, use)
+            return {"bound_to": f"{use[0]}-{use[-1]} ({len(use)} of {len(allowed)} allowed cores)", "source": "NVML"}
+        return {"bound_to": None, "note": f"GPU-local cores ({len(cpus)}) cover all {len(allowed)} allowed cores: one NUMA domain visible"}
+    except Exception as exc:  # no NVML, or a cpuset that forbids it: run unbound
+        return {"bound_to": None, "note": f"affinity not set: {type(exc).__name__}"}
+
+
+def time_kernels(cfg, q, k, v, dout, reps, deterministic=False):
     """Average device time of each kernel of one step, CUDA events on the launching stream."""
     import ctypes
 
@@ -415,12 +500,20 @@ def time_kernels(cfg, q, k, v, dout, reps):
     code = _lib.dtype_code(q.dtype)
     word = _lib.status_word(dev).data_ptr()
     stream = _lib.stream_ptr(dev)
-    calls = {
-        "fwd": lambda: lib.kfa_fwd(T["q"], T["k"], T["v"], T["out"], lse.data_ptr(), scale, block, code, word, stream),
-        "prepare": lambda: lib.kfa_bwd_prepare(T["out"], T["dout"], lse.data_ptr(), stats.data_ptr(), code, stream),
-        "dkdv": lambda: lib.kfa_bwd_dkdv(T["q"], T["k"], T["v"], T["dout"], stats.data_ptr(), T["dk"], T["dv"], scale, block, code, word, stream),
-        "dq": lambda: lib.kfa_bwd_dq(T["q"], T["k"], T["v"], T["dout"], stats.data_ptr(), T["dq"], scale, block, code, word, stream),
-    }
+    calls = {"fwd": lambda: lib.kfa_fwd(T["q"], T["k"], T["v"], T["out"], lse.data_ptr(), scale, block, code, word, stream)}
+    if deterministic:
+        calls |= {
+            "prepare": lambda: lib.kfa_bwd_prepare(T["out"], T["dout"], lse.data_ptr(), stats.data_ptr(), code, stream),
+            "dkdv": lambda: lib.kfa_bwd_dkdv(T["q"], T["k"], T["v"], T["dout"], stats.data_ptr(), T["dk"], T["dv"], scale, block, code, word, stream),
+            "dq": lambda: lib.kfa_bwd_dq(T["q"], T["k"], T["v"], T["dout"], stats.data_ptr(), T["dq"], scale, block, code, word, stream),
+        }
+    else:
+        acc = q.new_empty(lib.kfa_bwd_dq_acc_bytes(*q.shape) // 4, dtype=torch.float32)
+        calls |= {
+            "prepare": lambda: lib.kfa_bwd_prepare_fused(T["out"], T["dout"], lse.data_ptr(), stats.data_ptr(), acc.data_ptr(), code, stream),
+            "fused": lambda: lib.kfa_bwd_fused_main(T["q"], T["k"], T["v"], T["dout"], stats.data_ptr(), acc.data_ptr(), T["dk"], T["dv"], scale, block, code, word, stream),
+            "convert": lambda: lib.kfa_bwd_dq_convert(acc.data_ptr(), T["dq"], scale, code, word, stream),
+        }
     reps = max(3, min(reps, 10))
     events = {n: [] for n in calls}
     for _ in range(reps):
@@ -434,10 +527,171 @@ def time_kernels(cfg, q, k, v, dout, reps):
     return {n: sum(a.elapsed_time(b) for a, b in ev) / len(ev) for n, ev in events.items()}
 
 
+def ring_record(rank, world, dev, barrier, steps=2):
+    """The context-parallel ring on C5 (causal bf16, B=1, H=32, S=131072, D=128 spread zig-zag over the
+    ``world`` GPUs), measured and checked under the same launch as the main line:
+
+    * ``value`` / ``ms_per_step``: forward + backward of the WHOLE problem (strong scaling), device time, max
+      over ranks; ``stream_ms``: where the compute stream's time went on the slowest rank (kernels against
+      stalls waiting for NCCL transfers), from events around every wait;
+    * ``parity_s16384``: the ring's out / dQ / dK / dV at S = 16384 against the single-GPU kernels on the same
+      tensors (relative L2 error, max over ranks);
+    * ``fp64_spot_checks``: at the full length, 4 heads x (first, middle, last) 512 query rows of out and dQ,
+      and dK / dV of the last 512 keys, against a chunk-free fp64 evaluation of those rows (relative L2
+      error; the tolerance is the bf16 one of the tests, 2e-2).
+    The inputs are drawn on the device (seeded per 8192-row piece): the checks are computed from the very
+    tensors the kernels read."""
+    import torch.distributed as dist
+
+    from kohakufa_b200 import ring, workloads
+    from kohakufa_b200.op import attention_bwd_op, attention_fwd_op
+
+    cfg = workloads.CONFIGS["C5"]
+    scale = cfg.scale
+
+    def my_ranges(seq):
+        chunk = seq // (2 * world)
+        return [(c * chunk, (c + 1) * chunk) for c in sorted({rank, 2 * world - 1 - rank})]
+
+    def shard_only(seq):  # this rank's rows, generated piece by piece (chunks are whole pieces)
+        return workloads.make_piecewise_inputs(cfg, my_ranges(seq), device=dev, device_rng=True)
+
+    def shard_and_full(seq):  # a short sequence: every rank builds all of it and cuts its rows out
+        full = workloads.make_piecewise_inputs(cfg, [(0, seq)], device=dev, device_rng=True)
+        return tuple(ring.zigzag_shard(t, rank, world) for t in full), full
+
+    def rel(got, want):
+        return float((got.double() - want.double()).norm() / want.double().norm().clamp_min(1e-300))
+
+    def reduce_max(x):
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    rec = {"workload": f"C5: token-causal bf16 B=1 H={cfg.heads} S={cfg.seq} D={cfg.dim}, zig-zag shards over {world} GPUs"}
+
+    # ---- (1) parity with the single-GPU kernels at S = 16384 ----
+    small = 16384
+    (q, k, v, dout), full = shard_and_full(small)
+    out, lse = ring.ring_forward(q, k, v, scale)
+    dq, dk, dv = ring.ring_backward(q, k, v, out, dout, lse, scale)
+    fq, fk, fv, fdo = full
+    fout, flse = attention_fwd_op(fq, fk, fv, scale, 1)
+    fgrads = attention_bwd_op(fq, fk, fv, fout, fdo, flse, scale, 1)
+    rec["parity_s16384"] = {
+        name: reduce_max(rel(got, ring.zigzag_shard(want, rank, world)))
+        for name, got, want in zip(("out", "dq", "dk", "dv"), (out, dq, dk, dv), (fout, *fgrads))
+    }
+    del q, k, v, dout, full, out, lse, dq, dk, dv, fq, fk, fv, fdo, fout, flse, fgrads
+    torch.cuda.empty_cache()
+
+    # ---- (2) the full length: timing with a per-wait breakdown ----
+    q, k, v, dout = shard_only(cfg.seq)
+
+    def step(trace=None):
+        out, lse = ring.ring_forward(q, k, v, scale, trace=trace)
+        return out, lse, ring.ring_backward(q, k, v, out, dout, lse, scale, trace=trace)
+
+    step()
+    barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        step()
+    stop.record()
+    barrier()
+    ms = reduce_max(start.elapsed_time(stop)) / steps
+    flops = workloads.attention_flops(cfg.batch, cfg.heads, cfg.seq, cfg.seq, cfg.dim, cfg.block)
+    rec |= {"value": flops / (ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms, "steps": steps, "scaling": "strong"}
+    trace = []
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    out, lse, (dq, dk, dv) = step(trace)
+    b.record()
+    barrier()
+    parts = ring.trace_summary(trace)
+    parts["whole step"] = a.elapsed_time(b)
+    parts["other (packing, finalize, prepare)"] = parts["whole step"] - sum(v_ for k_, v_ in parts.items() if k_ != "whole step")
+    # report the slowest rank's breakdown
+    mine = torch.tensor([parts["whole step"], float(rank)], device=dev, dtype=torch.float64)
+    every = [torch.zeros_like(mine) for _ in range(world)]
+    dist.all_gather(every, mine)
+    slowest = int(max(every, key=lambda t: float(t[0]))[1].item())
+    keys = sorted(parts)
+    vals = torch.tensor([parts[k_] for k_ in keys], device=dev, dtype=torch.float64)
+    dist.broadcast(vals, src=slowest)
+    rec["stream_ms"] = {"rank": slowest} | {k_: float(x) for k_, x in zip(keys, vals)}
+
+    # ---- (3) fp64 spot checks of the full-length result ----
+    heads = [0, cfg.heads // 3, 2 * cfg.heads // 3, cfg.heads - 1]
+    c = cfg.seq // (2 * world)
+
+    def gather_heads(t):  # this rank's rows of the chosen heads -> the whole sequence, [heads, S, D]
+        mine = t[0, heads].contiguous()
+        parts_ = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(parts_, mine)
+        return ring.zigzag_unshard([p_.unsqueeze(0) for p_ in parts_])[0]
+
+    K, V = gather_heads(k), gather_heads(v)
+    # (global first row, local first row, owner) of the three 512-row blocks
+    blocks = {"first": (0, 0, 0), "middle": (world * c - 256, c - 256, world - 1), "last": (cfg.seq - 512, 2 * c - 512, 0)}
+    errs = {}
+    for name, (g0, l0, owner) in blocks.items():
+        worst = {"out": 0.0, "dq": 0.0}
+        if name == "last":
+            worst |= {"dk": 0.0, "dv": 0.0}
+        if rank == owner:
+            n_keys = g0 + 512
+            for hi, h in enumerate(heads):
+                qb, dob = q[0, h, l0 : l0 + 512].double(), dout[0, h, l0 : l0 + 512].double()
+                kk, vv = K[hi, :n_keys].double(), V[hi, :n_keys].double()
+                s_ = (qb @ kk.T) * scale
+                cols = torch.arange(n_keys, device=dev)[None, :]
+                s_.masked_fill_(cols > (g0 + torch.arange(512, device=dev))[:, None], float("-inf"))
+                p_ = torch.softmax(s_, dim=-1)
+                del s_
+                o_ = p_ @ vv
+                ds_ = p_ * (dob @ vv.T - (dob * o_).sum(-1, keepdim=True))
+                worst["out"] = max(worst["out"], rel(out[0, h, l0 : l0 + 512], o_))
+                worst["dq"] = max(worst["dq"], rel(dq[0, h, l0 : l0 + 512], ds_ @ kk * scale))
+                if name == "last":  # only these 512 queries see the last 512 keys
+                    worst["dk"] = max(worst["dk"], rel(dk[0, h, l0 : l0 + 512], ds_[:, g0:].T @ qb * scale))
+                    worst["dv"] = max(worst["dv"], rel(dv[0, h, l0 : l0 + 512], p_[:, g0:].T @ dob))
+                del p_, ds_, o_
+        errs[name] = {k_: reduce_max(x) for k_, x in worst.items()}
+    rec["fp64_spot_checks"] = {"heads": heads, "rows": 512, "rel_err": errs, "tolerance": 2e-2}
+    rec["checks_pass"] = all(x < 2e-2 for blk in errs.values() for x in blk.values()) and all(
+        x < 1e-3 for x in rec["parity_s16384"].values()
+    )
+    return rec
+
+
+def copy_rates(host, dev, reps=3):
+    """GB/s of the host-to-device and the device-to-host copy alone, with the bench's own pinned buffers."""
+    dst = [torch.empty_like(t, device=dev) for t in host]
+    nbytes = sum(t.numel() * t.element_size() for t in host)
+    rates = {}
+    for name, pairs in (("h2d_gbs", list(zip(dst, host))), ("d2h_gbs", list(zip(host, dst)))):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(reps):
+            for d, s_ in pairs:
+                d.copy_(s_, non_blocking=True)
+        b.record()
+        torch.cuda.synchronize()
+        rates[name] = nbytes * reps / (a.elapsed_time(b) * 1e-3) / 1e9
+    return rates
+
+
 def end_to_end(cfg, host, dev, attention, world, flops, steps, barrier, reduce_max=False):
     """The same metric through ``kohakufa_b200.attention`` with HOST buffers: every step copies q, k,
-    v, dout from pinned host memory, runs forward + backward, and copies out, dq, dk, dv back."""
+    v, dout from pinned host memory, runs forward + backward, and copies out, dq, dk, dv back. Also
+    reports the two copy directions timed alone on every rank at once (the PCIe / host-memory bound)."""
     hq, hk, hv, hdo = host
+    barrier()
+    rates = copy_rates(host, dev)
+    barrier()
     if reduce_max:  # ring mode: one sequence over all ranks, no batch to pipeline over
         outs = [torch.empty_like(hq).pin_memory() for _ in range(4)]
 
@@ -472,9 +726,10 @@ def end_to_end(cfg, host, dev, attention, world, flops, steps, barrier, reduce_m
     if world > 1 or reduce_max:
         import torch.distributed as dist
 
-        t = torch.tensor([ms], device=dev)
+        t = torch.tensor([ms, -rates["h2d_gbs"], -rates["d2h_gbs"]], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+        ms = float(t[0].item())
+        rates = {"h2d_gbs": -float(t[1].item()), "d2h_gbs": -float(t[2].item())}
     nbytes = sum(t.numel() * t.element_size() for t in host)
     return {
         "value": world * flops / (ms / steps * 1e-3) / 1e12,
@@ -483,6 +738,7 @@ def end_to_end(cfg, host, dev, attention, world, flops, steps, barrier, reduce_m
         "steps": steps,
         "h2d_bytes_per_step": nbytes,
         "d2h_bytes_per_step": nbytes,
+        "copy_only_per_rank": rates | {"note": "each direction alone, all ranks copying at once, slowest rank"},
     }
 
 

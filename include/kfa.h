@@ -94,6 +94,17 @@ int kfa_bwd(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const
  * `stats`: kfa_bwd_stats_bytes(B, H, Sq) bytes; `dq_acc`: kfa_bwd_dq_acc_bytes(B, H, Sq, D) bytes
  * (fp32, whole 128-row tiles: 4 * D bytes per padded query row), 16-byte aligned; both are scratch. */
 int64_t kfa_bwd_dq_acc_bytes(int64_t B, int64_t H, int64_t Sq, int64_t D);
+/* Its three launches one by one (kfa_bwd_fused = these in this order):
+ *   kfa_bwd_prepare_fused  statistics as kfa_bwd_prepare, and zero-fills dq_acc   (bwd.py:1358-1388)
+ *   kfa_bwd_fused_main     dK, dV written; dQ tiles added to dq_acc                 (bwd.py:1248-1350)
+ *   kfa_bwd_dq_convert     dq = 16-bit(scale * dq_acc)                              (bwd.py:1391-1410) */
+int kfa_bwd_prepare_fused(const KfaTensor4* out, const KfaTensor4* dout, const float* lse, float* stats,
+                          float* dq_acc, int dtype, void* stream);
+int kfa_bwd_fused_main(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* dout,
+                       const float* stats, float* dq_acc, const KfaTensor4* dk, const KfaTensor4* dv,
+                       float scale, int block, int dtype, int* dev_status, void* stream);
+int kfa_bwd_dq_convert(const float* dq_acc, const KfaTensor4* dq, float scale, int dtype,
+                       const int* dev_status, void* stream);
 int kfa_bwd_fused(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* out,
                   const KfaTensor4* dout, const float* lse, float* stats, float* dq_acc, const KfaTensor4* dq,
                   const KfaTensor4* dk, const KfaTensor4* dv, float scale, int block, int dtype,

@@ -10,7 +10,11 @@ from pathlib import Path
 
 import torch
 
-LIB_PATH = Path(__file__).resolve().parent / "libkfa.so"
+import os
+
+# The in-tree build; the environment variable KFA_LIBRARY points the package at another build of the same
+# sources (e.g. one compiled with different tuning macros) without touching the tree.
+LIB_PATH = Path(os.environ.get("KFA_LIBRARY") or Path(__file__).resolve().parent / "libkfa.so")
 
 KFA_F16, KFA_BF16 = 0, 1
 ABI_VERSION = 1
@@ -26,6 +30,9 @@ SYMBOLS = (
     "kfa_bwd_dq",
     "kfa_bwd",
     "kfa_bwd_dq_acc_bytes",
+    "kfa_bwd_prepare_fused",
+    "kfa_bwd_fused_main",
+    "kfa_bwd_dq_convert",
     "kfa_bwd_fused",
     "kfa_bwd_static_scratch",
     "kfa_fwd_varlen",
@@ -113,6 +120,9 @@ def load() -> ctypes.CDLL:
         lib.kfa_bwd.argtypes = [T, T, T, T, T, fp, fp, T, T, T, ctypes.c_float, ctypes.c_int, ctypes.c_int, ip, vp]
         lib.kfa_bwd_dq_acc_bytes.restype = ctypes.c_int64
         lib.kfa_bwd_dq_acc_bytes.argtypes = [ctypes.c_int64] * 4
+        lib.kfa_bwd_prepare_fused.argtypes = [T, T, fp, fp, fp, ctypes.c_int, vp]
+        lib.kfa_bwd_fused_main.argtypes = [T, T, T, T, fp, fp, T, T, ctypes.c_float, ctypes.c_int, ctypes.c_int, ip, vp]
+        lib.kfa_bwd_dq_convert.argtypes = [fp, T, ctypes.c_float, ctypes.c_int, ip, vp]
         lib.kfa_bwd_fused.argtypes = [T, T, T, T, T, fp, fp, fp, T, T, T, ctypes.c_float, ctypes.c_int, ctypes.c_int, ip, vp]
         lib.kfa_bwd_static_scratch.argtypes = [T, T, T, T, T, fp, T, T, T, ctypes.c_float, ctypes.c_int, ctypes.c_int, ip, vp]
         A = ctypes.POINTER(KfaAcc32)

@@ -16,6 +16,11 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libkfa.so"
+# The same library with every pipeline wait limited to a few hundred cycles, so that the first wait for
+# a copy from global memory runs out by itself: what tests/test_abort.py loads to see the kernels'
+# give-up path (status word, NaN outputs, clean teardown) run on a device without hanging anything.
+LIB_SHORT_WAIT = PKG / "libkfa_shortwait.so"
+SHORT_WAIT_FLAGS = ["-DKFA_WAIT_CYCLES=300ll"]
 SOURCES = [CSRC / "kfa_api.cu"]
 HEADERS = [
     CSRC / "kfa_ptx.cuh",
@@ -49,24 +54,30 @@ def nvcc_path() -> str:
     return found
 
 
-def stale() -> bool:
-    if not LIB.exists():
+def stale(lib: Path = LIB) -> bool:
+    if not lib.exists():
         return True
-    built = LIB.stat().st_mtime
+    built = lib.stat().st_mtime
     return any(p.stat().st_mtime > built for p in SOURCES + HEADERS)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile the library if it is missing or older than its sources; returns its path."""
-    if not force and not stale():
-        return LIB
-    cmd = [nvcc_path(), *NVCC_FLAGS, "-o", str(LIB), *map(str, SOURCES)]
+def _compile(lib: Path, extra, log: str, verbose: bool) -> None:
+    cmd = [nvcc_path(), *NVCC_FLAGS, *extra, "-o", str(lib), *map(str, SOURCES)]
     proc = subprocess.run(cmd, capture_output=True, text=True)
-    (PKG / "build.log").write_text(" ".join(cmd) + "\n" + proc.stdout + proc.stderr)
+    (PKG / log).write_text(" ".join(cmd) + "\n" + proc.stdout + proc.stderr)
     if proc.returncode != 0:
         raise RuntimeError(f"nvcc failed:\n{proc.stdout}\n{proc.stderr}")
     if verbose:
         print(proc.stderr)
+
+
+def build(force: bool = False, verbose: bool = False, short_wait: bool = True) -> Path:
+    """Compile the library (and, with ``short_wait``, its short-wait test twin) if missing or older than
+    the sources; returns the library's path."""
+    jobs = [(LIB, [], "build.log")] + ([(LIB_SHORT_WAIT, SHORT_WAIT_FLAGS, "build_shortwait.log")] if short_wait else [])
+    for lib, extra, log in jobs:
+        if force or stale(lib):
+            _compile(lib, extra, log, verbose and lib is LIB)
     return LIB
 
 

@@ -456,18 +456,37 @@ int launch_fused(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap
   if (grid > 0x7fffffffll) return fail(KFA_ERR_ARG, "too many tiles");
   kern<<<static_cast<unsigned>(grid), kfa::FUSED_THREADS, smem, s>>>(mq, mk, mv, mdo, p, dq_acc);
   KFA_CUDA(cudaGetLastError());
+  return KFA_OK;
+}
+
+template <int D, bool BF16>
+int launch_dq_convert(const float* dq_acc, const KfaTensor4* dq, float scale, const int* status, cudaStream_t s) {
+  const int H = static_cast<int>(dq->shape[1]), Sq = static_cast<int>(dq->shape[2]);
   auto conv = kfa::kfa_bwd_dq_convert_kernel<D, BF16>;
-  conv<<<dim3(p.n_q128, p.B * p.H), 256, 0, s>>>(dq_acc, p.dq, p.dq_sb, p.dq_sh, p.dq_ss, p.H, p.Sq, p.scale);
+  conv<<<dim3((Sq + 127) / 128, static_cast<unsigned>(dq->shape[0] * H)), 256, 0, s>>>(
+      dq_acc, dq->ptr, dq->stride[0], dq->stride[1], dq->stride[2], H, Sq, scale, status);
   KFA_CUDA(cudaGetLastError());
   return KFA_OK;
 }
 
-int fused_impl(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* dout,
-               const float* stats, float* dq_acc, const KfaTensor4* dq, const KfaTensor4* dk, const KfaTensor4* dv,
-               float scale, int block, int dtype, int* dev_status, void* stream) {
+int convert_impl(const float* dq_acc, const KfaTensor4* dq, float scale, int dtype, const int* dev_status, void* stream) {
   int rc;
-  if ((rc = check_qkv(q, k, v, dtype, block)) || (rc = check_like(dout, q, "dout")) || (rc = check_like(dq, q, "dq")) ||
-      (rc = check_like(dk, k, "dk")) || (rc = check_like(dv, v, "dv")))
+  if ((rc = check_tensor(dq, "dq"))) return rc;
+  if (!dq_acc || !dev_status) return fail(KFA_ERR_ARG, "dq_acc / dev_status: null pointer");
+  if (dtype != KFA_F16 && dtype != KFA_BF16) return fail(KFA_ERR_ARG, "dtype %d", dtype);
+  const int64_t D = dq->shape[3];
+  if (D != 64 && D != 128) return fail(KFA_ERR_ARG, "head_dim %lld: 64 or 128", (long long)D);
+  if (dq->shape[0] * dq->shape[1] > 65535) return fail(KFA_ERR_ARG, "B * H > 65535");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  KFA_DISPATCH(D, dtype, (launch_dq_convert<KD, KB>(dq_acc, dq, scale, dev_status, s)));
+}
+
+int fused_impl(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* dout,
+               const float* stats, float* dq_acc, const KfaTensor4* dk, const KfaTensor4* dv, float scale, int block,
+               int dtype, int* dev_status, void* stream) {
+  int rc;
+  if ((rc = check_qkv(q, k, v, dtype, block)) || (rc = check_like(dout, q, "dout")) || (rc = check_like(dk, k, "dk")) ||
+      (rc = check_like(dv, v, "dv")))
     return rc;
   if (!stats || !dq_acc || !dev_status) return fail(KFA_ERR_ARG, "stats / dq_acc / dev_status: null pointer");
   if (reinterpret_cast<uintptr_t>(dq_acc) % 16) return fail(KFA_ERR_ARG, "dq_acc: not 16-byte aligned");
@@ -477,11 +496,6 @@ int fused_impl(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, co
     return rc;
   kfa::BwdParams p;
   fill_bwd_params(p, q, k, stats, scale, block, dev_status);
-  if (static_cast<long long>(p.B) * p.H > 65535) return fail(KFA_ERR_ARG, "B * H > 65535");
-  p.dq = dq->ptr;
-  p.dq_sb = dq->stride[0];
-  p.dq_sh = dq->stride[1];
-  p.dq_ss = dq->stride[2];
   p.dk = dk->ptr;
   p.dk_sb = dk->stride[0];
   p.dk_sh = dk->stride[1];
@@ -591,15 +605,33 @@ int64_t kfa_bwd_dq_acc_bytes(int64_t B, int64_t H, int64_t Sq, int64_t D) {
   return B * H * ((Sq + 127) / 128) * 128 * D * 4;
 }
 
+int kfa_bwd_prepare_fused(const KfaTensor4* out, const KfaTensor4* dout, const float* lse, float* stats, float* dq_acc,
+                          int dtype, void* stream) {
+  if (!dq_acc) return fail(KFA_ERR_ARG, "dq_acc: null pointer");
+  return prepare_impl(out, dout, lse, stats, nullptr, dtype, stream, dq_acc);
+}
+
+int kfa_bwd_fused_main(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* dout,
+                       const float* stats, float* dq_acc, const KfaTensor4* dk, const KfaTensor4* dv, float scale,
+                       int block, int dtype, int* dev_status, void* stream) {
+  return fused_impl(q, k, v, dout, stats, dq_acc, dk, dv, scale, block, dtype, dev_status, stream);
+}
+
+int kfa_bwd_dq_convert(const float* dq_acc, const KfaTensor4* dq, float scale, int dtype, const int* dev_status,
+                       void* stream) {
+  return convert_impl(dq_acc, dq, scale, dtype, dev_status, stream);
+}
+
 int kfa_bwd_fused(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* out,
                   const KfaTensor4* dout, const float* lse, float* stats, float* dq_acc, const KfaTensor4* dq,
                   const KfaTensor4* dk, const KfaTensor4* dv, float scale, int block, int dtype, int* dev_status,
                   void* stream) {
   int rc;
-  if ((rc = check_like(out, q, "out"))) return rc;
-  if (!dq_acc) return fail(KFA_ERR_ARG, "dq_acc: null pointer");
-  if ((rc = prepare_impl(out, dout, lse, stats, nullptr, dtype, stream, dq_acc))) return rc;
-  return fused_impl(q, k, v, dout, stats, dq_acc, dq, dk, dv, scale, block, dtype, dev_status, stream);
+  if ((rc = check_like(out, q, "out")) || (rc = check_like(dq, q, "dq"))) return rc;
+  if (static_cast<long long>(q->shape[0]) * q->shape[1] > 65535) return fail(KFA_ERR_ARG, "B * H > 65535");
+  if ((rc = kfa_bwd_prepare_fused(out, dout, lse, stats, dq_acc, dtype, stream))) return rc;
+  if ((rc = fused_impl(q, k, v, dout, stats, dq_acc, dk, dv, scale, block, dtype, dev_status, stream))) return rc;
+  return convert_impl(dq_acc, dq, scale, dtype, dev_status, stream);
 }
 
 }  // extern "C"
@@ -660,10 +692,3 @@ extern "C" int kfa_bwd_static_scratch(const KfaTensor4* q, const KfaTensor4* k, 
 #include "kfa_scores.cuh"
 #include "kfa_selftest.cuh"
 
-#ifdef KFA_PROFILE
-// Debug builds only (not part of the ABI): where the per-role wait-cycle counters are written.
-extern "C" int kfa_debug_set_profile(long long* device_buffer) {
-  KFA_CUDA(cudaMemcpyToSymbol(kfa::g_kfa_prof, &device_buffer, sizeof(device_buffer)));
-  return KFA_OK;
-}
-#endif

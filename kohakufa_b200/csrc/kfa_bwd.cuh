@@ -479,15 +479,7 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   // step s -> query tile and query head
   auto tile_of = [&](int s) { return use_list ? static_cast<int>(s_list[s] & 0xffffu) : first_i + s % n_per; };
   auto head_of = [&](int s) { return hk * p.group + (use_list ? static_cast<int>(s_list[s] >> 16) : s / n_per); };
-#ifdef KFA_PROFILE
-  long long prof_acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
-  long long kfa_prof_tb = 0;
-  (void)kfa_prof_tb;
-  const long long prof_t0 = clock64();
-  const Ctl ctl{s_abort, p.status, prof_acc};
-#else
   const Ctl ctl{s_abort, p.status};
-#endif
   const bool dead = (*s_abort != 0);
 
   if (dead) {
@@ -524,11 +516,8 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         issued = s + 1;
       }
       if (!ok) {  // aborting: let the copies in flight land before the CTA gives up its shared memory
-        for (int s = max(issued - NSL, 0); s < issued; ++s) {
-          const long long t0 = clock64();
-          while (!mbar_try_wait(bar(B_QREADY + s % NSL), (s / NSL) & 1) && clock64() - t0 < 2000000ll) {
-          }
-        }
+        mbar_drain(bar(B_KV), 0);
+        for (int s = max(issued - NSL, 0); s < issued; ++s) mbar_drain(bar(B_QREADY + s % NSL), (s / NSL) & 1);
       }
     }
   } else if (warp == 8) {
@@ -564,7 +553,7 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (!ok) break;
         tc_fence_after();
         issue_tmemA_k64<D>(lead, tDV, tST, sdesc_lo(do_s, TILE_BYTES_64), IDESC_ACC, s > 0, 0);
-        ok = mbar_wait_warp(bar(B_P), s & 1, ctl, 14);
+        ok = mbar_wait_warp(bar(B_P), s & 1, ctl, 20);
         if (!ok) break;
         tc_fence_after();
         issue_tmemA_k64<D>(lead, tDV, tST, sdesc_lo(do_s, TILE_BYTES_64), IDESC_ACC, s > 0, 1);
@@ -587,11 +576,7 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
       if (ok) umma_commit_lead(lead, bar(B_ACC));
       umma_commit_lead(lead, bar(B_DRAIN));
-      {
-        const long long t0 = clock64();
-        while (!mbar_try_wait(bar(B_DRAIN), 0) && clock64() - t0 < KFA_WAIT_CYCLES) {
-        }
-      }
+      mbar_drain(bar(B_DRAIN), 0);
     }
   } else {
     // =========================== P^T / dS^T and epilogue ===========================
@@ -637,7 +622,6 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       if (n_steps > 0) mask_fetch(0);
     }
     for (int s = 0; s < n_steps; ++s) {
-      KFA_PROF_BEGIN();
       uint2 wcur[4];
       if constexpr (MASKW) {
 #pragma unroll
@@ -657,8 +641,6 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           reinterpret_cast<const float*>(smem + 2 * Cfg::TILE_BYTES + slot * Cfg::KV_SLOT_BYTES +
                                          2 * Cfg::TILE_BYTES) + 64 * hq + col0;
       float2 pr[32];  // fp32 P of this thread's 64 elements, kept for the dS phase
-      KFA_PROF_END(5);
-      KFA_PROF_BEGIN();
       {
         float2 sv[32];
         tmem_ld_16x256b_x8(tS, reinterpret_cast<uint32_t*>(sv));
@@ -693,13 +675,9 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tc_fence_before();
       if constexpr (D != 128) mbar_arrive(bar(B_PLO));
       mbar_arrive(bar(B_P));
-      KFA_PROF_END(3);
-      KFA_PROF_BEGIN();
       ok = mbar_wait_warp(bar(B_DP), s & 1, ctl, 19);
       if (!ok) break;
       tc_fence_after();
-      KFA_PROF_END(6);
-      KFA_PROF_BEGIN();
       {
         float2 dp[32];
         tmem_ld_16x256b_x8(tDP, reinterpret_cast<uint32_t*>(dp));
@@ -713,7 +691,6 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar(B_DS));
-      KFA_PROF_END(4);
     }
     // ---- epilogue: warps 0-3 store dV, warps 4-7 store scale * dK ----
     const bool valid = key < Skv;
@@ -734,7 +711,7 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       if (valid && p.acc_mode == 1)
         for (int cc = 0; cc < D; cc += 4) *reinterpret_cast<float4*>(grow32 + cc) = make_float4(0.f, 0.f, 0.f, 0.f);
     } else {
-      ok = mbar_wait_warp(bar(B_ACC), 0, ctl, 19) && ok;
+      ok = mbar_wait_warp(bar(B_ACC), 0, ctl, 21) && ok;
       if (ok) {
         tc_fence_after();
         const uint32_t tacc = tmem + (hq ? Cfg::TM_ACC1 : Cfg::TM_ACC0) + lane_base;
@@ -746,13 +723,19 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
   }
 
-#ifdef KFA_PROFILE
-  prof_acc[0] = clock64() - prof_t0;
-  if (lane == 0 && (warp == 0 || warp == 4 || warp == 8 || warp == 9))
-    kfa_prof_flush(prof_acc, warp == 0 ? 0 : (warp == 4 ? 1 : (warp == 8 ? 2 : 3)));
-#endif
   tc_fence_before();
   __syncthreads();
+  if (*s_abort) {  // gave up (or an earlier kernel did): the rows of this CTA read as NaN
+    const int r1 = min(kv0 + 128, Skv);
+    if (p.acc_mode == 0) {
+      fill_rows_nan16(reinterpret_cast<uint8_t*>(p.dk) + 2 * (bc * p.dk_sb + hk * p.dk_sh), p.dk_ss, k_base + kv0, k_base + r1, D);
+      fill_rows_nan16(reinterpret_cast<uint8_t*>(p.dv) + 2 * (bc * p.dv_sb + hk * p.dv_sh), p.dv_ss, k_base + kv0, k_base + r1, D);
+    } else if (r1 > kv0) {
+      const long long bhl = static_cast<long long>(b) * p.Hkv + hk;
+      fill_nan32(p.dk32 + bhl * p.dk32_sh + static_cast<long long>(kv0) * D, static_cast<long long>(r1 - kv0) * D);
+      fill_nan32(p.dv32 + bhl * p.dv32_sh + static_cast<long long>(kv0) * D, static_cast<long long>(r1 - kv0) * D);
+    }
+  }
   if (warp == 0) {
     tc_fence_after();
     tmem_dealloc(tmem, Cfg::TMEM_COLS);
@@ -867,15 +850,7 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   const uint32_t tmem = *s_tmem;
   if (use_list) n_steps = static_cast<int>(s_tmem[2]);
   auto tile_of = [&](int it) { return use_list ? static_cast<int>(s_list[it]) : it; };
-#ifdef KFA_PROFILE
-  long long prof_acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
-  long long kfa_prof_tb = 0;
-  (void)kfa_prof_tb;
-  const long long prof_t0 = clock64();
-  const Ctl ctl{s_abort, p.status, prof_acc};
-#else
   const Ctl ctl{s_abort, p.status};
-#endif
   const bool dead = (*s_abort != 0);
 
   if (dead) {
@@ -894,14 +869,14 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       int issued_k = 0, issued_v = 0;
       for (int j = 0; j < n_steps; ++j) {
         const int ks = j % NK, vs = j % NV;
-        if (j >= NK) ok = mbar_wait(bar(B_KFREE + ks), (j / NK - 1) & 1, ctl, 21);
+        if (j >= NK) ok = mbar_wait(bar(B_KFREE + ks), (j / NK - 1) & 1, ctl, 51);
         if (!ok) break;
         mbar_expect_tx(bar(B_KREADY + ks), Cfg::TILE_BYTES);
         for (int ch = 0; ch < CH; ++ch)
           tma_load_4d(sKr + ks * Cfg::TILE_BYTES + ch * TILE_BYTES_64, &tmK, bar(B_KREADY + ks), ch * 64,
                       k_base + tile_of(j) * 128, h / p.group, bc);
         issued_k = j + 1;
-        if (j >= NV) ok = mbar_wait(bar(B_VFREE + vs), (j / NV - 1) & 1, ctl, 21);
+        if (j >= NV) ok = mbar_wait(bar(B_VFREE + vs), (j / NV - 1) & 1, ctl, 52);
         if (!ok) break;
         mbar_expect_tx(bar(B_VREADY + vs), Cfg::TILE_BYTES);
         for (int ch = 0; ch < CH; ++ch)
@@ -910,16 +885,9 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         issued_v = j + 1;
       }
       if (!ok) {  // aborting: let the copies in flight land before the CTA gives up its shared memory
-        for (int j = max(issued_k - NK, 0); j < issued_k; ++j) {
-          const long long t0 = clock64();
-          while (!mbar_try_wait(bar(B_KREADY + j % NK), (j / NK) & 1) && clock64() - t0 < 2000000ll) {
-          }
-        }
-        for (int j = max(issued_v - NV, 0); j < issued_v; ++j) {
-          const long long t0 = clock64();
-          while (!mbar_try_wait(bar(B_VREADY + j % NV), (j / NV) & 1) && clock64() - t0 < 2000000ll) {
-          }
-        }
+        mbar_drain(bar(B_Q), 0);
+        for (int j = max(issued_k - NK, 0); j < issued_k; ++j) mbar_drain(bar(B_KREADY + j % NK), (j / NK) & 1);
+        for (int j = max(issued_v - NV, 0); j < issued_v; ++j) mbar_drain(bar(B_VREADY + j % NV), (j / NV) & 1);
       }
     }
   } else if (warp == 8) {
@@ -930,13 +898,13 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       constexpr uint32_t IDESC_ACC = make_idesc(BF16, true, 128, D);
       const uint32_t tS = tmem + Cfg::TM_S, tDP = tmem + Cfg::TM_DP, tDQ = tmem + Cfg::TM_ACC0;
       const uint32_t q_lo = sdesc_lo(sQ, 16), do_lo = sdesc_lo(sDO, 16);
-      bool ok = mbar_wait_warp(bar(B_Q), 0, ctl, 22);
-      if (ok) ok = mbar_wait_warp(bar(B_KREADY + 0), 0, ctl, 23);
+      bool ok = mbar_wait_warp(bar(B_Q), 0, ctl, 53);
+      if (ok) ok = mbar_wait_warp(bar(B_KREADY + 0), 0, ctl, 54);
       if (ok) {
         tc_fence_after();
         issue_kmajor_n128<D>(lead, tS, q_lo, sdesc_lo(sKr, 16), IDESC_S);
         umma_commit_lead(lead, bar(B_S));
-        ok = mbar_wait_warp(bar(B_VREADY + 0), 0, ctl, 23);
+        ok = mbar_wait_warp(bar(B_VREADY + 0), 0, ctl, 55);
       }
       if (ok) {
         tc_fence_after();
@@ -949,21 +917,21 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         const int nk = (j + 1) % NK, nv = (j + 1) % NV;
         const bool more = j + 1 < n_steps;
         if (more) {  // S(j+1) as soon as the warpgroups hold S(j) in registers
-          ok = mbar_wait_warp(bar(B_KREADY + nk), ((j + 1) / NK) & 1, ctl, 24);
-          if (ok) ok = mbar_wait_warp(bar(B_SREAD), j & 1, ctl, 25);
+          ok = mbar_wait_warp(bar(B_KREADY + nk), ((j + 1) / NK) & 1, ctl, 56);
+          if (ok) ok = mbar_wait_warp(bar(B_SREAD), j & 1, ctl, 57);
           if (!ok) break;
           tc_fence_after();
           issue_kmajor_n128<D>(lead, tS, q_lo, sdesc_lo(sKr + nk * Cfg::TILE_BYTES, 16), IDESC_S);
           umma_commit_lead(lead, bar(B_S));
         }
         // dQ += dS(j) K_j, then dP(j+1) may overwrite the dS columns
-        ok = mbar_wait_warp(bar(B_DS), j & 1, ctl, 26);
+        ok = mbar_wait_warp(bar(B_DS), j & 1, ctl, 58);
         if (!ok) break;
         tc_fence_after();
         issue_tmemA_k128<D>(lead, tDQ, tDP, sdesc_lo(k_s, TILE_BYTES_64), IDESC_ACC, j > 0);
         umma_commit_lead(lead, bar(B_KFREE + j % NK));
         if (more) {
-          ok = mbar_wait_warp(bar(B_VREADY + nv), ((j + 1) / NV) & 1, ctl, 24);
+          ok = mbar_wait_warp(bar(B_VREADY + nv), ((j + 1) / NV) & 1, ctl, 59);
           if (!ok) break;
           tc_fence_after();
           issue_kmajor_n128<D>(lead, tDP, do_lo, sdesc_lo(sVr + nv * Cfg::TILE_BYTES, 16), IDESC_S);
@@ -973,11 +941,7 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       }
       if (ok) umma_commit_lead(lead, bar(B_ACC));
       umma_commit_lead(lead, bar(B_DRAIN));
-      {
-        const long long t0 = clock64();
-        while (!mbar_try_wait(bar(B_DRAIN), 0) && clock64() - t0 < KFA_WAIT_CYCLES) {
-        }
-      }
+      mbar_drain(bar(B_DRAIN), 0);
     }
   } else {
     const int hk = warp >> 2;  // which 64 key columns of every tile
@@ -1006,12 +970,11 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       if constexpr (MASKW) {
         if (j + 1 < n_steps) mnext = __ldg(mrow + 2 * tile_of(j + 1));
       }
-      ok = mbar_wait_warp(bar(B_S), j & 1, ctl, 27);
+      ok = mbar_wait_warp(bar(B_S), j & 1, ctl, 60);
       if (!ok) break;
       tc_fence_after();
       const int lim = my_limit - j * 128 - 64 * hk;  // visible columns of this warpgroup (masked tiles)
       float2 pr[32];
-      KFA_PROF_BEGIN();
       {
         float2 sv[32];
         tmem_ld32(tS, reinterpret_cast<uint32_t*>(sv));
@@ -1029,11 +992,9 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             p_cols_by_key<false>(sv + 16 * g, nm, c2, nl, 32, pr + 16 * g);
         }
       }
-      KFA_PROF_END(3);
-      ok = mbar_wait_warp(bar(B_DP), j & 1, ctl, 28);
+      ok = mbar_wait_warp(bar(B_DP), j & 1, ctl, 61);
       if (!ok) break;
       tc_fence_after();
-      KFA_PROF_BEGIN();
       {
         float2 dp[32];
         tmem_ld32(tDP, reinterpret_cast<uint32_t*>(dp));
@@ -1049,9 +1010,8 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar(B_DS));
-      KFA_PROF_END(4);
     }
-    ok = mbar_wait_warp(bar(B_ACC), 0, ctl, 29) && ok;
+    ok = mbar_wait_warp(bar(B_ACC), 0, ctl, 62) && ok;
     if (ok) {
       tc_fence_after();
       if (p.acc_mode == 0) {
@@ -1066,13 +1026,16 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     }
   }
 
-#ifdef KFA_PROFILE
-  prof_acc[0] = clock64() - prof_t0;
-  if (lane == 0 && (warp == 0 || warp == 4 || warp == 8 || warp == 9))
-    kfa_prof_flush(prof_acc, warp == 0 ? 0 : (warp == 4 ? 1 : (warp == 8 ? 2 : 3)));
-#endif
   tc_fence_before();
   __syncthreads();
+  if (*s_abort) {  // gave up (or an earlier kernel did): the rows of this CTA read as NaN
+    const int r1 = min(row0 + 128, Sq);
+    if (p.acc_mode == 0)
+      fill_rows_nan16(reinterpret_cast<uint8_t*>(p.dq) + 2 * (bc * p.dq_sb + h * p.dq_sh), p.dq_ss, q_base + row0, q_base + r1, D);
+    else if (r1 > row0)
+      fill_nan32(p.dq32 + (static_cast<long long>(b) * p.H + h) * p.dq32_sh + static_cast<long long>(row0) * D,
+                 static_cast<long long>(r1 - row0) * D);
+  }
   if (warp == 0) {
     tc_fence_after();
     tmem_dealloc(tmem, Cfg::TMEM_COLS);

@@ -41,8 +41,8 @@ namespace kfa {
 constexpr int FUSED_THREADS = 512;
 // Registers per thread: the kernel starts with 128 everywhere (512 threads x 128 = the whole register
 // file); the dQ warpgroup and the MMA + TMA warpgroup then hand registers to the P / dS warpgroups:
-// 2 x 128 x 176 + 128 x 96 + 128 x 64 = 65536.
-constexpr int FUSED_REGS_COMPUTE = 176, FUSED_REGS_REDUCE = 96, FUSED_REGS_ISSUE = 64;
+// 2 x 128 x 144 + 128 x 152 + 128 x 64 = 64512 (the dQ warpgroup holds a whole 128 x 128 fp32 tile).
+constexpr int FUSED_REGS_COMPUTE = 144, FUSED_REGS_REDUCE = 152, FUSED_REGS_ISSUE = 64;
 
 template <int D>
 struct FusedCfg {
@@ -51,11 +51,34 @@ struct FusedCfg {
   // Q_i is read first by S^T(i) and last by dK(i), a whole step later, and S^T(i+1) is issued before
   // dK(i): three slots let the copy of Q_(i+2) start a step ahead. dO_i is done after dV(i), long
   // before dP^T(i+1) can be issued: one slot is enough at D = 128 (where no more fit), two at D = 64.
-  static constexpr int NQ = 3;
-  static constexpr int NDO = (D == 128) ? 1 : 2;
+#ifndef KFA_EXP_NQ128
+#define KFA_EXP_NQ128 3
+#endif
+#ifndef KFA_EXP_NDO128
+#define KFA_EXP_NDO128 1
+#endif
+#ifndef KFA_EXP_DOBUFS128
+#define KFA_EXP_DOBUFS128 KFA_EXP_NDO128
+#endif
+  static constexpr int NQ = (D == 128) ? KFA_EXP_NQ128 : 3;
+  static constexpr int NDO = (D == 128) ? KFA_EXP_NDO128 : 2;
+  static constexpr int DO_BUFS = (D == 128) ? KFA_EXP_DOBUFS128 : 2;
   static constexpr int DS_BYTES = 2 * TILE_BYTES_64;  // dS^T: two [128 keys][64 queries] boxes
-  static constexpr int SMEM_TILES = (2 + NQ + NDO) * TILE_BYTES + DS_BYTES;
-  static constexpr int SMEM_BYTES = SMEM_TILES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  // dQ staging for the bulk reduce-adds: two buffers of 128 rows x 32 columns fp32
+#ifdef KFA_DQ_VIA_TMA
+  static constexpr int STAGE_BYTES = 2 * 128 * 32 * 4;
+#else
+  static constexpr int STAGE_BYTES = 0;
+#endif
+  static constexpr int SMEM_TILES = (2 + NQ + DO_BUFS) * TILE_BYTES + DS_BYTES + STAGE_BYTES;
+  // per-query statistics of a step: (-m, -log2 l) double-buffered (read by the P phase), -delta single
+  // (read by the dS phase, reloaded while the next P phase runs)
+  static constexpr int ML_BYTES = 2 * 128 * 4, DELTA_BYTES = 128 * 4;
+  static constexpr int STATS_SMEM = 2 * ML_BYTES + DELTA_BYTES;
+  // At D = 128 the tiles fill the 227 KB to within 3 KB: no room for alignment slack, the kernel relies on
+  // (and checks) a 1024-byte aligned dynamic shared memory base.
+  static constexpr int ALIGN_SLACK = (D == 128) ? 0 : 1024;
+  static constexpr int SMEM_BYTES = SMEM_TILES + STATS_SMEM + 256 /*barriers*/ + ALIGN_SLACK;
   static constexpr uint32_t TMEM_COLS = 512;
   static constexpr uint32_t TM_S = 0, TM_DP = 128, TM_DV = 256, TM_DK = 256 + D;
   static constexpr uint32_t TM_DQ = (D == 128) ? TM_DP : 256 + 2 * D;
@@ -63,21 +86,8 @@ struct FusedCfg {
 };
 static_assert(FusedCfg<128>::SMEM_BYTES <= 232448 && FusedCfg<64>::SMEM_BYTES <= 232448, "shared memory");
 
-template <int N>
-__device__ __forceinline__ void reg_budget_inc() {
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
-}
-template <int N>
-__device__ __forceinline__ void reg_budget_dec() {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
-}
-
 __device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
-
-__device__ __forceinline__ void prefetch_l1(const void* p) {
-  asm volatile("prefetch.global.L1 [%0];" ::"l"(p));
 }
 
 // Instruction descriptor with the A operand MN-major as well (bit 15): dQ = dS K reads dS^T's shared-memory
@@ -86,41 +96,18 @@ __host__ __device__ constexpr uint32_t make_idesc_amn(bool bf16, int m, int n) {
   return make_idesc(bf16, true, m, n) | (1u << 15);
 }
 
-// P^T of the thread's 4 keys x 16 queries (see p_frag in kfa_bwd.cuh for the element order), with the
-// per-query statistics read from global memory (they stay in L1: the tile was prefetched a step ahead).
-template <bool BF16, bool MASKED, int J0>
-__device__ __forceinline__ void p_frag_g(const float2* sv, const float* st, float2 c2, int q_first, const int* qmin,
-                                         float2* pr, uint32_t* pk) {
-#pragma unroll
-  for (int j = J0; j < J0 + 4; ++j) {
-    const float2 nm = __ldg(reinterpret_cast<const float2*>(st + 8 * j));
-    const float2 nl = __ldg(reinterpret_cast<const float2*>(st + 128 + 8 * j));
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int idx = 16 * (e >> 1) + 2 * j + (e & 1);
-      const float2 x = __ffma2_rn(__fadd2_rn(sv[idx], nm), c2, nl);
-      float2 pv = make_float2(ex2(x.x), ex2(x.y));
-      if constexpr (MASKED) {
-        if (q_first + 8 * j < qmin[e]) pv.x = 0.f;
-        if (q_first + 8 * j + 1 < qmin[e]) pv.y = 0.f;
-      }
-      pr[idx] = pv;
-      pk[idx] = pack16<BF16>(pv.x, pv.y);
-    }
-  }
-}
-
 // dS^T = (dP^T - delta) * P of the same elements, rounded once to 16 bits, unscaled, written to the
 // 128-byte swizzled [key][64 queries] box of this warpgroup: element order as above, so word
 // (key row, query pair 8j + 2(lane % 4)) lands in 16-byte chunk j ^ (row % 8) of its row.
+// nd: -delta of this thread's first column, in shared memory.
 template <bool BF16>
-__device__ __forceinline__ void ds_frag_to_smem(const float2* dp, const float2* pr, const float* st, uint32_t s_row0,
+__device__ __forceinline__ void ds_frag_to_smem(const float2* dp, const float2* pr, const float* nd_s, uint32_t s_row0,
                                                 int lane) {
   const uint32_t sw = static_cast<uint32_t>(lane >> 2);  // row % 8 of every row this thread owns
   const uint32_t word = static_cast<uint32_t>(lane & 3) * 4u;
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
-    const float2 nd = __ldg(reinterpret_cast<const float2*>(st + 256 + 8 * j));
+    const float2 nd = *reinterpret_cast<const float2*>(nd_s + 8 * j);
     const uint32_t col = ((static_cast<uint32_t>(j) ^ sw) << 4) + word;
 #pragma unroll
     for (int e = 0; e < 4; ++e) {  // e = 2 * half + sel: row offset 16 * half + 8 * sel
@@ -170,15 +157,24 @@ kfa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   constexpr int NQ = Cfg::NQ, NDO = Cfg::NDO;
   constexpr int TB = Cfg::TILE_BYTES;
 
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + static_cast<uint32_t>(Cfg::ALIGN_SLACK ? 1023 : 0)) & ~static_cast<uint32_t>(Cfg::ALIGN_SLACK ? 1023 : 0);
+  if ((smem_base & 1023u) != 0u) {  // (never seen; the swizzled tiles would be garbage: report and leave)
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, KFA_DEV_BAD_SMEM_BASE);
+    return;
+  }
   uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t sK = smem_base;
   const uint32_t sV = smem_base + TB;
   const uint32_t sQ = smem_base + 2 * TB;           // ring of NQ
   const uint32_t sDO = sQ + NQ * TB;                // ring of NDO
-  const uint32_t sDS = sDO + NDO * TB;              // dS^T
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::SMEM_TILES);
+  const uint32_t sDS = sDO + Cfg::DO_BUFS * TB;     // dS^T
+  const uint32_t sStage = sDS + Cfg::DS_BYTES;       // dQ staging (if any)
+  const uint32_t sML = smem_base + Cfg::SMEM_TILES;  // 2 x (-m[128], -log2 l[128])
+  const uint32_t sDL = sML + 2 * Cfg::ML_BYTES;      // -delta[128]
+  const float* ml_smem = reinterpret_cast<const float*>(smem + Cfg::SMEM_TILES);
+  const float* dl_smem = ml_smem + 2 * Cfg::ML_BYTES / 4;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::SMEM_TILES + Cfg::STATS_SMEM);
   constexpr int B_KV = 0;                      // K, V landed
   constexpr int B_QREADY = 1;                  // NQ
   constexpr int B_QFREE = B_QREADY + NQ;       // NQ   dK(i), the last reader of Q_i, has retired
@@ -194,7 +190,13 @@ kfa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   constexpr int B_DQFREE = B_S + 7;            // dQ(i) copied to registers (128 arrivals)
   constexpr int B_ACC = B_S + 8;               // dV, dK complete
   constexpr int B_DRAIN = B_S + 9;
-  constexpr int N_BARS = B_S + 10;
+  constexpr int B_MLREADY = B_S + 10;          // 2   (-m, -log2 l) of a step landed
+  constexpr int B_MLFREE = B_S + 12;           // 2   both warpgroups are done with them (256 arrivals)
+  constexpr int B_DLREADY = B_S + 14;          // -delta of a step landed
+  constexpr int B_DLFREE = B_S + 15;           // both warpgroups are done with it (256 arrivals)
+  constexpr int B_STGFREE = B_S + 16;          // dQ staging: the buffer about to be written has been read out
+  constexpr int B_STGFULL = B_S + 17;          // dQ staging: all 128 threads have written their part
+  constexpr int N_BARS = B_S + 18;
   static_assert(N_BARS * 8 + 16 <= 256, "barrier block too small");
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + N_BARS);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
@@ -243,6 +245,14 @@ kfa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     mbar_init(bar(B_DQFREE), 128);
     mbar_init(bar(B_ACC), 1);
     mbar_init(bar(B_DRAIN), 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(B_MLREADY + i), 1);
+      mbar_init(bar(B_MLFREE + i), 256);
+    }
+    mbar_init(bar(B_DLREADY), 1);
+    mbar_init(bar(B_DLFREE), 256);
+    mbar_init(bar(B_STGFREE), 1);
+    mbar_init(bar(B_STGFULL), 128);
     *s_abort = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
     fence_mbar_init();
   }
@@ -261,10 +271,33 @@ kfa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   // up, the others wait until theirs are available.
   if (dead) {
   } else if (warp == 15) {
-    reg_budget_dec<FUSED_REGS_ISSUE>();
+    // =========================== copies of the per-query statistics ===========================
+    reg_budget<FUSED_REGS_ISSUE>();
+    if (lane == 0 && n_steps > 0) {
+      bool ok = true;
+      int ml_issued = 0, dl_issued = 0;
+      for (int s = 0; s < n_steps; ++s) {
+        const float* src = p.stats + (static_cast<long long>(b) * p.H + head_of(s)) * p.stats_sh + tile_of(s) * 384ll;
+        const int slot = s & 1, use = s >> 1;
+        if (use > 0) ok = mbar_wait(bar(B_MLFREE + slot), (use - 1) & 1, ctl, 48);
+        if (!ok) break;
+        mbar_expect_tx(bar(B_MLREADY + slot), Cfg::ML_BYTES);
+        bulk_load(sML + slot * Cfg::ML_BYTES, src, Cfg::ML_BYTES, bar(B_MLREADY + slot));
+        ml_issued = s + 1;
+        if (s > 0) ok = mbar_wait(bar(B_DLFREE), (s - 1) & 1, ctl, 49);
+        if (!ok) break;
+        mbar_expect_tx(bar(B_DLREADY), Cfg::DELTA_BYTES);
+        bulk_load(sDL, src + 256, Cfg::DELTA_BYTES, bar(B_DLREADY));
+        dl_issued = s + 1;
+      }
+      if (!ok) {
+        for (int s = max(ml_issued - 2, 0); s < ml_issued; ++s) mbar_drain(bar(B_MLREADY + (s & 1)), (s >> 1) & 1);
+        if (dl_issued > 0) mbar_drain(bar(B_DLREADY), (dl_issued - 1) & 1);
+      }
+    }
   } else if (warp == 13) {
     // =========================== TMA producer: K, V, then the Q ring ===========================
-    reg_budget_dec<FUSED_REGS_ISSUE>();
+    reg_budget<FUSED_REGS_ISSUE>();
     if (lane == 0 && n_steps > 0) {
       prefetch_tensormap(&tmQ);
       prefetch_tensormap(&tmK);
@@ -287,16 +320,13 @@ kfa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         issued = s + 1;
       }
       if (!ok) {  // aborting: let the copies in flight land before the CTA gives up its shared memory
-        for (int s = max(issued - NQ, 0); s < issued; ++s) {
-          const long long t0 = clock64();
-          while (!mbar_try_wait(bar(B_QREADY + s % NQ), (s / NQ) & 1) && clock64() - t0 < 2000000ll) {
-          }
-        }
+        mbar_drain(bar(B_KV), 0);
+        for (int s = max(issued - NQ, 0); s < issued; ++s) mbar_drain(bar(B_QREADY + s % NQ), (s / NQ) & 1);
       }
     }
   } else if (warp == 14) {
     // =========================== TMA producer: the dO ring ===========================
-    reg_budget_dec<FUSED_REGS_ISSUE>();
+    reg_budget<FUSED_REGS_ISSUE>();
     if (lane == 0 && n_steps > 0) {
       prefetch_tensormap(&tmDO);
       bool ok = true;
@@ -307,21 +337,16 @@ kfa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         if (!ok) break;
         mbar_expect_tx(bar(B_DOREADY + slot), TB);
         for (int ch = 0; ch < CH; ++ch)
-          tma_load_4d(sDO + slot * TB + ch * TILE_BYTES_64, &tmDO, bar(B_DOREADY + slot), ch * 64, tile_of(s) * 128,
+          tma_load_4d(sDO + (slot % Cfg::DO_BUFS) * TB + ch * TILE_BYTES_64, &tmDO, bar(B_DOREADY + slot), ch * 64, tile_of(s) * 128,
                       head_of(s), b);
         issued = s + 1;
       }
-      if (!ok) {
-        for (int s = max(issued - NDO, 0); s < issued; ++s) {
-          const long long t0 = clock64();
-          while (!mbar_try_wait(bar(B_DOREADY + s % NDO), (s / NDO) & 1) && clock64() - t0 < 2000000ll) {
-          }
-        }
-      }
+      if (!ok)
+        for (int s = max(issued - NDO, 0); s < issued; ++s) mbar_drain(bar(B_DOREADY + s % NDO), (s / NDO) & 1);
     }
   } else if (warp == 12) {
     // =========================== MMA issue ===========================
-    reg_budget_dec<FUSED_REGS_ISSUE>();
+    reg_budget<FUSED_REGS_ISSUE>();
     if (n_steps > 0) {
       const bool lead = elect_one();
       constexpr uint32_t IDESC_S = make_idesc(BF16, false, 128, 128);   // A, B K-major
@@ -347,7 +372,7 @@ kfa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       }
       for (int s = 0; s < n_steps && ok; ++s) {
         const uint32_t q_s = sQ + (s % NQ) * TB;
-        const uint32_t do_s = sDO + (s % NDO) * TB;
+        const uint32_t do_s = sDO + ((s % NDO) % Cfg::DO_BUFS) * TB;
         const bool more = s + 1 < n_steps;
         // dV += P^T(s) dO_s in two parts (the first 32 queries of each warpgroup's P^T are signalled
         // early), then S^T(s+1) may overwrite the P^T columns
@@ -386,21 +411,17 @@ kfa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           if (ok && Cfg::DQ_ALIASES_DP) ok = mbar_wait_warp(bar(B_DQFREE), s & 1, ctl, 42);
           if (!ok) break;
           tc_fence_after();
-          issue_kmajor_n128<D>(lead, tDP, v_lo, sdesc_lo(sDO + ((s + 1) % NDO) * TB, 16), IDESC_S);
+          issue_kmajor_n128<D>(lead, tDP, v_lo, sdesc_lo(sDO + (((s + 1) % NDO) % Cfg::DO_BUFS) * TB, 16), IDESC_S);
           umma_commit_lead(lead, bar(B_DP));
         }
       }
       if (ok) umma_commit_lead(lead, bar(B_ACC));
       umma_commit_lead(lead, bar(B_DRAIN));
-      {
-        const long long t0 = clock64();
-        while (!mbar_try_wait(bar(B_DRAIN), 0) && clock64() - t0 < KFA_WAIT_CYCLES) {
-        }
-      }
+      mbar_drain(bar(B_DRAIN), 0);
     }
   } else if (warp >= 8 && warp < 12) {
     // =========================== dQ: TMEM -> registers -> reduce-adds ===========================
-    reg_budget_dec<FUSED_REGS_REDUCE>();
+    reg_budget<FUSED_REGS_REDUCE>();
     const int r_in = tid & 127;
     const uint32_t tDQ = tmem + Cfg::TM_DQ + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     bool ok = true;
@@ -410,31 +431,77 @@ kfa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       ok = mbar_wait_warp(bar(B_DQ), s & 1, ctl, 43);
       if (!ok) break;
       tc_fence_after();
-      // 64 columns at a time (a thread's registers hold no more): the first half's adds are under way
-      // while the second half is read; the columns are free once that read has completed
+      // the whole tile goes to registers first, so that its columns are free at once (dP^T of the next step
+      // is waiting for them at D = 128); the adds then drain at the rate the memory system takes them
       float* dst = dq_acc + (static_cast<long long>(b) * p.H + head) * dq_acc_head_floats(Sq, D) +
                    static_cast<long long>(i) * (128 * D) + r_in * 4;
       const bool valid = i * 128 + r_in < Sq;  // (padded query rows hold exact zeros)
+      float v[D];
 #pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 64) {
-        float v[64];
-        tmem_ld32(tDQ + c0, reinterpret_cast<uint32_t*>(v));
-        tmem_ld32(tDQ + c0 + 32, reinterpret_cast<uint32_t*>(v + 32));
-        tmem_wait_ld();
-        if (c0 + 64 == D) {
-          tc_fence_before();
-          mbar_arrive(bar(B_DQFREE));
+      for (int c = 0; c < D; c += 32) tmem_ld32(tDQ + c, reinterpret_cast<uint32_t*>(v + c));
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(bar(B_DQFREE));
+#ifdef KFA_DQ_VIA_TMA
+      // Through shared memory to the copy engine: 32 columns (16 KB) at a time into one of two staging
+      // buffers laid out like the accumulator ([4-column group][row][4]), each then added to global memory
+      // by one bulk reduce. The thread that issues the copies (the warpgroup's first) also owns their
+      // completion groups: before a buffer is rewritten, the reduce two commits back has read it.
+      (void)valid;
+      (void)dst;
+      float* tile = dq_acc + (static_cast<long long>(b) * p.H + head) * dq_acc_head_floats(Sq, D) +
+                    static_cast<long long>(i) * (128 * D);
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        const uint32_t buf = sStage + (c & 1) * 16384;
+        const uint32_t n = static_cast<uint32_t>(s) * (D / 32) + c;  // running count of staged pieces
+        if (tid == 256) {
+          asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          mbar_arrive(bar(B_STGFREE));
         }
-        if (valid) {
+        ok = mbar_wait_warp(bar(B_STGFREE), n & 1, ctl, 29);
+        if (!ok) break;
 #pragma unroll
-          for (int c4 = 0; c4 < 16; ++c4)
-            red_add_v4(dst + (c0 / 4 + c4) * 512, v[4 * c4], v[4 * c4 + 1], v[4 * c4 + 2], v[4 * c4 + 3]);
+        for (int g = 0; g < 8; ++g) {
+          const uint32_t addr = buf + (g * 128 + r_in) * 16;
+          asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v[32 * c + 4 * g]),
+                       "f"(v[32 * c + 4 * g + 1]), "f"(v[32 * c + 4 * g + 2]), "f"(v[32 * c + 4 * g + 3])
+                       : "memory");
+        }
+        fence_async_smem();
+        mbar_arrive(bar(B_STGFULL));
+        if (tid == 256) {
+          if (mbar_wait(bar(B_STGFULL), n & 1, ctl, 28)) {
+            asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(tile + c * 4096),
+                         "r"(buf), "r"(16384)
+                         : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
         }
       }
+      if (!ok) break;
+#else
+#ifdef KFA_EXP_NO_RED
+      if (valid && p.scale == 12345.f) {
+#else
+      if (valid) {
+#endif
+#pragma unroll
+        for (int c4 = 0; c4 < D / 4; ++c4) {
+          red_add_v4(dst + c4 * 512, v[4 * c4], v[4 * c4 + 1], v[4 * c4 + 2], v[4 * c4 + 3]);
+#ifdef KFA_RED_PACE_NS
+          if ((c4 & 3) == 3) __nanosleep(KFA_RED_PACE_NS);
+#endif
+        }
+      }
+#endif
     }
+#ifdef KFA_DQ_VIA_TMA
+    if (tid == 256) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // shared memory stays valid until read
+#endif
   } else if (warp < 8) {
     // =========================== P^T / dS^T and the dV / dK epilogue ===========================
-    reg_budget_inc<FUSED_REGS_COMPUTE>();
+    reg_budget<FUSED_REGS_COMPUTE>();
     const int hq = warp >> 2;  // which 64 query columns of every tile
     const int k_in = tid & 127;
     const int key = kv0 + k_in;  // the epilogue's row (one TMEM lane per thread)
@@ -457,18 +524,14 @@ kfa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     const uint32_t s_row0 = sDS + hq * TILE_BYTES_64 + static_cast<uint32_t>((warp & 3) * 32 + (lane >> 2)) * 128u;
     const float2 c2 = make_float2(p.c, p.c);
     bool ok = true;
-    auto stats_of = [&](int s) {
-      return p.stats + (static_cast<long long>(b) * p.H + head_of(s)) * p.stats_sh + tile_of(s) * 384ll;
-    };
-    if (n_steps > 0 && k_in < 12 && hq == 0) prefetch_l1(stats_of(0) + 32 * k_in);
     for (int s = 0; s < n_steps; ++s) {
       const int i = tile_of(s);
       const int q0 = i * 128 + 64 * hq + col0;  // query of this thread's first column
       // masked step: some (key, query) pair of this tile pair is hidden, or keys are padded
       const bool masked = ragged_keys || (p.P > 0 && key_limit(i * 128, p.P, Skv) < kv0 + 128);
-      const float* st = stats_of(s) + 64 * hq + col0;
-      if (s + 1 < n_steps && k_in < 12 && hq == 0) prefetch_l1(stats_of(s + 1) + 32 * k_in);
-      ok = mbar_wait_warp(bar(B_S), s & 1, ctl, 44);
+      const float* st = ml_smem + (s & 1) * (Cfg::ML_BYTES / 4) + 64 * hq + col0;  // -m here, -log2 l 128 floats on
+      ok = mbar_wait_warp(bar(B_MLREADY + (s & 1)), (s >> 1) & 1, ctl, 50);
+      if (ok) ok = mbar_wait_warp(bar(B_S), s & 1, ctl, 44);
       if (!ok) break;
       tc_fence_after();
       float2 pr[32];  // fp32 P of this thread's 64 elements, kept for the dS phase
@@ -481,9 +544,9 @@ kfa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         // 16-bit P^T goes over the first 32 of the 64 columns this warp has just read (all its lanes),
         // in two parts of 32 queries (16 packed columns) each
         if (masked)
-          p_frag_g<BF16, true, 0>(sv, st, c2, q0, qmin, pr, pk);
+          p_frag<BF16, true, 0>(sv, st, c2, q0, qmin, pr, pk);
         else
-          p_frag_g<BF16, false, 0>(sv, st, c2, q0, qmin, pr, pk);
+          p_frag<BF16, false, 0>(sv, st, c2, q0, qmin, pr, pk);
         tmem_st_16x128b_x4(tS, pk);
         tmem_st_16x128b_x4(tS + HALF, pk + 16);
         if constexpr (D == 128) {  // (at D = 64 the dV MMA is too short for the early start to pay)
@@ -492,9 +555,9 @@ kfa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           mbar_arrive(bar(B_PLO));
         }
         if (masked)
-          p_frag_g<BF16, true, 4>(sv, st, c2, q0, qmin, pr, pk);
+          p_frag<BF16, true, 4>(sv, st, c2, q0, qmin, pr, pk);
         else
-          p_frag_g<BF16, false, 4>(sv, st, c2, q0, qmin, pr, pk);
+          p_frag<BF16, false, 4>(sv, st, c2, q0, qmin, pr, pk);
         tmem_st_16x128b_x4(tS + 16, pk + 8);
         tmem_st_16x128b_x4(tS + HALF + 16, pk + 24);
       }
@@ -502,8 +565,10 @@ kfa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       tc_fence_before();
       if constexpr (D != 128) mbar_arrive(bar(B_PLO));
       mbar_arrive(bar(B_P));
+      mbar_arrive(bar(B_MLFREE + (s & 1)));
       ok = mbar_wait_warp(bar(B_DP), s & 1, ctl, 45);
       if (ok && s > 0) ok = mbar_wait_warp(bar(B_DSFREE), (s - 1) & 1, ctl, 46);
+      if (ok) ok = mbar_wait_warp(bar(B_DLREADY), s & 1, ctl, 30);
       if (!ok) break;
       tc_fence_after();
       {
@@ -511,11 +576,12 @@ kfa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         tmem_ld_16x256b_x8(tDP, reinterpret_cast<uint32_t*>(dp));
         tmem_ld_16x256b_x8(tDP + HALF, reinterpret_cast<uint32_t*>(dp + 16));
         tmem_wait_ld();
-        ds_frag_to_smem<BF16>(dp, pr, st, s_row0, lane);
+        ds_frag_to_smem<BF16>(dp, pr, dl_smem + 64 * hq + col0, s_row0, lane);
       }
       fence_async_smem();  // the MMAs read dS^T through the async proxy
       tc_fence_before();
       mbar_arrive(bar(B_DS));
+      mbar_arrive(bar(B_DLFREE));
     }
     // ---- epilogue: warps 0-3 store dV, warps 4-7 store scale * dK ----
     const bool valid = key < Skv;
@@ -539,18 +605,23 @@ kfa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   tc_fence_before();
   __syncthreads();
+  if (*s_abort) {  // gave up (or an earlier kernel did): dK, dV rows of this CTA read as NaN (dQ: see the convert kernel)
+    const int r1 = min(kv0 + 128, Skv);
+    fill_rows_nan16(reinterpret_cast<uint8_t*>(p.dk) + 2 * (b * p.dk_sb + hk * p.dk_sh), p.dk_ss, kv0, r1, D);
+    fill_rows_nan16(reinterpret_cast<uint8_t*>(p.dv) + 2 * (b * p.dv_sb + hk * p.dv_sh), p.dv_ss, kv0, r1, D);
+  }
   if (warp == 0) {
     tc_fence_after();
     tmem_dealloc(tmem, Cfg::TMEM_COLS);
   }
 }
 
-// dq = 16-bit(scale * accumulator): one CTA per (128-query tile, batch x head); the accumulator tile is
+// dq = 16-bit(scale * accumulator), or NaN if the status word says that a kernel gave up: one CTA per (128-query tile, batch x head); the accumulator tile is
 // [D / 4][128 rows][4] floats (see above), so a warp reads 512 contiguous bytes per load.
 template <int D, bool BF16>
 __global__ void __launch_bounds__(256) kfa_bwd_dq_convert_kernel(const float* __restrict__ dq_acc, void* dq,
                                                                  long long dq_sb, long long dq_sh, long long dq_ss,
-                                                                 int H, int Sq, float scale) {
+                                                                 int H, int Sq, float scale, const int* status) {
   const int tile = blockIdx.x, bh = blockIdx.y;
   const int b = bh / H, h = bh % H;
   const int r_in = threadIdx.x & 127, half = threadIdx.x >> 7;
@@ -559,6 +630,11 @@ __global__ void __launch_bounds__(256) kfa_bwd_dq_convert_kernel(const float* __
   const float* src = dq_acc + static_cast<long long>(bh) * dq_acc_head_floats(Sq, D) +
                      static_cast<long long>(tile) * (128 * D) + r_in * 4;
   uint8_t* drow = reinterpret_cast<uint8_t*>(dq) + 2 * (b * dq_sb + h * dq_sh + static_cast<long long>(row) * dq_ss);
+  if (*status != 0) {  // a kernel before this one gave up: the accumulator is incomplete
+    for (int c8 = half * (D / 16); c8 < (half + 1) * (D / 16); ++c8)
+      *reinterpret_cast<uint4*>(drow + 16 * c8) = make_uint4(0x7fff7fffu, 0x7fff7fffu, 0x7fff7fffu, 0x7fff7fffu);
+    return;
+  }
 #pragma unroll
   for (int c8 = half * (D / 16); c8 < (half + 1) * (D / 16); ++c8) {
     const float4 a = *reinterpret_cast<const float4*>(src + (2 * c8) * 512);

@@ -5,11 +5,14 @@
 // Replaces the reference's Gluon forward (src/kohakufa/sm100/fwd.py:1065-1136 kernel,
 // 578-1039 partitions, 76-418 tile scheduler) with a hand-written kernel:
 //
-//   CTA = 256 query rows of one (batch, head), as two 128-row halves; key tiles of 128.
-//   warps 0-3   softmax + correction + epilogue for half 0   (thread t <-> query row t)
+//   CTA = 256 query rows of one (batch, head), as two 128-row halves; key tiles of 128. 512 threads:
+//   warps 0-3   softmax of half 0 (thread t <-> query row t): row max, exponentials, P, row sum
 //   warps 4-7   the same for half 1
-//   warp  8     MMA issue (one thread): S_h = Q_h K_j^T, O_h += P_h V_j      (tcgen05, TMEM)
-//   warp  9     TMA producer (one thread): Q halves once, K_j / V_j through a ring
+//   warps 8-11  correction for both halves: exact rescale of O_h whenever a row's max moved, and the
+//               epilogue (O / l -> 16 bits -> global, statistics); runs beside the exponentials
+//   warp  12    MMA issue (one lane): S_h = Q_h K_j^T, O_h += P_h V_j      (tcgen05, TMEM)
+//   warp  13    TMA producer (one lane): Q halves once, K_j / V_j through a ring
+//   Register budgets per role (setmaxnreg): the softmax warpgroups take what the others give up.
 //
 //   TMEM columns: S0 [0,128)  S1 [128,256)  O0 [256,256+D)  O1 [256+D,256+2D).
 //   A key tile's 128 score columns are produced and consumed as two parts of 64 keys: S_h part p sits in
@@ -71,7 +74,12 @@ struct FwdParams {
 // Longest list of visited tiles a CTA keeps in shared memory (masks with more tiles per row visit all).
 constexpr int TILE_LIST_CAP = 1024;
 
-constexpr int FWD_THREADS = 320;
+constexpr int FWD_THREADS = 512;
+// Registers per thread once the roles have set their budgets (the kernel starts with 128 each):
+// 2 softmax warpgroups, the correction warpgroup, the MMA + TMA warpgroup: 2 x 128 x 152 + 128 x 96 + 128 x 88 = 62464.
+constexpr int FWD_REGS_SOFTMAX = 152, FWD_REGS_CORRECTION = 96, FWD_REGS_ISSUE = 88;
+constexpr int FWD_BAR_BYTES = 512;        // mbarriers + the tensor-memory address
+constexpr int FWD_HANDOVER_BYTES = 4096;  // alpha [half][part][128] and final (m, l) [half][2][128], fp32
 constexpr int TILE_BYTES_64 = 128 * 64 * 2;  // one 128-row x 64-column 16-bit box = 16 KB
 
 template <int D>
@@ -84,7 +92,7 @@ struct FwdCfg {
   static constexpr int STAGES = (D == 128) ? 4 : 6;
 #endif
   static constexpr int SMEM_TILES = 2 * TILE_BYTES + STAGES * TILE_BYTES;
-  static constexpr int SMEM_BYTES = SMEM_TILES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int SMEM_BYTES = SMEM_TILES + 1024 /*alignment slack*/ + FWD_BAR_BYTES + FWD_HANDOVER_BYTES;
   static constexpr int SMEM_BYTES_LIST = SMEM_BYTES + 2 * TILE_LIST_CAP;  // + the list of visited key tiles
   static constexpr uint32_t TMEM_COLS = 512;
   static constexpr uint32_t TM_S0 = 0, TM_S1 = 128, TM_O0 = 256, TM_O1 = 256 + D;
@@ -116,14 +124,20 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   constexpr int B_KVREADY = 2;            // NS
   constexpr int B_KVFREE = 2 + NS;        // NS
   constexpr int B_SREADY = 2 + 2 * NS;    // 4: [half][part] the 64 score columns of that part are in TMEM
-  constexpr int B_PREADY = 6 + 2 * NS;    // 4: [half][part] the 64 keys of P_h of that part stored, O_h rescaled
+  constexpr int B_PREADY = 6 + 2 * NS;    // 4: [half][part] the 64 keys of P_h of that part are stored (128 arrivals)
   constexpr int B_OFINAL = 10 + 2 * NS;   // 2
   constexpr int B_DRAIN = 12 + 2 * NS;    // 1
   constexpr int B_PVDONE = 13 + 2 * NS;   // 4: [half][part] that part of O_h += P V has retired
-  constexpr int N_BARS = 17 + 2 * NS;
-  static_assert(N_BARS * 8 + 16 <= 256, "barrier block too small");
+  constexpr int B_ALPHA = 17 + 2 * NS;    // 4: [half][part] the rows' rescale factors are in shared memory (128 arrivals)
+  constexpr int B_OREADY = 21 + 2 * NS;   // 4: [half][part] O_h is rescaled for that part (128 arrivals)
+  constexpr int B_LFINAL = 25 + 2 * NS;   // 2: [half] the rows' final m and l are in shared memory (128 arrivals)
+  constexpr int N_BARS = 27 + 2 * NS;
+  static_assert(N_BARS * 8 + 16 <= FWD_BAR_BYTES, "barrier block too small");
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + N_BARS);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+  // hand-over between the softmax and the correction warpgroups: alpha [half][part][row], then (m, l) [half][2][row]
+  float* s_alpha = reinterpret_cast<float*>(smem + Cfg::SMEM_TILES + FWD_BAR_BYTES);
+  float* s_final = s_alpha + 4 * 128;
   const uint32_t bar0 = smem_u32(bars);
   auto bar = [&](int i) { return bar0 + 8u * i; };
 
@@ -163,7 +177,7 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   }
   int n_max = max(n_tiles[0], n_tiles[1]);
   // boolean masks with a tile table: the key tiles this CTA visits, in shared memory
-  uint16_t* s_list = reinterpret_cast<uint16_t*>(smem + Cfg::SMEM_TILES + 256);
+  uint16_t* s_list = reinterpret_cast<uint16_t*>(smem + Cfg::SMEM_TILES + FWD_BAR_BYTES + FWD_HANDOVER_BYTES);
   const bool use_list = MASKW && p.mt != nullptr;
 
   // ---- setup ----
@@ -177,9 +191,14 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     for (int i = 0; i < 4; ++i) {
       mbar_init(bar(B_SREADY + i), 1);
       mbar_init(bar(B_PREADY + i), 128);
+      mbar_init(bar(B_PVDONE + i), 1);
+      mbar_init(bar(B_ALPHA + i), 128);
+      mbar_init(bar(B_OREADY + i), 128);
     }
-    for (int i = 0; i < 2; ++i) mbar_init(bar(B_OFINAL + i), 1);
-    for (int i = 0; i < 4; ++i) mbar_init(bar(B_PVDONE + i), 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(B_OFINAL + i), 1);
+      mbar_init(bar(B_LFINAL + i), 128);
+    }
     mbar_init(bar(B_DRAIN), 1);
     // An earlier failure (status word already set): allocate, skip the work, free.
     *s_abort = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
@@ -219,21 +238,17 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     n_tiles[1] = n_tiles[1] > 0 ? n_max : 0;
   }
   auto tile_of = [&](int it) { return use_list ? static_cast<int>(s_list[it]) : it; };
-#ifdef KFA_PROFILE
-  long long prof_acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
-  long long kfa_prof_tb = 0;
-  (void)kfa_prof_tb;
-  const long long prof_t0 = clock64();
-  const Ctl ctl{s_abort, p.status, prof_acc};
-#else
   const Ctl ctl{s_abort, p.status};
-#endif
   const bool dead = (*s_abort != 0);
 
+  // Each role sets its register budget first (the kernel starts with 128 per thread).
   if (dead) {
     // nothing to do
-  } else if (warp == 9) {
+  } else if (warp >= 14) {
+    reg_budget<FWD_REGS_ISSUE>();
+  } else if (warp == 13) {
     // =========================== TMA producer ===========================
+    reg_budget<FWD_REGS_ISSUE>();
     if (lane == 0) {
       prefetch_tensormap(&tmQ);
       prefetch_tensormap(&tmK);
@@ -263,17 +278,16 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
       if (!ok) {
         // Aborting: let the copies already in flight land before the CTA gives up its smem.
+        for (int hf = 0; hf < 2; ++hf)
+          if (n_tiles[hf] > 0) mbar_drain(bar(B_QREADY + hf), 0);
         for (int i = 0; i < NS; ++i)
-          if (armed[i] >= 0) {
-            const long long t0 = clock64();
-            while (!mbar_try_wait(bar(B_KVREADY + i), armed[i] & 1) && clock64() - t0 < 2000000ll) {
-            }
-          }
+          if (armed[i] >= 0) mbar_drain(bar(B_KVREADY + i), armed[i] & 1);
       }
     }
-  } else if (warp == 8) {
+  } else if (warp == 12) {
     // =========================== MMA issue ===========================
     // The whole warp runs this role converged; one elected lane issues the tcgen05 instructions.
+    reg_budget<FWD_REGS_ISSUE>();
     {
       const bool lead = elect_one();
       constexpr uint32_t IDESC_S = make_idesc(BF16, false, 128, 64);
@@ -320,40 +334,34 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
       if (ok) umma_commit_lead(lead, bar(B_KVFREE + 0));
 
-      // Per key tile and 64-key part, for each half: O_h += P V of the part, then the next tile's
-      // scores of the same part overwrite it. The other part of S_h is untouched meanwhile, so the
-      // softmax of one part runs while the tensor core works on the other.
+      // Per key tile and 64-key part, for each half: O_h += P V of the part (once its P is stored and O_h
+      // carries the part's rescale), then the next tile's scores of the same part overwrite it. The other
+      // part of S_h is untouched meanwhile, so the softmax of one part runs while the tensor core works on
+      // the other.
       for (int j = 0; j < n_max && ok; ++j) {
         const int iv = 2 * j + 1;  // V_j
         const int ik = 2 * j + 2;  // K_{j+1}
         const bool more = (j + 1 < n_max);
-        KFA_PROF_BEGIN();
         ok = kv_wait(iv);
         if (!ok) break;
         if (more) {
           ok = kv_wait(ik);
           if (!ok) break;
         }
-        KFA_PROF_END(5);
         for (int part = 0; part < 2 && ok; ++part) {
           for (int hf = 0; hf < 2 && ok; ++hf) {
             if (j < n_tiles[hf]) {
-              KFA_PROF_BEGIN();
               ok = mbar_wait_warp(bar(B_PREADY + 2 * hf + part), j & 1, ctl, 4);
+              if (ok) ok = mbar_wait_warp(bar(B_OREADY + 2 * hf + part), j & 1, ctl, 8);
               if (!ok) break;
               tc_fence_after();
-              KFA_PROF_END(3);
-              KFA_PROF_BEGIN();
               issue_PV(hf, iv % NS, j > 0, part);
               umma_commit_lead(lead, bar(B_PVDONE + 2 * hf + part));
               if (part == 1 && j == n_tiles[hf] - 1) umma_commit_lead(lead, bar(B_OFINAL + hf));
-              KFA_PROF_END(7);
             }
             if (more && j + 1 < n_tiles[hf]) {
-              KFA_PROF_BEGIN();
               issue_S(hf, ik % NS, part);
               umma_commit_lead(lead, bar(B_SREADY + 2 * hf + part));
-              KFA_PROF_END(6);
             }
           }
         }
@@ -364,20 +372,147 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
       // Everything issued has to retire before TMEM is freed.
       umma_commit_lead(lead, bar(B_DRAIN));
-      {
-        const long long t0 = clock64();
-        while (!mbar_try_wait(bar(B_DRAIN), 0) && clock64() - t0 < KFA_WAIT_CYCLES) {
+      mbar_drain(bar(B_DRAIN), 0);
+    }
+  } else if (warp >= 8) {
+    // =========================== correction: rescale of O, epilogue ===========================
+    // Thread t <-> row t of BOTH halves. For every (half, part) in the order the MMA warp consumes them:
+    // take the rows' factors alpha = exp2((m_old - m_new) c) from the softmax warpgroup, multiply O_h by
+    // them if any row of the warp moved its max (exact; bit-identical to always multiplying), release the
+    // part's P V. This runs while the softmax warpgroup computes the part's exponentials.
+    reg_budget<FWD_REGS_CORRECTION>();
+    const int r_in = tid & 127;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tOh[2] = {tmem + Cfg::TM_O0 + lane_base, tmem + Cfg::TM_O1 + lane_base};
+    bool ok = true;
+    for (int j = 0; j < n_max && ok; ++j) {
+      for (int part = 0; part < 2 && ok; ++part) {
+        for (int hf = 0; hf < 2; ++hf) {
+          if (j >= n_tiles[hf]) continue;
+          ok = mbar_wait_warp(bar(B_ALPHA + 2 * hf + part), j & 1, ctl, 9);
+          if (!ok) break;
+          const float alpha = s_alpha[(2 * hf + part) * 128 + r_in];
+          if ((j > 0 || part > 0) && !__all_sync(0xffffffffu, alpha == 1.0f)) {
+            // every part of O_h += P V issued so far has to have retired (the barrier of the previous part
+            // cannot be two phases ahead: the part after the next needs this release)
+            const int prev = 2 * j + part - 1;
+            ok = mbar_wait_warp(bar(B_PVDONE + 2 * hf + (prev & 1)), (prev >> 1) & 1, ctl, 7);
+            if (!ok) break;
+            tc_fence_after();
+            const float2 a2 = make_float2(alpha, alpha);
+#pragma unroll
+            for (int c0 = 0; c0 < D; c0 += 32) {
+              float2 o[16];
+              tmem_ld32(tOh[hf] + c0, reinterpret_cast<uint32_t*>(o));
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 16; ++i) o[i] = __fmul2_rn(o[i], a2);
+              tmem_st32(tOh[hf] + c0, reinterpret_cast<const uint32_t*>(o));
+            }
+            tmem_wait_st();
+          }
+          tc_fence_before();
+          mbar_arrive(bar(B_OREADY + 2 * hf + part));
+        }
+      }
+    }
+    // ---- epilogue, one half after the other ----
+    for (int hf = 0; hf < 2 && ok; ++hf) {
+      const int nt = n_tiles[hf];
+      if (nt == 0) continue;
+      ok = mbar_wait_warp(bar(B_LFINAL + hf), 0, ctl, 5);
+      if (ok) ok = mbar_wait_warp(bar(B_OFINAL + hf), 0, ctl, 6);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = row0 + 128 * hf + r_in;
+      const uint32_t tO = tOh[hf];
+      float m = s_final[(2 * hf) * 128 + r_in];
+      float l = s_final[(2 * hf + 1) * 128 + r_in];
+      const float c = p.c;
+      if (p.mode != 0) {
+        // Partial result of a context-parallel step: the unnormalised fp32 O with its (m, l) goes to
+        // (mode 1), or is merged into (mode 2), the carry in global memory. Merging keeps the two
+        // statistics apart and shifts both sides to the common row max before anything is rounded.
+        const bool valid = row < Sq;
+        const long long bhl = static_cast<long long>(b) * p.H + h;
+        float* mlp = p.ml + bhl * p.ml_sh + row;
+        float* arow = p.o_acc + bhl * p.oa_sh + static_cast<long long>(row) * D;
+        float a_new = 1.0f, a_old = 0.0f;
+        if (p.mode == 2 && valid) {
+          const float m_old = mlp[0], l_old = mlp[p.ml_plane];
+          const float m_tot = fmaxf(m, m_old);
+          a_new = ex2(__fmul_rn(__fsub_rn(m, m_tot), c));
+          a_old = ex2(__fmul_rn(__fsub_rn(m_old, m_tot), c));
+          l = l * a_new + l_old * a_old;
+          m = m_tot;
+        }
+#pragma unroll
+        for (int cc = 0; cc < D; cc += 32) {
+          float o[32];
+          tmem_ld32(tO + cc, reinterpret_cast<uint32_t*>(o));
+          tmem_wait_ld();
+          if (valid) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              float4 w = make_float4(o[i] * a_new, o[i + 1] * a_new, o[i + 2] * a_new, o[i + 3] * a_new);
+              if (p.mode == 2) {
+                const float4 old = *reinterpret_cast<const float4*>(arow + cc + i);
+                w.x = fmaf(old.x, a_old, w.x);
+                w.y = fmaf(old.y, a_old, w.y);
+                w.z = fmaf(old.z, a_old, w.z);
+                w.w = fmaf(old.w, a_old, w.w);
+              }
+              *reinterpret_cast<float4*>(arow + cc + i) = w;
+            }
+          }
+        }
+        if (valid) {
+          mlp[0] = m;
+          mlp[p.ml_plane] = l;
+        }
+      } else {
+        float inv = 1.0f / l;
+        float log2_l = log2f(l);
+        if (MASKW && l == 0.f) {  // a row with no visible key: output 0, m = +inf, so every P of its backward is 0
+          inv = 0.f;
+          m = INFINITY;
+          log2_l = 0.f;
+        }
+        const bool valid = row < Sq;
+        uint8_t* orow = reinterpret_cast<uint8_t*>(p.o) +
+                        2 * (bc * p.o_sb + h * p.o_sh + static_cast<long long>(q_base + row) * p.o_ss);
+#pragma unroll
+        for (int cc = 0; cc < D; cc += 32) {
+          float o[32];
+          tmem_ld32(tO + cc, reinterpret_cast<uint32_t*>(o));
+          tmem_wait_ld();
+          if (valid) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 w;
+              w.x = pack16<BF16>(o[i] * inv, o[i + 1] * inv);
+              w.y = pack16<BF16>(o[i + 2] * inv, o[i + 3] * inv);
+              w.z = pack16<BF16>(o[i + 4] * inv, o[i + 5] * inv);
+              w.w = pack16<BF16>(o[i + 6] * inv, o[i + 7] * inv);
+              *reinterpret_cast<uint4*>(orow + 2 * (cc + i)) = w;
+            }
+          }
+        }
+        if (valid) {
+          float* lse = p.lse + (static_cast<long long>(bc) * p.H + h) * 2 * p.Sq + q_base;
+          lse[row] = m;
+          lse[p.Sq + row] = log2_l;
         }
       }
     }
   } else {
-    // =========================== softmax / correction / epilogue ===========================
+    // =========================== softmax ===========================
+    reg_budget<FWD_REGS_SOFTMAX>();
     const int hf = warp >> 2;
     const int r_in = tid & 127;
     const int row = row0 + 128 * hf + r_in;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tS = tmem + (hf ? Cfg::TM_S1 : Cfg::TM_S0) + lane_base;
-    const uint32_t tO = tmem + (hf ? Cfg::TM_O1 : Cfg::TM_O0) + lane_base;
     const int nt = n_tiles[hf];
     const int nu = n_unmasked[hf];
     const int my_limit = key_limit(min(row, Sq - 1), p.P, Skv);
@@ -406,15 +541,12 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       // tensor core refills one part while this thread works on the other.
 #pragma unroll
       for (int part = 0; part < 2; ++part) {
-        KFA_PROF_BEGIN();
         ok = mbar_wait_warp(bar(B_SREADY + 2 * hf + part), j & 1, ctl, 5);
         if (!ok) break;
         tc_fence_after();
-        KFA_PROF_END(6);
         const uint32_t tSp = tS + 64 * part;
         const int lim = my_limit - j * 128 - 64 * part;
         float s[64];
-        KFA_PROF_BEGIN();
         tmem_ld32(tSp, reinterpret_cast<uint32_t*>(s));
         tmem_ld32(tSp + 32, reinterpret_cast<uint32_t*>(s + 32));
         tmem_wait_ld();
@@ -443,9 +575,10 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         // Shift first, then scale: the largest exponent of the row is exactly 0.
         const float alpha = ex2(__fmul_rn(__fsub_rn(m, m_shift), c));
         m = m_new;
-        KFA_PROF_END(7);
+        // hand the factor to the correction warpgroup: it rescales O_h while the exponentials below run
+        s_alpha[(2 * hf + part) * 128 + r_in] = alpha;
+        mbar_arrive(bar(B_ALPHA + 2 * hf + part));
         // ---- the exponentials ----
-        KFA_PROF_BEGIN();
         const float2 neg_m = make_float2(-m_shift, -m_shift);
         const float2 c2 = make_float2(c, c);
         float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
@@ -463,128 +596,36 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           pk[i + 1] = pack16<BF16>(p1.x, p1.y);
         }
         tmem_st32(tSp, pk);  // P of this part over its own score columns, already in registers
-        KFA_PROF_END(8);
-        // ---- exact rescale of O whenever any row of this warp moved its max; every part of
-        //      O_h += P V issued so far has to have retired first (they had the exponent loop's
-        //      time to do so: the wait is normally over at once) ----
-        KFA_PROF_BEGIN();
-        // (Only a warp that rescales waits: the barrier of the previous part cannot run two phases
-        //  ahead of this thread, since the part after the next needs this thread's P.)
-        if ((j > 0 || part > 0) && !__all_sync(0xffffffffu, alpha == 1.0f)) {
-          const int prev = 2 * j + part - 1;  // the part issued before this one
-          ok = mbar_wait_warp(bar(B_PVDONE + 2 * hf + (prev & 1)), (prev >> 1) & 1, ctl, 7);
-          if (!ok) break;
-          tc_fence_after();
-          {
-            const float2 a2 = make_float2(alpha, alpha);
-#pragma unroll
-            for (int c0 = 0; c0 < D; c0 += 32) {  // (32 columns at a time: the scores stay in registers)
-              float2 o[16];
-              tmem_ld32(tO + c0, reinterpret_cast<uint32_t*>(o));
-              tmem_wait_ld();
-#pragma unroll
-              for (int i = 0; i < 16; ++i) o[i] = __fmul2_rn(o[i], a2);
-              tmem_st32(tO + c0, reinterpret_cast<const uint32_t*>(o));
-            }
-          }
-        }
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(bar(B_PREADY + 2 * hf + part));
         l = l * alpha + ((la.x + la.y) + (lb.x + lb.y));
-        KFA_PROF_END(9);
       }
       if (!ok) break;
     }
-    // ---- epilogue ----
-    if (nt > 0) ok = mbar_wait_warp(bar(B_OFINAL + hf), 0, ctl, 6) && ok;
-    if (ok && nt > 0 && p.mode != 0) {
-      // Partial result of a context-parallel step: the unnormalised fp32 O with its (m, l) goes to
-      // (mode 1), or is merged into (mode 2), the carry in global memory. Merging keeps the two
-      // statistics apart and shifts both sides to the common row max before anything is rounded.
-      tc_fence_after();
-      const bool valid = row < Sq;
-      const long long bhl = static_cast<long long>(b) * p.H + h;
-      float* mlp = p.ml + bhl * p.ml_sh + row;
-      float* arow = p.o_acc + bhl * p.oa_sh + static_cast<long long>(row) * D;
-      float a_new = 1.0f, a_old = 0.0f;
-      if (p.mode == 2 && valid) {
-        const float m_old = mlp[0], l_old = mlp[p.ml_plane];
-        const float m_tot = fmaxf(m, m_old);
-        a_new = ex2(__fmul_rn(__fsub_rn(m, m_tot), c));
-        a_old = ex2(__fmul_rn(__fsub_rn(m_old, m_tot), c));
-        l = l * a_new + l_old * a_old;
-        m = m_tot;
-      }
-#pragma unroll
-      for (int cc = 0; cc < D; cc += 32) {
-        float o[32];
-        tmem_ld32(tO + cc, reinterpret_cast<uint32_t*>(o));
-        tmem_wait_ld();
-        if (valid) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            float4 w = make_float4(o[i] * a_new, o[i + 1] * a_new, o[i + 2] * a_new, o[i + 3] * a_new);
-            if (p.mode == 2) {
-              const float4 old = *reinterpret_cast<const float4*>(arow + cc + i);
-              w.x = fmaf(old.x, a_old, w.x);
-              w.y = fmaf(old.y, a_old, w.y);
-              w.z = fmaf(old.z, a_old, w.z);
-              w.w = fmaf(old.w, a_old, w.w);
-            }
-            *reinterpret_cast<float4*>(arow + cc + i) = w;
-          }
-        }
-      }
-      if (valid) {
-        mlp[0] = m;
-        mlp[p.ml_plane] = l;
-      }
-    } else if (ok && nt > 0) {
-      tc_fence_after();
-      float inv = 1.0f / l;
-      float log2_l = log2f(l);
-      if (MASKW && l == 0.f) {  // a row with no visible key: output 0, m = +inf, so every P of its backward is 0
-        inv = 0.f;
-        m = INFINITY;
-        log2_l = 0.f;
-      }
-      const bool valid = row < Sq;
-      uint8_t* orow = reinterpret_cast<uint8_t*>(p.o) +
-                      2 * (bc * p.o_sb + h * p.o_sh + static_cast<long long>(q_base + row) * p.o_ss);
-#pragma unroll
-      for (int cc = 0; cc < D; cc += 32) {
-        float o[32];
-        tmem_ld32(tO + cc, reinterpret_cast<uint32_t*>(o));
-        tmem_wait_ld();
-        if (valid) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 w;
-            w.x = pack16<BF16>(o[i] * inv, o[i + 1] * inv);
-            w.y = pack16<BF16>(o[i + 2] * inv, o[i + 3] * inv);
-            w.z = pack16<BF16>(o[i + 4] * inv, o[i + 5] * inv);
-            w.w = pack16<BF16>(o[i + 6] * inv, o[i + 7] * inv);
-            *reinterpret_cast<uint4*>(orow + 2 * (cc + i)) = w;
-          }
-        }
-      }
-      if (valid) {
-        float* lse = p.lse + (static_cast<long long>(bc) * p.H + h) * 2 * p.Sq + q_base;
-        lse[row] = m;
-        lse[p.Sq + row] = log2_l;
-      }
+    if (ok && nt > 0) {  // the rows' final statistics, for the epilogue
+      s_final[(2 * hf) * 128 + r_in] = m;
+      s_final[(2 * hf + 1) * 128 + r_in] = l;
+      mbar_arrive(bar(B_LFINAL + hf));
     }
   }
 
   // ---- teardown (every thread gets here, also after an abort) ----
-#ifdef KFA_PROFILE
-  prof_acc[0] = clock64() - prof_t0;
-  if (lane == 0 && (warp == 0 || warp == 4 || warp == 8 || warp == 9))
-    kfa_prof_flush(prof_acc, warp == 0 ? 0 : (warp == 4 ? 1 : (warp == 8 ? 2 : 3)));
-#endif
   tc_fence_before();
   __syncthreads();
+  if (*s_abort) {  // gave up (or an earlier kernel did): the rows of this CTA read as NaN
+    const int r1 = min(row0 + 256, Sq);
+    const long long bhl = static_cast<long long>(b) * p.H + h;
+    if (p.mode == 0) {
+      fill_rows_nan16(reinterpret_cast<uint8_t*>(p.o) + 2 * (bc * p.o_sb + h * p.o_sh), p.o_ss, q_base + row0, q_base + r1, D);
+      float* lse = p.lse + (static_cast<long long>(bc) * p.H + h) * 2 * p.Sq + q_base;
+      fill_nan32(lse + row0, r1 - row0);
+      fill_nan32(lse + p.Sq + row0, r1 - row0);
+    } else {
+      fill_nan32(p.ml + bhl * p.ml_sh + row0, r1 - row0);
+      fill_nan32(p.ml + bhl * p.ml_sh + p.ml_plane + row0, r1 - row0);
+    }
+  }
   if (warp == 0) {
     tc_fence_after();
     tmem_dealloc(tmem, Cfg::TMEM_COLS);

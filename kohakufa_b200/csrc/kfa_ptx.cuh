@@ -19,12 +19,22 @@ namespace kfa {
 // Status codes written to the device status word (first failure wins).
 enum : int {
   KFA_DEV_OK = 0,
-  KFA_DEV_TIMEOUT_BASE = 100,  // 100 + id of the wait site that gave up: 1-9 forward, 11-19 dK/dV, 21-29 dQ kernel
+  // 100 + id of the wait that gave up; every wait in the library has an id of its own:
+  // 1-9 forward, 11-21 dK/dV kernel, 30-50 fused backward, 51-62 dQ kernel, 91-99 self-test and diagnostics
+  KFA_DEV_TIMEOUT_BASE = 100,
+  KFA_DEV_BAD_SMEM_BASE = 99,  // the dynamic shared memory of a kernel that needs it did not start on a 1 KB boundary
 };
 
+// Longest time a wait may take, in SM clock cycles: ~2 s at 1.9 GHz. Legitimate waits last
+// microseconds; the margin is for a CTA that is preempted or time-sliced (the cycle counter keeps
+// running) or replayed under a profiler.
 #ifndef KFA_WAIT_CYCLES
-#define KFA_WAIT_CYCLES 400000000ll  // ~0.2 s at 1.9 GHz: far beyond any legitimate wait
+#define KFA_WAIT_CYCLES 4000000000ll
 #endif
+// The limit of the waits of the teardown itself (a CTA that gives up still lets the MMAs it has issued
+// retire and the copies it has started land before it frees its tensor memory and shared memory):
+// never shortened, also not in the test build that sets a tiny KFA_WAIT_CYCLES.
+#define KFA_DRAIN_CYCLES 4000000000ll
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -55,15 +65,29 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
+// A limit this short only occurs in the test build whose waits are meant to run out: it then polls
+// without letting the hardware suspend the thread, and looks at the clock on every turn.
+constexpr bool KFA_SHORT_WAITS = (KFA_WAIT_CYCLES < 1000000ll);
+
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.b32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
+  if constexpr (KFA_SHORT_WAITS) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+  }
   return ok != 0;
 }
 
@@ -71,65 +95,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 struct Ctl {
   volatile int* s_abort;
   int* g_status;
-#ifdef KFA_PROFILE
-  long long* acc;  // this thread's cycle counters: [0] role total, [site % 10] cycles spent waiting
-#endif
 };
-
-#ifdef KFA_PROFILE
-// Debug builds only: per-CTA, per-role wait-cycle counters, [cta][4 roles][10] (see kfa_prof_flush).
-__device__ long long* g_kfa_prof = nullptr;
-__device__ __forceinline__ void kfa_prof_flush(const long long* acc, int role) {
-  if (g_kfa_prof == nullptr) return;
-  long long* dst = g_kfa_prof + (static_cast<long long>(blockIdx.x) * 4 + role) * 10;
-#pragma unroll
-  for (int i = 0; i < 10; ++i) dst[i] = acc[i];
-}
-#endif
-
-// Debug-build section timers (compile to nothing otherwise): cycles between BEGIN and END are added
-// to counter `slot` of the calling thread.
-#ifdef KFA_PROFILE
-// A time stamp the compiler cannot move across other volatile statements (clock64() may be).
-__device__ __forceinline__ long long kfa_clock() {
-  long long t;
-  asm volatile("mov.u64 %0, %%clock64;" : "=l"(t)::"memory");
-  return t;
-}
-#define KFA_PROF_BEGIN() kfa_prof_tb = kfa_clock()
-#define KFA_PROF_END(slot) prof_acc[slot] += kfa_clock() - kfa_prof_tb
-#else
-#define KFA_PROF_BEGIN() do { } while (0)
-#define KFA_PROF_END(slot) do { } while (0)
-#endif
 
 // Bounded wait for the phase with the given parity to complete. Returns false when the
 // CTA is aborting (this wait or another ran out of time, or another CTA reported a failure).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const Ctl& ctl, int site) {
-#ifdef KFA_PROFILE
-  {  // try_wait may block inside the hardware for a while: time the first attempt too
-    const long long tp = kfa_clock();
-    const bool hit = mbar_try_wait(bar, parity);
-    ctl.acc[site % 10] += kfa_clock() - tp;
-    if (hit) return true;
-  }
-#else
   if (mbar_try_wait(bar, parity)) return true;
-#endif
-#ifdef KFA_PROFILE
-  const long long t0 = kfa_clock();
-#else
   const long long t0 = clock64();
-#endif
   uint32_t spins = 0;
   for (;;) {
-    if (mbar_try_wait(bar, parity)) {
-#ifdef KFA_PROFILE
-      ctl.acc[site % 10] += kfa_clock() - t0;
-#endif
-      return true;
-    }
-    if ((++spins & 31u) == 0u) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (KFA_SHORT_WAITS || (++spins & 31u) == 0u) {
       if (*ctl.s_abort) return false;
       if ((spins & 1023u) == 0u && *reinterpret_cast<volatile int*>(ctl.g_status) != 0) {
         *ctl.s_abort = 1;
@@ -144,18 +120,20 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const C
   }
 }
 
+// For a thread that gives up while copies it has started may still be in flight: waits (bounded, without
+// touching the abort state) until the phase has completed, so that nothing lands in shared memory after
+// the CTA has released it.
+__device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity) {
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity) && clock64() - t0 < KFA_DRAIN_CYCLES) {
+  }
+}
+
 // The same for a full warp about to run warp-aligned tcgen05 instructions: the warp reconverges
 // and every lane gets the same answer (false if any lane gave up).
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, const Ctl& ctl, int site) {
   const bool ok = mbar_wait(bar, parity, ctl, site);
-#ifdef KFA_PROFILE
-  const long long tp = kfa_clock();
-  const bool all = __all_sync(0xffffffffu, ok);
-  ctl.acc[2] += kfa_clock() - tp;  // (slot 2 doubles as "time to reconverge" in debug builds)
-  return all;
-#else
   return __all_sync(0xffffffffu, ok);
-#endif
 }
 
 // ----------------------------------------------------------------------------------
@@ -409,6 +387,34 @@ __device__ __forceinline__ void tmem_st_16x128b_x4(uint32_t taddr, const uint32_
       "tcgen05.st.sync.aligned.16x128b.x4.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
       ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
       : "memory");
+}
+
+// Sets the calling warpgroup's registers per thread (all four warps must call it). The kernel starts
+// with 128 per thread: a budget above that waits until other warpgroups have released enough.
+template <int N>
+__device__ __forceinline__ void reg_budget() {
+  static_assert(N % 8 == 0 && N >= 24 && N <= 256, "register budget");
+  if constexpr (N > 128) {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+  } else if constexpr (N < 128) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+  }
+}
+
+// ----------------------------------------------------------------------------------
+// What a CTA that gives up leaves behind: NaN in every output row it owns, so that a timed-out wait
+// cannot pass for a result (0x7fff is a NaN in fp16 and in bf16). Called by all threads of the CTA.
+// ----------------------------------------------------------------------------------
+__device__ __forceinline__ void fill_rows_nan16(void* base, long long row_stride, int r0, int r1, int dim) {
+  const int chunks = dim / 8;
+  const uint4 nan8 = make_uint4(0x7fff7fffu, 0x7fff7fffu, 0x7fff7fffu, 0x7fff7fffu);
+  for (int i = threadIdx.x; i < (r1 - r0) * chunks; i += blockDim.x) {
+    const long long r = r0 + i / chunks;
+    *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(base) + 2 * (r * row_stride + (i % chunks) * 8)) = nan8;
+  }
+}
+__device__ __forceinline__ void fill_nan32(float* base, long long count) {
+  for (long long i = threadIdx.x; i < count; i += blockDim.x) base[i] = __int_as_float(0x7fc00000);
 }
 
 // ----------------------------------------------------------------------------------

@@ -65,6 +65,8 @@ kfa_scores_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         umma_ss(tmem, make_sdesc(sQ + off, 16, 1024), make_sdesc(sK + off, 16, 1024), IDESC, kk > 0);
       }
       umma_commit(bar0 + 8);
+    } else {
+      mbar_drain(bar0, 0);  // gave up: the copies still have to land before the CTA leaves
     }
   }
   if (ok) ok = mbar_wait_warp(bar0 + 8, 0, ctl, 95);

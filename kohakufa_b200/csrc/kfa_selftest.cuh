@@ -56,6 +56,8 @@ kfa_selftest_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         umma_ss(tmem, make_sdesc(sA + off, 16, 1024), make_sdesc(sB + off, 16, 1024), IDESC, kk > 0);
       }
       umma_commit(bar0 + 8);
+    } else {
+      mbar_drain(bar0, 0);  // gave up: the copies still have to land before the CTA leaves
     }
   }
   ok = mbar_wait_warp(bar0 + 8, 0, ctl, 92);

@@ -15,7 +15,7 @@ import ctypes
 import torch
 
 from kohakufa_b200 import _lib
-from kohakufa_b200.op import _check
+from kohakufa_b200.op import _check, is_deterministic
 
 
 class HostPipeline:
@@ -47,6 +47,8 @@ class HostPipeline:
         stats_floats = self.lib.kfa_bwd_stats_bytes(n, heads, seq_q) // 4
         self.lse = [torch.empty(n, heads, 2, seq_q, dtype=torch.float32, device=self.device) for _ in range(2)]
         self.stats = [torch.empty(stats_floats, dtype=torch.float32, device=self.device) for _ in range(2)]
+        acc_floats = self.lib.kfa_bwd_dq_acc_bytes(n, heads, seq_q, q.shape[3]) // 4
+        self.dq_acc = [torch.empty(acc_floats, dtype=torch.float32, device=self.device) for _ in range(2)]
         self.outputs = [host_like(q), host_like(q), host_like(k), host_like(v)]  # out, dq, dk, dv
         _check(*self.inputs[0][:3])
 
@@ -60,9 +62,14 @@ class HostPipeline:
         with torch.cuda.device(self.device):
             _lib.check(self.lib.kfa_fwd(ref(q), ref(k), ref(v), ref(out), self.lse[buf].data_ptr(), scale, block, dtype,
                                         self.status.data_ptr(), stream))
-            _lib.check(self.lib.kfa_bwd(ref(q), ref(k), ref(v), ref(out), ref(dout), self.lse[buf].data_ptr(),
-                                        self.stats[buf].data_ptr(), ref(dq), ref(dk), ref(dv), scale, block, dtype,
-                                        self.status.data_ptr(), stream))
+            if is_deterministic():
+                _lib.check(self.lib.kfa_bwd(ref(q), ref(k), ref(v), ref(out), ref(dout), self.lse[buf].data_ptr(),
+                                            self.stats[buf].data_ptr(), ref(dq), ref(dk), ref(dv), scale, block, dtype,
+                                            self.status.data_ptr(), stream))
+            else:
+                _lib.check(self.lib.kfa_bwd_fused(ref(q), ref(k), ref(v), ref(out), ref(dout), self.lse[buf].data_ptr(),
+                                                  self.stats[buf].data_ptr(), self.dq_acc[buf].data_ptr(), ref(dq),
+                                                  ref(dk), ref(dv), scale, block, dtype, self.status.data_ptr(), stream))
 
     def run(self, q, k, v, dout, scale, block):
         cur = torch.cuda.current_stream(self.device)

@@ -311,8 +311,10 @@ def varlen_fwd_op(
 ) -> tuple[Tensor, Tensor]:  # fmt: skip
     lib = _lib.load()
     total_q, heads, _ = q.shape
-    out = torch.empty_like(q)
-    lse = q.new_empty(1, heads, 2, total_q, dtype=torch.float32)
+    # zero-filled: rows no CTA writes (a sequence with queries but no keys, rows outside cu_seqlens) read
+    # as "no visible key": output 0, statistics 0
+    out = torch.zeros_like(q)
+    lse = q.new_zeros(1, heads, 2, total_q, dtype=torch.float32)
     with torch.cuda.device(q.device):
         rc = lib.kfa_fwd_varlen(
             *(ctypes.byref(_lib.tensor4(_as4(t))) for t in (q, k, v, out)),
@@ -344,7 +346,7 @@ def varlen_bwd_op(
 ) -> tuple[Tensor, Tensor, Tensor]:  # fmt: skip
     lib = _lib.load()
     n_seqs = cu_seqlens_q.numel() - 1
-    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    dq, dk, dv = torch.zeros_like(q), torch.zeros_like(k), torch.zeros_like(v)  # unwritten rows: zero gradient
     stats = q.new_empty(lib.kfa_bwd_stats_bytes(n_seqs, q.shape[1], max_q) // 4, dtype=torch.float32)
     with torch.cuda.device(q.device):
         rc = lib.kfa_bwd_varlen(

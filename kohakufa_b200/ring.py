@@ -215,9 +215,35 @@ def _shift(tensor_out, tensor_in, group):
     return dist.batch_isend_irecv(ops)
 
 
-def _wait(reqs):
+def _wait(reqs, trace=None, label="wait"):
+    """Makes the compute stream wait for the transfers. With a ``trace`` the stall is bracketed by events:
+    the time between them is what the stream spent idle waiting for NCCL."""
+    _mark(trace, "begin:" + label)
     for r in reqs:
         r.wait()
+    _mark(trace, "end:" + label)
+
+
+def _mark(trace, label):
+    """Appends (label, event recorded now on the current stream) to ``trace`` (a list, or None = off)."""
+    if trace is not None:
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        trace.append((label, ev))
+
+
+def trace_summary(trace):
+    """Milliseconds per label from a ``trace`` filled by ``ring_forward`` / ``ring_backward``: for every
+    ``begin:x`` ... ``end:x`` pair the device time between the two events, summed per ``x`` (the events
+    must have completed: synchronise first)."""
+    total, open_at = {}, {}
+    for label, ev in trace:
+        kind, name = label.split(":", 1)
+        if kind == "begin":
+            open_at[name] = ev
+        else:
+            total[name] = total.get(name, 0.0) + open_at.pop(name).elapsed_time(ev)
+    return total
 
 
 def _pack_kv(k, v):
@@ -232,8 +258,9 @@ def _views(kv):
     return kv[0].transpose(1, 2), kv[1].transpose(1, 2)
 
 
-def ring_forward(q, k, v, scale, group=None):
-    """out, lse of this rank's queries. The K / V of step t+1 travel while step t computes."""
+def ring_forward(q, k, v, scale, group=None, trace=None):
+    """out, lse of this rank's queries. The K / V of step t+1 travel while step t computes.
+    ``trace``: a list that receives timing marks (see ``trace_summary``)."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     _check_local(q, k, v)
     st = _Rank(rank, world, q, scale)
@@ -243,14 +270,16 @@ def ring_forward(q, k, v, scale, group=None):
     for t in range(world):
         reqs = _shift(cur, nxt, group) if t + 1 < world else []
         kc, vc = _views(cur)
+        _mark(trace, "begin:fwd kernels")
         st.fwd_step(t, q, kc, vc)
+        _mark(trace, "end:fwd kernels")
         if reqs:
-            _wait(reqs)
+            _wait(reqs, trace, "fwd wait for K/V")
             cur, nxt = nxt, cur
     return st.fwd_end(q)
 
 
-def ring_backward(q, k, v, out, dout, lse, scale, group=None):
+def ring_backward(q, k, v, out, dout, lse, scale, group=None, trace=None):
     """dq, dk, dv of this rank's rows. Per step: the dQ kernel runs while the fp32 dK / dV accumulator
     of the visiting K / V is still arriving from the previous rank, then the dK / dV kernel adds to it
     and it moves on; after N hops it is back at its owner."""
@@ -265,17 +294,21 @@ def ring_backward(q, k, v, out, dout, lse, scale, group=None):
     for t in range(world):
         kv_reqs = _shift(cur, nxt, group) if t + 1 < world else []
         kc, vc = _views(cur)
+        _mark(trace, "begin:bwd dQ kernel")
         st.bwd_dq_step(t, q, dout, kc, vc)
+        _mark(trace, "end:bwd dQ kernel")
         if acc_reqs:  # the accumulator for this step's K / V, sent by the previous rank after its step t-1
-            _wait(acc_reqs)
+            _wait(acc_reqs, trace, "bwd wait for dK/dV accumulator")
             acc, acc_in = acc_in, acc
+        _mark(trace, "begin:bwd dK/dV kernel")
         st.bwd_dkdv_step(t, q, dout, kc, vc, acc)
+        _mark(trace, "end:bwd dK/dV kernel")
         acc_reqs = _shift(acc, acc_in, group) if world > 1 else []
         if kv_reqs:
-            _wait(kv_reqs)
+            _wait(kv_reqs, trace, "bwd wait for K/V")
             cur, nxt = nxt, cur
     if acc_reqs:  # the last hop brings this rank's own accumulator home
-        _wait(acc_reqs)
+        _wait(acc_reqs, trace, "bwd wait for dK/dV accumulator")
         acc = acc_in
     dq = st.grad_end(st.dq_acc, q)
     dk = st.grad_end(acc[0], k)

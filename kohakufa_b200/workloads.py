@@ -73,19 +73,22 @@ def _bshd(x: torch.Tensor) -> torch.Tensor:
 PIECE_ROWS = 8192  # granularity of make_piecewise_inputs: one seed per 8192 rows of the sequence
 
 
-def make_piecewise_inputs(cfg: Config, row_ranges, device="cpu"):
+def make_piecewise_inputs(cfg: Config, row_ranges, device="cpu", device_rng=False):
     """q, k, v, dout for the given row ranges of ``cfg``'s sequence, generated piece by piece (one seed
     per PIECE_ROWS rows), so that a rank of a context-parallel run builds only its own rows and every
     world size sees the same global tensors. ``row_ranges``: list of (start, stop), multiples of
-    PIECE_ROWS. Returns ``[B, H, rows, D]`` views of ``[B, rows, H, D]`` storage."""
+    PIECE_ROWS. Returns ``[B, H, rows, D]`` views of ``[B, rows, H, D]`` storage.
+    ``device_rng``: draw the numbers with ``device``'s own generator (fast for long sequences; the values
+    then depend on the GPU model, which is fine where the check is computed from the same tensors)."""
     outs = []
+    rng_device = device if device_rng else "cpu"
     for which in range(4):
         parts = []
         for start, stop in row_ranges:
             assert start % PIECE_ROWS == 0 and stop % PIECE_ROWS == 0
             for piece in range(start // PIECE_ROWS, stop // PIECE_ROWS):
-                gen = torch.Generator().manual_seed(1_000_003 * (cfg.seed + 1) + 4 * piece + which)
-                x = torch.randn(cfg.batch, PIECE_ROWS, cfg.heads, cfg.dim, generator=gen) * cfg.std
+                gen = torch.Generator(device=rng_device).manual_seed(1_000_003 * (cfg.seed + 1) + 4 * piece + which)
+                x = torch.randn(cfg.batch, PIECE_ROWS, cfg.heads, cfg.dim, generator=gen, device=rng_device) * cfg.std
                 parts.append(x.to(cfg.dtype))
         outs.append(torch.cat(parts, dim=1).to(device).transpose(1, 2))
     return tuple(outs)

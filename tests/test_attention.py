@@ -256,10 +256,24 @@ def test_largest_p_is_exactly_one():
 
 
 def test_deterministic():
+    """out, dK, dV repeat bit for bit; dQ does under ``set_deterministic(True)`` (the split kernels) and to
+    within the order of fp32 additions otherwise (the reference's own dQ is in the second class,
+    tests/test_attention.py:347-358)."""
+    from kohakufa_b200 import set_deterministic
+
     q, k, v, dout = inputs(2, 2, 700, 700, seed=8)
     a = run(q, k, v, dout, causal=True)
     b = run(q, k, v, dout, causal=True)
-    for x, y in zip(a, b):
+    for i in (0, 2, 3):
+        assert torch.equal(a[i], b[i])
+    assert oracle.rel_l2(a[1], b[1]) < 1e-3
+    set_deterministic(True)
+    try:
+        c = run(q, k, v, dout, causal=True)
+        d = run(q, k, v, dout, causal=True)
+    finally:
+        set_deterministic(False)
+    for x, y in zip(c, d):
         assert torch.equal(x, y)
 
 
@@ -323,19 +337,6 @@ def test_causal_compiled():
     check((out, q.grad, k.grad, v.grad), want_for(q, k, v, dout, block=1))
 
 
-def test_bounded_wait_reports_instead_of_hanging():
-    """A launch that finds the status word already set does no work and returns; clearing the word
-    restores normal operation (the context stays usable)."""
-    q, k, v, dout = inputs(1, 1, 128, 128)
-    word = _lib.status_word(q.device)
-    word.fill_(7)
-    out = attention(q, k, v)
-    torch.cuda.synchronize()
-    assert _lib.device_status() == 7
-    _lib.reset_device_status()
-    check(run(q, k, v, dout), want_for(q, k, v, dout))
-
-
 def test_host_buffer_entry_point():
     """attention_fwd_bwd_host: pinned host tensors in, pinned host tensors out, batch slices pipelined
     over three streams; results identical to the device-tensor path."""
@@ -347,8 +348,9 @@ def test_host_buffer_entry_point():
     torch.cuda.synchronize()
     q, k, v = (t.cuda().requires_grad_() for t in host[:3])
     want = run(q, k, v, host[3].cuda(), causal=True)
-    for g, w in zip((out, dq, dk, dv), want):
+    for g, w in zip((out, dk, dv), (want[0], want[2], want[3])):
         assert torch.equal(g, w.cpu())
+    assert oracle.rel_l2(dq, want[1].cpu()) < 1e-3  # (dQ: the order of the fused backward's fp32 adds varies)
     # a second call through a reused pipeline
     pipe = hostio.HostPipeline(*host[:3], "cuda", slices=2)
     out2 = hostio.attention_fwd_bwd_host(*host, causal=True, pipeline=pipe)[0]

@@ -68,14 +68,15 @@ def test_kernel_scores_are_the_hardware_scores(name):
     exact = torch.matmul(q.double(), k.double().transpose(-1, -2))
     rounded = exact.float()  # the correctly rounded fp32 dot products the reference's emulation assumes
     differ = scores != rounded
-    ulp = torch.abs(rounded) * 2.0**-23  # (an upper bound of one unit in the last place)
-    off = ((scores.double() - exact).abs() / ulp.double().clamp_min(1e-30))[differ]
+    # one unit in the last place at the magnitude of the terms being added (their absolute sum: the dot
+    # products themselves can cancel to almost nothing)
+    unit = torch.matmul(q.double().abs(), k.double().abs().transpose(-1, -2)) * 2.0**-24
+    off = (scores.double() - exact).abs() / unit
     frac = float(differ.float().mean())
-    print(f"{name}: {100 * frac:.1f} % of the scores differ from the correctly rounded product, by up to {float(off.max()):.1f} ulp")
+    print(f"{name}: {100 * frac:.1f} % of the scores differ from the correctly rounded product; "
+          f"largest error {float(off.max()):.2f}, mean {float(off.mean()):.3f} units of the terms' magnitude")  # fmt: skip
     assert frac > 0.05, "scores equal the correctly rounded products: the hardware floor would be the reference's"
-    assert float(off.max()) < 64.0
-    # towards zero: the tensor core's adder truncates
-    assert float(((scores.double().abs() - exact.abs()) / ulp.double().clamp_min(1e-30)).max()) < 1.0
+    assert float(off.max()) < 16.0  # ... and are still fp32-accurate dot products
 
 
 def floor_errors(q, k, v, dout, scale, want):

@@ -1,9 +1,11 @@
 """The fused backward (``kfa_bwd_fused``: dK, dV and dQ from one P and one dS per tile pair, dQ through
 fp32 reduce-adds) against the split, bit-reproducible kernels (``kfa_bwd``) and the fp64 oracle.
 
-dK and dV must be bit-identical to the split kernels' (same operands, same accumulation order); dQ may
-differ in the order of its fp32 additions only: ``rel_err < 1e-3``, the tolerance the reference uses for
-its own run-to-run dQ comparison (KohakuFA tests/test_attention.py:347-358)."""
+Both paths feed the tensor cores the same rounded operands; they differ only in the order of fp32
+additions (dQ: atomic adds in whatever order the CTAs get there; dK, dV: the fused kernel walks the query
+tiles starting at a different tile per key tile). So every gradient must agree with the split kernels' to
+``rel_err < 1e-3``, the tolerance the reference uses for its own run-to-run dQ comparison (KohakuFA
+tests/test_attention.py:347-358), and dK, dV must repeat bit for bit from run to run."""
 
 import ctypes
 
@@ -76,10 +78,9 @@ def test_fused_matches_split_and_oracle(case):
     scale = dim**-0.5
     out, split, fused = backward_both(q, k, v, dout, scale, block)
     assert all(bool(torch.isfinite(g).all()) for g in fused)
-    assert torch.equal(fused[1], split[1]), "dK differs from the split kernel's"
-    assert torch.equal(fused[2], split[2]), "dV differs from the split kernel's"
-    dq_err = oracle.rel_l2(fused[0], split[0]) if float(split[0].abs().max()) > 0 else float(fused[0].abs().max())
-    assert dq_err < 1e-3, f"dQ: {dq_err:.3e} away from the split kernel's"
+    for name, f, s in zip(("dQ", "dK", "dV"), fused, split):
+        err = oracle.rel_l2(f, s) if float(s.abs().max()) > 0 else float(f.abs().max())
+        assert err < 1e-3, f"{name}: {err:.3e} away from the split kernel's"
     want = oracle.attention_fp64(q, k, v, dout, scale, block=block, groups=heads // kv_heads)
     tol = 5e-3 if dtype == torch.float16 else 2e-2
     for name, g, w in zip(("dq", "dk", "dv"), fused, want[1:]):
@@ -111,8 +112,8 @@ def test_autograd_uses_fused_by_default_and_split_on_request():
     finally:
         set_deterministic(False)
     assert _lib.device_status() == 0
-    assert torch.equal(grads[False][1], grads[True][1]) and torch.equal(grads[False][2], grads[True][2])
-    assert oracle.rel_l2(grads[False][0], grads[True][0]) < 1e-3
+    for a, b in zip(grads[False], grads[True]):
+        assert oracle.rel_l2(a, b) < 1e-3
     # the deterministic path repeats bit for bit
     set_deterministic(True)
     try:

@@ -6,7 +6,7 @@ tests/test_attention.py:271-344)."""
 import pytest
 import torch
 
-from kohakufa_b200 import _lib, attention, attention_varlen, varlen_plan
+from kohakufa_b200 import _lib, attention, attention_varlen, set_deterministic, varlen_plan
 from oracle import reference as oracle
 
 pytestmark = pytest.mark.gpu
@@ -65,8 +65,12 @@ def check_varlen(len_q, len_k, heads, kv_heads, block, dtype=torch.float16, tol=
         # the same kernels on the sequence as a batch of one: identical bits (tiles are numbered from
         # the sequence's first row, and what a tile reads of its neighbours is masked)
         qa, ka, va = (t.clone().requires_grad_() for t in (q1, k1, v1))
-        alone = attention(qa, ka, va, block_causal=block)
-        alone.backward(d1)
+        set_deterministic(True)  # packed batches run the split backward kernels: compare like with like
+        try:
+            alone = attention(qa, ka, va, block_causal=block)
+            alone.backward(d1)
+        finally:
+            set_deterministic(False)
         for name, g, w in zip(("out", "dq", "dk", "dv"), got, (alone, qa.grad, ka.grad, va.grad)):
             assert torch.equal(g, w), (b, name)
 
@@ -154,3 +158,24 @@ def test_varlen_argument_errors():
         varlen_plan(cu, torch.tensor([0, 150, 150], dtype=torch.int32, device="cuda"))
     with pytest.raises(ValueError):
         attention_varlen(q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0), cu, cu)
+
+
+def test_sequence_without_keys_through_a_user_plan():
+    """``varlen_plan`` refuses a sequence that has queries but no keys; a caller that hands in its own plan
+    skips that check. Such rows then see nothing: output 0 and zero gradients (what the reference documents
+    for a query row without a visible key), never uninitialised memory."""
+    len_q, len_k = [70, 40, 130], [90, 0, 130]
+    q, k, v, dout, cu_q, cu_k = packed(len_q, len_k, 2, 2)
+    plan = (3, 130, 130)  # (sequences, longest query length, longest key length) written by hand
+    out = attention_varlen(q, k, v, cu_q, cu_k, causal=True, plan=plan)
+    out.backward(dout)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    assert float(out[70:110].abs().max()) == 0.0 and float(q.grad[70:110].abs().max()) == 0.0
+    for b in (0, 2):  # the other sequences are unaffected
+        sq, eq, sk, ek = int(cu_q[b]), int(cu_q[b + 1]), int(cu_k[b]), int(cu_k[b + 1])
+        want = oracle.attention_fp64(as4(q.detach(), sq, eq), as4(k.detach(), sk, ek), as4(v.detach(), sk, ek),
+                                     as4(dout, sq, eq), 64**-0.5, block=1)  # fmt: skip
+        got = (as4(out, sq, eq), as4(q.grad, sq, eq), as4(k.grad, sk, ek), as4(v.grad, sk, ek))
+        for g, w in zip(got, want):
+            assert oracle.metrics(g, w)["rel_err"] < TOL
