@@ -244,7 +244,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=None, help="override the configuration's batch (profiling a small case)")
     ap.add_argument("--heads", type=int, default=None, help="override the configuration's head count")
-    ap.add_argument("--deterministic", action="store_true", help="time the split, bit-reproducible backward kernels")
+    ap.add_argument("--backward", default=None, choices=["auto", "fused", "split"],
+                    help="backward implementation (default: the package's, 'auto' unless KFA_BACKWARD says otherwise)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-ring", action="store_true", help="N > 1: skip the context-parallel C5 record")
@@ -264,10 +265,12 @@ def main():
 
     import torch.distributed as dist
 
-    from kohakufa_b200 import _lib, attention, set_deterministic
-    from kohakufa_b200.op import attention_bwd_op, attention_fwd_op
+    from kohakufa_b200 import _lib, attention, get_backward, set_backward
+    from kohakufa_b200.op import attention_bwd_op, attention_fwd_op, use_fused_backward
 
-    set_deterministic(args.deterministic)
+    if args.backward:
+        set_backward(args.backward)
+    fused = use_fused_backward(cfg.dim, cfg.batch * cfg.heads)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -345,7 +348,7 @@ def main():
         stop.record()
         barrier()
         # per-kernel device times, same workload, still inside the sampled region
-        kernel_ms = time_kernels(cfg, q, k, v, dout, args.steps, args.deterministic)
+        kernel_ms = time_kernels(cfg, q, k, v, dout, args.steps, not fused)
         # a short timed region can end before nvidia-smi's next sample: keep the same load running
         # (untimed) until three samples under load exist, for at most 1.5 s
         t_extra = time.perf_counter()
@@ -412,7 +415,7 @@ def main():
         "data": "synthetic",
         "config": config_dict(cfg, world)
         | {"timing": f"one CUDA graph of {args.steps} steps" if use_graph else "eager launches, CUDA events"}
-        | {"backward": "split kernels (deterministic)" if args.deterministic else "fused kernel"},
+        | {"backward": f"{'fused kernel' if fused else 'split kernels'} (mode {get_backward()})"},
         "pct_of_peak": {
             "of_measured_burst": value / world / peaks["bf16_tflops"],
             "of_measured_sustained": value / world / peaks["bf16_tflops_sustained"],
@@ -435,7 +438,7 @@ def main():
             "clock-normalised = 4096 MAC x 2 x 148 SMs x the median SM clock sampled during the timed region; "
             "traffic = DRAM bytes of one launch from an ncu capture of a 16-head case, scaled by the head count",
         },
-        "gpu_launches": (3 * world + 5 if ring_mode else 4) * args.steps,
+        "gpu_launches": (3 * world + 5 if ring_mode else 4) * args.steps,  # fwd + 3 backward launches either way
         "clocks": clocks,
         "e2e": e2e,
     }

@@ -51,26 +51,15 @@ struct FusedCfg {
   // Q_i is read first by S^T(i) and last by dK(i), a whole step later, and S^T(i+1) is issued before
   // dK(i): three slots let the copy of Q_(i+2) start a step ahead. dO_i is done after dV(i), long
   // before dP^T(i+1) can be issued: one slot is enough at D = 128 (where no more fit), two at D = 64.
-#ifndef KFA_EXP_NQ128
-#define KFA_EXP_NQ128 3
-#endif
-#ifndef KFA_EXP_NDO128
-#define KFA_EXP_NDO128 1
-#endif
-#ifndef KFA_EXP_DOBUFS128
-#define KFA_EXP_DOBUFS128 KFA_EXP_NDO128
-#endif
-  static constexpr int NQ = (D == 128) ? KFA_EXP_NQ128 : 3;
-  static constexpr int NDO = (D == 128) ? KFA_EXP_NDO128 : 2;
-  static constexpr int DO_BUFS = (D == 128) ? KFA_EXP_DOBUFS128 : 2;
+  static constexpr int NQ = 3;
+  static constexpr int NDO = (D == 128) ? 1 : 2;
   static constexpr int DS_BYTES = 2 * TILE_BYTES_64;  // dS^T: two [128 keys][64 queries] boxes
-  // dQ staging for the bulk reduce-adds: two buffers of 128 rows x 32 columns fp32
-#ifdef KFA_DQ_VIA_TMA
-  static constexpr int STAGE_BYTES = 2 * 128 * 32 * 4;
-#else
-  static constexpr int STAGE_BYTES = 0;
-#endif
-  static constexpr int SMEM_TILES = (2 + NQ + DO_BUFS) * TILE_BYTES + DS_BYTES + STAGE_BYTES;
+  // How a finished dQ tile reaches the accumulator. D = 64: through two shared-memory staging buffers (128
+  // rows x 32 columns fp32 each) and bulk reduce-adds by the copy engine. D = 128: no shared memory is left
+  // for staging, the warpgroup issues the reduce-adds from registers (measured at D = 64: 10 % slower).
+  static constexpr bool DQ_VIA_COPY_ENGINE = (D == 64);
+  static constexpr int STAGE_BYTES = DQ_VIA_COPY_ENGINE ? 2 * 128 * 32 * 4 : 0;
+  static constexpr int SMEM_TILES = (2 + NQ + NDO) * TILE_BYTES + DS_BYTES + STAGE_BYTES;
   // per-query statistics of a step: (-m, -log2 l) double-buffered (read by the P phase), -delta single
   // (read by the dS phase, reloaded while the next P phase runs)
   static constexpr int ML_BYTES = 2 * 128 * 4, DELTA_BYTES = 128 * 4;
@@ -168,7 +157,7 @@ kfa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const uint32_t sV = smem_base + TB;
   const uint32_t sQ = smem_base + 2 * TB;           // ring of NQ
   const uint32_t sDO = sQ + NQ * TB;                // ring of NDO
-  const uint32_t sDS = sDO + Cfg::DO_BUFS * TB;     // dS^T
+  const uint32_t sDS = sDO + NDO * TB;              // dS^T
   const uint32_t sStage = sDS + Cfg::DS_BYTES;       // dQ staging (if any)
   const uint32_t sML = smem_base + Cfg::SMEM_TILES;  // 2 x (-m[128], -log2 l[128])
   const uint32_t sDL = sML + 2 * Cfg::ML_BYTES;      // -delta[128]
@@ -337,7 +326,7 @@ kfa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         if (!ok) break;
         mbar_expect_tx(bar(B_DOREADY + slot), TB);
         for (int ch = 0; ch < CH; ++ch)
-          tma_load_4d(sDO + (slot % Cfg::DO_BUFS) * TB + ch * TILE_BYTES_64, &tmDO, bar(B_DOREADY + slot), ch * 64, tile_of(s) * 128,
+          tma_load_4d(sDO + slot * TB + ch * TILE_BYTES_64, &tmDO, bar(B_DOREADY + slot), ch * 64, tile_of(s) * 128,
                       head_of(s), b);
         issued = s + 1;
       }
@@ -372,7 +361,7 @@ kfa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       }
       for (int s = 0; s < n_steps && ok; ++s) {
         const uint32_t q_s = sQ + (s % NQ) * TB;
-        const uint32_t do_s = sDO + ((s % NDO) % Cfg::DO_BUFS) * TB;
+        const uint32_t do_s = sDO + (s % NDO) * TB;
         const bool more = s + 1 < n_steps;
         // dV += P^T(s) dO_s in two parts (the first 32 queries of each warpgroup's P^T are signalled
         // early), then S^T(s+1) may overwrite the P^T columns
@@ -411,7 +400,7 @@ kfa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           if (ok && Cfg::DQ_ALIASES_DP) ok = mbar_wait_warp(bar(B_DQFREE), s & 1, ctl, 42);
           if (!ok) break;
           tc_fence_after();
-          issue_kmajor_n128<D>(lead, tDP, v_lo, sdesc_lo(sDO + (((s + 1) % NDO) % Cfg::DO_BUFS) * TB, 16), IDESC_S);
+          issue_kmajor_n128<D>(lead, tDP, v_lo, sdesc_lo(sDO + ((s + 1) % NDO) * TB, 16), IDESC_S);
           umma_commit_lead(lead, bar(B_DP));
         }
       }
@@ -433,72 +422,60 @@ kfa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       tc_fence_after();
       // the whole tile goes to registers first, so that its columns are free at once (dP^T of the next step
       // is waiting for them at D = 128); the adds then drain at the rate the memory system takes them
-      float* dst = dq_acc + (static_cast<long long>(b) * p.H + head) * dq_acc_head_floats(Sq, D) +
-                   static_cast<long long>(i) * (128 * D) + r_in * 4;
-      const bool valid = i * 128 + r_in < Sq;  // (padded query rows hold exact zeros)
       float v[D];
 #pragma unroll
       for (int c = 0; c < D; c += 32) tmem_ld32(tDQ + c, reinterpret_cast<uint32_t*>(v + c));
       tmem_wait_ld();
       tc_fence_before();
       mbar_arrive(bar(B_DQFREE));
-#ifdef KFA_DQ_VIA_TMA
-      // Through shared memory to the copy engine: 32 columns (16 KB) at a time into one of two staging
-      // buffers laid out like the accumulator ([4-column group][row][4]), each then added to global memory
-      // by one bulk reduce. The thread that issues the copies (the warpgroup's first) also owns their
-      // completion groups: before a buffer is rewritten, the reduce two commits back has read it.
-      (void)valid;
-      (void)dst;
-      float* tile = dq_acc + (static_cast<long long>(b) * p.H + head) * dq_acc_head_floats(Sq, D) +
-                    static_cast<long long>(i) * (128 * D);
+      if constexpr (Cfg::DQ_VIA_COPY_ENGINE) {
+        // Through shared memory to the copy engine: 32 columns (16 KB) at a time into one of two staging
+        // buffers laid out like the accumulator ([4-column group][row][4]), each then added to global
+        // memory by one bulk reduce. The thread that issues the copies (the warpgroup's first) also owns
+        // their completion groups: before a buffer is rewritten, the reduce two commits back has read it.
+        // The hand-shakes inside the warpgroup are bounded mbarrier waits, like every other wait here.
+        float* tile = dq_acc + (static_cast<long long>(b) * p.H + head) * dq_acc_head_floats(Sq, D) +
+                      static_cast<long long>(i) * (128 * D);
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        const uint32_t buf = sStage + (c & 1) * 16384;
-        const uint32_t n = static_cast<uint32_t>(s) * (D / 32) + c;  // running count of staged pieces
-        if (tid == 256) {
-          asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-          mbar_arrive(bar(B_STGFREE));
-        }
-        ok = mbar_wait_warp(bar(B_STGFREE), n & 1, ctl, 29);
-        if (!ok) break;
+        for (int c = 0; c < D / 32; ++c) {
+          const uint32_t buf = sStage + (c & 1) * 16384;
+          const uint32_t n = static_cast<uint32_t>(s) * (D / 32) + c;  // running count of staged pieces
+          if (tid == 256) {
+            asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            mbar_arrive(bar(B_STGFREE));
+          }
+          ok = mbar_wait_warp(bar(B_STGFREE), n & 1, ctl, 29);
+          if (!ok) break;
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          const uint32_t addr = buf + (g * 128 + r_in) * 16;
-          asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v[32 * c + 4 * g]),
-                       "f"(v[32 * c + 4 * g + 1]), "f"(v[32 * c + 4 * g + 2]), "f"(v[32 * c + 4 * g + 3])
-                       : "memory");
-        }
-        fence_async_smem();
-        mbar_arrive(bar(B_STGFULL));
-        if (tid == 256) {
-          if (mbar_wait(bar(B_STGFULL), n & 1, ctl, 28)) {
+          for (int g = 0; g < 8; ++g) {
+            const uint32_t addr = buf + (g * 128 + r_in) * 16;
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v[32 * c + 4 * g]),
+                         "f"(v[32 * c + 4 * g + 1]), "f"(v[32 * c + 4 * g + 2]), "f"(v[32 * c + 4 * g + 3])
+                         : "memory");
+          }
+          fence_async_smem();
+          mbar_arrive(bar(B_STGFULL));
+          if (tid == 256 && mbar_wait(bar(B_STGFULL), n & 1, ctl, 28)) {
             asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(tile + c * 4096),
                          "r"(buf), "r"(16384)
                          : "memory");
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           }
         }
-      }
-      if (!ok) break;
-#else
-#ifdef KFA_EXP_NO_RED
-      if (valid && p.scale == 12345.f) {
-#else
-      if (valid) {
-#endif
+        if (!ok) break;
+      } else {
+        // Straight from registers; padded query rows hold exact zeros and are left out.
+        float* dst = dq_acc + (static_cast<long long>(b) * p.H + head) * dq_acc_head_floats(Sq, D) +
+                     static_cast<long long>(i) * (128 * D) + r_in * 4;
+        if (i * 128 + r_in < Sq) {
 #pragma unroll
-        for (int c4 = 0; c4 < D / 4; ++c4) {
-          red_add_v4(dst + c4 * 512, v[4 * c4], v[4 * c4 + 1], v[4 * c4 + 2], v[4 * c4 + 3]);
-#ifdef KFA_RED_PACE_NS
-          if ((c4 & 3) == 3) __nanosleep(KFA_RED_PACE_NS);
-#endif
+          for (int c4 = 0; c4 < D / 4; ++c4)
+            red_add_v4(dst + c4 * 512, v[4 * c4], v[4 * c4 + 1], v[4 * c4 + 2], v[4 * c4 + 3]);
         }
       }
-#endif
     }
-#ifdef KFA_DQ_VIA_TMA
-    if (tid == 256) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // shared memory stays valid until read
-#endif
+    if (Cfg::DQ_VIA_COPY_ENGINE && tid == 256)
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // the staging buffers stay valid until read
   } else if (warp < 8) {
     // =========================== P^T / dS^T and the dV / dK epilogue ===========================
     reg_budget<FUSED_REGS_COMPUTE>();

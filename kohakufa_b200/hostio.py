@@ -15,7 +15,7 @@ import ctypes
 import torch
 
 from kohakufa_b200 import _lib
-from kohakufa_b200.op import _check, is_deterministic
+from kohakufa_b200.op import _check, use_fused_backward
 
 
 class HostPipeline:
@@ -62,7 +62,7 @@ class HostPipeline:
         with torch.cuda.device(self.device):
             _lib.check(self.lib.kfa_fwd(ref(q), ref(k), ref(v), ref(out), self.lse[buf].data_ptr(), scale, block, dtype,
                                         self.status.data_ptr(), stream))
-            if is_deterministic():
+            if not use_fused_backward(self.inputs[buf][0].shape[3], n * self.inputs[buf][0].shape[1]):
                 _lib.check(self.lib.kfa_bwd(ref(q), ref(k), ref(v), ref(out), ref(dout), self.lse[buf].data_ptr(),
                                             self.stats[buf].data_ptr(), ref(dq), ref(dk), ref(dv), scale, block, dtype,
                                             self.status.data_ptr(), stream))

@@ -36,24 +36,50 @@ def kernel_dim_for(dim: int) -> int:
     return min(d for d in KERNEL_DIMS if d >= dim)
 
 
-# Which backward runs. The fused kernel (one P and one dS per tile pair, dQ accumulated with fp32
-# reduce-adds) is the fast one; its dQ varies in the last bits from run to run because the order of
-# those adds does. The split kernels (dK / dV kernel + dQ kernel that recomputes S and dP) give
-# bit-identical gradients every run at about 1.4x the backward time.
-_deterministic = os.environ.get("KFA_DETERMINISTIC", "0") not in ("", "0")
+# Which backward runs. Two implementations exist:
+#   fused  one key-major kernel, dK, dV and dQ from one P and one dS per tile pair (five matrix products),
+#          dQ accumulated across key tiles with fp32 reduce-adds in global memory: its last bits vary from
+#          run to run with the order of those adds;
+#   split  a dK / dV kernel plus a dQ kernel that recomputes S and dP (seven matrix products): bit-identical
+#          gradients every run.
+# "auto" picks by measured speed on B200: at head dim 64 the fused kernel wins (the backward is bound by the
+# exponentials, which it computes once); at head dim 128 the reduce-add traffic (64 KB per tile pair into
+# L2) costs more than the two recomputed products, and the split kernels win.
+_backward_mode = os.environ.get("KFA_BACKWARD", "auto")
+if os.environ.get("KFA_DETERMINISTIC", "0") not in ("", "0"):
+    _backward_mode = "split"
+FUSED_IS_FASTER = {64: True, 128: False}
+
+
+def set_backward(mode: str) -> None:
+    """``"auto"`` (default), ``"fused"`` or ``"split"``: the backward implementation of dense / causal /
+    block-causal ``attention`` (masks and packed batches always run the split kernels). Also settable with
+    the environment variable ``KFA_BACKWARD`` before the import."""
+    global _backward_mode
+    if mode not in ("auto", "fused", "split"):
+        raise ValueError(f"backward mode {mode!r}: 'auto', 'fused' or 'split'")
+    _backward_mode = mode
+
+
+def get_backward() -> str:
+    return _backward_mode
 
 
 def set_deterministic(flag: bool) -> None:
-    """``True``: every later backward uses the split, bit-reproducible kernels; ``False`` (the default,
-    unless the environment variable ``KFA_DETERMINISTIC`` is set to something other than 0): the fused
-    kernel. Applies to dense / causal / block-causal ``attention``; masks and packed batches always
-    run the split kernels."""
-    global _deterministic
-    _deterministic = bool(flag)
+    """``True``: every later backward uses the split kernels, whose gradients repeat bit for bit;
+    ``False``: back to ``"auto"``. (``KFA_DETERMINISTIC=1`` in the environment does the same.)"""
+    set_backward("split" if flag else "auto")
 
 
 def is_deterministic() -> bool:
-    return _deterministic
+    return _backward_mode == "split"
+
+
+def use_fused_backward(dim: int, batch_heads: int) -> bool:
+    """Whether the fused kernel runs for this head dim under the current mode."""
+    if _backward_mode == "split" or batch_heads > 65535:
+        return False
+    return _backward_mode == "fused" or FUSED_IS_FASTER[dim]
 
 
 def _strides_ok(t: Tensor) -> bool:
@@ -136,7 +162,7 @@ def attention_bwd_op(
         _lib.stream_ptr(q.device),
     )
     with torch.cuda.device(q.device):
-        if _deterministic or batch * heads > 65535:
+        if not use_fused_backward(dim, batch * heads):
             rc = lib.kfa_bwd(*tensors[:5], lse.data_ptr(), stats.data_ptr(), *tensors[5:], *tail)
         else:
             dq_acc = q.new_empty(lib.kfa_bwd_dq_acc_bytes(batch, heads, seq_q, dim) // 4, dtype=torch.float32)

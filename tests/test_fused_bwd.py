@@ -12,7 +12,7 @@ import ctypes
 import pytest
 import torch
 
-from kohakufa_b200 import _lib, attention, set_deterministic
+from kohakufa_b200 import _lib, attention
 from kohakufa_b200.op import attention_fwd_op
 from oracle import reference as oracle
 
@@ -99,27 +99,32 @@ def test_fused_dq_run_to_run():
     assert torch.equal(first[1], second[1]) and torch.equal(first[2], second[2])
 
 
-def test_autograd_uses_fused_by_default_and_split_on_request():
-    q, k, v, dout = make(1, 2, 2, 640, 640, 128, torch.bfloat16, seed=8, std=0.5)
-    grads = {}
-    try:
-        for flag in (False, True):
-            set_deterministic(flag)
-            leaves = [t.detach().clone().requires_grad_() for t in (q, k, v)]
-            attention(*leaves, causal=True).backward(dout)
-            torch.cuda.synchronize()
-            grads[flag] = [t.grad for t in leaves]
-    finally:
-        set_deterministic(False)
-    assert _lib.device_status() == 0
-    for a, b in zip(grads[False], grads[True]):
-        assert oracle.rel_l2(a, b) < 1e-3
-    # the deterministic path repeats bit for bit
-    set_deterministic(True)
-    try:
+@pytest.mark.parametrize("dim", [64, 128])
+def test_autograd_backward_modes(dim):
+    """``set_backward``: "fused" and "split" give the same gradients to within the order of fp32 additions,
+    "auto" is one of the two, and "split" repeats bit for bit."""
+    from kohakufa_b200 import set_backward
+
+    q, k, v, dout = make(1, 2, 2, 640, 640, dim, torch.bfloat16, seed=8, std=0.5)
+
+    def grads():
         leaves = [t.detach().clone().requires_grad_() for t in (q, k, v)]
         attention(*leaves, causal=True).backward(dout)
         torch.cuda.synchronize()
-        assert all(torch.equal(a.grad, b) for a, b in zip(leaves, grads[True]))
+        assert _lib.device_status() == 0
+        return [t.grad for t in leaves]
+
+    got = {}
+    try:
+        for mode in ("fused", "split", "auto"):
+            set_backward(mode)
+            got[mode] = grads()
+        set_backward("split")
+        again = grads()
     finally:
-        set_deterministic(False)
+        set_backward("auto")
+    for a, b in zip(got["fused"], got["split"]):
+        assert oracle.rel_l2(a, b) < 1e-3
+    for a, b in zip(got["auto"], got["split"]):
+        assert oracle.rel_l2(a, b) < 1e-3
+    assert all(torch.equal(a, b) for a, b in zip(again, got["split"]))

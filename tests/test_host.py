@@ -121,7 +121,7 @@ def test_center_keys_is_a_pure_shift():
 
 def test_other_exports_raise():
     reference_exports = {"PackedMask", "attention", "attention_varlen", "pack_mask", "varlen_plan"}
-    own = {"check_status", "reset_status", "set_deterministic", "is_deterministic"}
+    own = {"check_status", "reset_status", "set_deterministic", "is_deterministic", "set_backward", "get_backward"}
     assert set(kohakufa_b200.__all__) == reference_exports | own
 
 
