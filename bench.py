@@ -538,7 +538,8 @@ def ring_record(rank, world, dev, barrier, steps=2):
       over ranks; ``stream_ms``: where the compute stream's time went on the slowest rank (kernels against
       stalls waiting for NCCL transfers), from events around every wait;
     * ``parity_s16384``: the ring's out / dQ / dK / dV at S = 16384 against the single-GPU kernels on the same
-      tensors (relative L2 error, max over ranks);
+      tensors (relative L2 distance, max over ranks; both are bf16 roundings of fp32 sums taken in a
+      different order, so they differ by single bf16 roundings: the bound is 2^-8);
     * ``fp64_spot_checks``: at the full length, 4 heads x (first, middle, last) 512 query rows of out and dQ,
       and dK / dV of the last 512 keys, against a chunk-free fp64 evaluation of those rows (relative L2
       error; the tolerance is the bf16 one of the tests, 2e-2).
@@ -595,7 +596,8 @@ def ring_record(rank, world, dev, barrier, steps=2):
         out, lse = ring.ring_forward(q, k, v, scale, trace=trace)
         return out, lse, ring.ring_backward(q, k, v, out, dout, lse, scale, trace=trace)
 
-    step()
+    for _ in range(2):  # warm-up: communicators, allocator
+        step()
     barrier()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
@@ -664,7 +666,7 @@ def ring_record(rank, world, dev, barrier, steps=2):
         errs[name] = {k_: reduce_max(x) for k_, x in worst.items()}
     rec["fp64_spot_checks"] = {"heads": heads, "rows": 512, "rel_err": errs, "tolerance": 2e-2}
     rec["checks_pass"] = all(x < 2e-2 for blk in errs.values() for x in blk.values()) and all(
-        x < 1e-3 for x in rec["parity_s16384"].values()
+        x < 2.0**-8 for x in rec["parity_s16384"].values()
     )
     return rec
 

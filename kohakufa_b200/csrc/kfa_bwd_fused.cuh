@@ -41,8 +41,8 @@ namespace kfa {
 constexpr int FUSED_THREADS = 512;
 // Registers per thread: the kernel starts with 128 everywhere (512 threads x 128 = the whole register
 // file); the dQ warpgroup and the MMA + TMA warpgroup then hand registers to the P / dS warpgroups:
-// 2 x 128 x 144 + 128 x 152 + 128 x 64 = 64512 (the dQ warpgroup holds a whole 128 x 128 fp32 tile).
-constexpr int FUSED_REGS_COMPUTE = 144, FUSED_REGS_REDUCE = 152, FUSED_REGS_ISSUE = 64;
+// 2 x 128 x 144 + 128 x 152 + 128 x 72 = 65536 (the dQ warpgroup holds a whole 128 x 128 fp32 tile).
+constexpr int FUSED_REGS_COMPUTE = 144, FUSED_REGS_REDUCE = 152, FUSED_REGS_ISSUE = 72;
 
 template <int D>
 struct FusedCfg {

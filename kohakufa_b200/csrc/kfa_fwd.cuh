@@ -77,7 +77,16 @@ constexpr int TILE_LIST_CAP = 1024;
 constexpr int FWD_THREADS = 512;
 // Registers per thread once the roles have set their budgets (the kernel starts with 128 each):
 // 2 softmax warpgroups, the correction warpgroup, the MMA + TMA warpgroup: 2 x 128 x 152 + 128 x 96 + 128 x 88 = 62464.
-constexpr int FWD_REGS_SOFTMAX = 152, FWD_REGS_CORRECTION = 96, FWD_REGS_ISSUE = 88;
+#if defined(KFA_FWD_PARTS) && KFA_FWD_PARTS == 1
+constexpr int FWD_REGS_SOFTMAX = 176, FWD_REGS_CORRECTION = 72, FWD_REGS_ISSUE = 88;
+#else
+constexpr int FWD_REGS_SOFTMAX = 152, FWD_REGS_CORRECTION = 96, FWD_REGS_ISSUE = 96;
+#endif
+#ifndef KFA_FWD_PARTS
+#define KFA_FWD_PARTS 2
+#endif
+constexpr int FWD_PARTS = KFA_FWD_PARTS;       // pieces a key tile's 128 score columns are produced and consumed in
+constexpr int FWD_PART_KEYS = 128 / FWD_PARTS;
 constexpr int FWD_BAR_BYTES = 512;        // mbarriers + the tensor-memory address
 constexpr int FWD_HANDOVER_BYTES = 4096;  // alpha [half][part][128] and final (m, l) [half][2][128], fp32
 constexpr int TILE_BYTES_64 = 128 * 64 * 2;  // one 128-row x 64-column 16-bit box = 16 KB
@@ -290,7 +299,7 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     reg_budget<FWD_REGS_ISSUE>();
     {
       const bool lead = elect_one();
-      constexpr uint32_t IDESC_S = make_idesc(BF16, false, 128, 64);
+      constexpr uint32_t IDESC_S = make_idesc(BF16, false, 128, FWD_PART_KEYS);
       constexpr uint32_t IDESC_O = make_idesc(BF16, true, 128, D);
       const uint32_t tmS[2] = {tmem + Cfg::TM_S0, tmem + Cfg::TM_S1};
       const uint32_t tmO[2] = {tmem + Cfg::TM_O0, tmem + Cfg::TM_O1};
@@ -299,20 +308,20 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 
       // S_h of the 64 keys of one part (rows 64 part .. of the K tile) into columns 64 part .. of S_h
       auto issue_S = [&](int hf, int stage, int part) {
-        const uint32_t k_lo = sdesc_lo(sKV + stage * Cfg::TILE_BYTES + part * (TILE_BYTES_64 / 2), 16);
+        const uint32_t k_lo = sdesc_lo(sKV + stage * Cfg::TILE_BYTES + part * (FWD_PART_KEYS * 128), 16);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = ((kk >> 2) * TILE_BYTES_64 + (kk & 3) * 32) >> 4;
-          umma_ss_lead(lead, tmS[hf] + 64 * part, q_lo[hf] + off, k_lo + off, IDESC_S, kk > 0 ? 1u : 0u);
+          umma_ss_lead(lead, tmS[hf] + FWD_PART_KEYS * part, q_lo[hf] + off, k_lo + off, IDESC_S, kk > 0 ? 1u : 0u);
         }
       };
       // O_h += P V over the 64 keys of one part; its 16-bit P sits in the first 32 columns of the part
       auto issue_PV = [&](int hf, int stage, bool acc, int part) {
         const uint32_t v_lo = sdesc_lo(sKV + stage * Cfg::TILE_BYTES, TILE_BYTES_64);
 #pragma unroll
-        for (int k4 = 0; k4 < 4; ++k4) {
-          const int kk = part * 4 + k4;
-          umma_ts_lead(lead, tmO[hf], tmS[hf] + 64 * part + k4 * 8, v_lo + ((kk * 2048) >> 4), IDESC_O,
+        for (int k4 = 0; k4 < FWD_PART_KEYS / 16; ++k4) {
+          const int kk = part * (FWD_PART_KEYS / 16) + k4;
+          umma_ts_lead(lead, tmO[hf], tmS[hf] + FWD_PART_KEYS * part + k4 * 8, v_lo + ((kk * 2048) >> 4), IDESC_O,
                        (acc || kk > 0) ? 1u : 0u);
         }
       };
@@ -327,7 +336,7 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         ok = mbar_wait_warp(bar(B_QREADY + hf), 0, ctl, 3);
         if (!ok) break;
         tc_fence_after();
-        for (int part = 0; part < 2; ++part) {
+        for (int part = 0; part < FWD_PARTS; ++part) {
           issue_S(hf, 0, part);
           umma_commit_lead(lead, bar(B_SREADY + 2 * hf + part));
         }
@@ -348,7 +357,7 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           ok = kv_wait(ik);
           if (!ok) break;
         }
-        for (int part = 0; part < 2 && ok; ++part) {
+        for (int part = 0; part < FWD_PARTS && ok; ++part) {
           for (int hf = 0; hf < 2 && ok; ++hf) {
             if (j < n_tiles[hf]) {
               ok = mbar_wait_warp(bar(B_PREADY + 2 * hf + part), j & 1, ctl, 4);
@@ -357,7 +366,7 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
               tc_fence_after();
               issue_PV(hf, iv % NS, j > 0, part);
               umma_commit_lead(lead, bar(B_PVDONE + 2 * hf + part));
-              if (part == 1 && j == n_tiles[hf] - 1) umma_commit_lead(lead, bar(B_OFINAL + hf));
+              if (part == FWD_PARTS - 1 && j == n_tiles[hf] - 1) umma_commit_lead(lead, bar(B_OFINAL + hf));
             }
             if (more && j + 1 < n_tiles[hf]) {
               issue_S(hf, ik % NS, part);
@@ -386,7 +395,7 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const uint32_t tOh[2] = {tmem + Cfg::TM_O0 + lane_base, tmem + Cfg::TM_O1 + lane_base};
     bool ok = true;
     for (int j = 0; j < n_max && ok; ++j) {
-      for (int part = 0; part < 2 && ok; ++part) {
+      for (int part = 0; part < FWD_PARTS && ok; ++part) {
         for (int hf = 0; hf < 2; ++hf) {
           if (j >= n_tiles[hf]) continue;
           ok = mbar_wait_warp(bar(B_ALPHA + 2 * hf + part), j & 1, ctl, 9);
@@ -395,8 +404,8 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           if ((j > 0 || part > 0) && !__all_sync(0xffffffffu, alpha == 1.0f)) {
             // every part of O_h += P V issued so far has to have retired (the barrier of the previous part
             // cannot be two phases ahead: the part after the next needs this release)
-            const int prev = 2 * j + part - 1;
-            ok = mbar_wait_warp(bar(B_PVDONE + 2 * hf + (prev & 1)), (prev >> 1) & 1, ctl, 7);
+            const int prev = FWD_PARTS * j + part - 1;
+            ok = mbar_wait_warp(bar(B_PVDONE + 2 * hf + (prev % FWD_PARTS)), (prev / FWD_PARTS) & 1, ctl, 7);
             if (!ok) break;
             tc_fence_after();
             const float2 a2 = make_float2(alpha, alpha);
@@ -540,30 +549,31 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       // The tile's 128 keys are handled as two parts of 64 with their own score columns, so that the
       // tensor core refills one part while this thread works on the other.
 #pragma unroll
-      for (int part = 0; part < 2; ++part) {
+      for (int part = 0; part < FWD_PARTS; ++part) {
+        constexpr int PK = FWD_PART_KEYS;
         ok = mbar_wait_warp(bar(B_SREADY + 2 * hf + part), j & 1, ctl, 5);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t tSp = tS + 64 * part;
-        const int lim = my_limit - j * 128 - 64 * part;
-        float s[64];
-        tmem_ld32(tSp, reinterpret_cast<uint32_t*>(s));
-        tmem_ld32(tSp + 32, reinterpret_cast<uint32_t*>(s + 32));
+        const uint32_t tSp = tS + PK * part;
+        const int lim = my_limit - j * 128 - PK * part;
+        float s[PK];
+#pragma unroll
+        for (int c0 = 0; c0 < PK; c0 += 32) tmem_ld32(tSp + c0, reinterpret_cast<uint32_t*>(s + c0));
         tmem_wait_ld();
         if constexpr (MASKW) {
           if (apply_bits) {
 #pragma unroll
-            for (int i = 0; i < 64; ++i)
-              if (!((mbits[2 * part + (i >> 5)] >> (i & 31)) & 1u)) s[i] = -INFINITY;
+            for (int i = 0; i < PK; ++i)
+              if (!((mbits[(PK / 32) * part + (i >> 5)] >> (i & 31)) & 1u)) s[i] = -INFINITY;
           }
         } else if (masked) {
 #pragma unroll
-          for (int i = 0; i < 64; ++i)
+          for (int i = 0; i < PK; ++i)
             if (i >= lim) s[i] = -INFINITY;
         }
         float mx0 = fmaxf(s[0], s[1]), mx1 = fmaxf(s[2], s[3]), mx2 = fmaxf(s[4], s[5]), mx3 = fmaxf(s[6], s[7]);
 #pragma unroll
-        for (int i = 8; i < 64; i += 8) {  // pairs of maxima: three-input max instructions
+        for (int i = 8; i < PK; i += 8) {  // pairs of maxima: three-input max instructions
           mx0 = fmaxf(mx0, fmaxf(s[i], s[i + 1]));
           mx1 = fmaxf(mx1, fmaxf(s[i + 2], s[i + 3]));
           mx2 = fmaxf(mx2, fmaxf(s[i + 4], s[i + 5]));
@@ -578,24 +588,27 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         // hand the factor to the correction warpgroup: it rescales O_h while the exponentials below run
         s_alpha[(2 * hf + part) * 128 + r_in] = alpha;
         mbar_arrive(bar(B_ALPHA + 2 * hf + part));
-        // ---- the exponentials ----
+        // ---- the exponentials, 64 keys at a time (their P goes to tensor memory as soon as it is packed) ----
         const float2 neg_m = make_float2(-m_shift, -m_shift);
         const float2 c2 = make_float2(c, c);
         float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
         const float2* s2 = reinterpret_cast<const float2*>(s);
-        uint32_t pk[32];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float2 x0 = __fmul2_rn(__fadd2_rn(s2[i], neg_m), c2);
-          const float2 x1 = __fmul2_rn(__fadd2_rn(s2[i + 1], neg_m), c2);
-          const float2 p0 = make_float2(ex2(x0.x), ex2(x0.y));
-          const float2 p1 = make_float2(ex2(x1.x), ex2(x1.y));
-          la = __fadd2_rn(la, p0);
-          lb = __fadd2_rn(lb, p1);
-          pk[i] = pack16<BF16>(p0.x, p0.y);
-          pk[i + 1] = pack16<BF16>(p1.x, p1.y);
+        for (int g = 0; g < PK / 64; ++g) {
+          uint32_t pk[32];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float2 x0 = __fmul2_rn(__fadd2_rn(s2[32 * g + i], neg_m), c2);
+            const float2 x1 = __fmul2_rn(__fadd2_rn(s2[32 * g + i + 1], neg_m), c2);
+            const float2 p0 = make_float2(ex2(x0.x), ex2(x0.y));
+            const float2 p1 = make_float2(ex2(x1.x), ex2(x1.y));
+            la = __fadd2_rn(la, p0);
+            lb = __fadd2_rn(lb, p1);
+            pk[i] = pack16<BF16>(p0.x, p0.y);
+            pk[i + 1] = pack16<BF16>(p1.x, p1.y);
+          }
+          tmem_st32(tSp + 32 * g, pk);  // P over the score columns already in registers
         }
-        tmem_st32(tSp, pk);  // P of this part over its own score columns, already in registers
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(bar(B_PREADY + 2 * hf + part));

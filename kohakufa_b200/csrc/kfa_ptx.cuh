@@ -132,8 +132,16 @@ __device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity) {
 // The same for a full warp about to run warp-aligned tcgen05 instructions: the warp reconverges
 // and every lane gets the same answer (false if any lane gave up).
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, const Ctl& ctl, int site) {
+#ifdef KFA_WAIT_ONE_LANE
+  // one lane polls, the warp-wide shuffle hands its answer (and, being a warp barrier, the ordering of what
+  // it observed) to the others: 32 times fewer polls on the shared-memory pipe
+  bool ok = true;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, ctl, site);
+  return __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+#else
   const bool ok = mbar_wait(bar, parity, ctl, site);
   return __all_sync(0xffffffffu, ok);
+#endif
 }
 
 // ----------------------------------------------------------------------------------
