@@ -436,7 +436,7 @@ def main():
             "note": f"algorithmic matmuls counted for this kernel: {units[dominant]} of 7; peak = {peak_kind} burst cuBLAS bf16 "
             "(the timed region lasts a fraction of a second); sustained = the same GEMM in a seconds-long loop; "
             "clock-normalised = 4096 MAC x 2 x 148 SMs x the median SM clock sampled during the timed region; "
-            "traffic = DRAM bytes of one launch from an ncu capture of a 16-head case, scaled by the head count",
+            "traffic = DRAM bytes of one launch from an ncu capture of a small case of the same shape, scaled by the (batch, head) pairs",
         },
         "gpu_launches": (3 * world + 5 if ring_mode else 4) * args.steps,  # fwd + 3 backward launches either way
         "clocks": clocks,
@@ -451,17 +451,22 @@ def main():
         dist.destroy_process_group()
 
 
-# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of the named kernel at B=1, H=16 of
-# a configuration, from ncu captures of that small case; a launch's traffic grows in proportion to the
-# number of (batch, head) pairs, so the full launch is this times heads / 16.
-NCU_DRAM_BYTES_16_HEADS = {
-    ("dkdv", 8192, 128, 1): 176.8e6,
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of a kernel, from ncu captures of a
+# small case of the configuration's shape: (kernel, S, D, block) -> (bytes, (batch, head) pairs of the
+# captured launch). A launch's traffic grows in proportion to the pairs, so a full launch is scaled by them.
+NCU_DRAM_BYTES = {
+    ("dkdv", 8192, 128, 1): (175.1e6, 16),
+    ("dq", 8192, 128, 1): (155.5e6, 16),
+    ("fwd", 8192, 128, 1): (119.1e6, 16),
+    ("fused", 8192, 128, 1): (299.9e6, 16),
+    ("fused", 4096, 64, 256): (296.4e6, 64),
+    ("fwd", 4096, 64, 256): (118.5e6, 64),
 }
 
 
 def ncu_traffic(kernel, cfg, q_heads):
-    per16 = NCU_DRAM_BYTES_16_HEADS.get((kernel, cfg.seq, cfg.dim, cfg.block))
-    return None if per16 is None else per16 / 16 * q_heads
+    entry = NCU_DRAM_BYTES.get((kernel, cfg.seq, cfg.dim, cfg.block))
+    return None if entry is None else entry[0] / entry[1] * q_heads
 
 
 def bind_to_gpu_cpus(index):

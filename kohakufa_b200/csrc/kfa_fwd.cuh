@@ -76,7 +76,7 @@ constexpr int TILE_LIST_CAP = 1024;
 
 constexpr int FWD_THREADS = 512;
 // Registers per thread once the roles have set their budgets (the kernel starts with 128 each):
-// 2 softmax warpgroups, the correction warpgroup, the MMA + TMA warpgroup: 2 x 128 x 152 + 128 x 96 + 128 x 88 = 62464.
+// 2 softmax warpgroups, the correction warpgroup, the MMA + TMA warpgroup: 2 x 128 x 152 + 128 x 96 + 128 x 96 = 63488 (one 128-key part per tile: 176 / 72 / 88).
 #if defined(KFA_FWD_PARTS) && KFA_FWD_PARTS == 1
 constexpr int FWD_REGS_SOFTMAX = 176, FWD_REGS_CORRECTION = 72, FWD_REGS_ISSUE = 88;
 #else

@@ -52,11 +52,16 @@ def _backward_both_ways(q, k, v, dout, block):
     got = [_like(q), _like(k), _like(v)]
     for x in got:
         x.fill_(float("nan"))  # the entry point has to write every element itself
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]  # bytes the driver can still hand out on this device
     _lib.check(
         lib.kfa_bwd_static_scratch(t["q"], t["k"], t["v"], t["out"], t["dout"], lse.data_ptr(),
                                    *(ctypes.byref(_lib.tensor4(x)) for x in got), scale, block, code, word, stream)
     )
     torch.cuda.synchronize()
+    # "allocates nothing", observed: the device's free memory is the same after the call as before it
+    # (torch's caching allocator is not involved either: no torch call sits between the two readings)
+    assert torch.cuda.mem_get_info()[0] == free_before
     assert _lib.device_status() == 0
     return want, got
 
