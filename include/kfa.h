@@ -238,6 +238,13 @@ int kfa_cp_bwd_dq_step(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor
 /* grad = acc rounded to 16 bits. */
 int kfa_cp_grad_finalize(const KfaAcc32* acc, const KfaTensor4* grad, int dtype, void* stream);
 
+/* Host plumbing for callers whose tensors live in pinned HOST memory (kohakufa_b200/hostio.py): one strided
+ * copy of `rows` rows of `row_bytes` bytes between host and device (cudaMemcpy2DAsync on `stream`;
+ * to_device != 0: host -> device), e.g. the rows of a group of heads out of [B, S, H, D] storage. No
+ * counterpart in the reference, whose callers hold CUDA tensors. */
+int kfa_copy_rows(void* dst, int64_t dst_pitch, const void* src, int64_t src_pitch, int64_t row_bytes,
+                  int64_t rows, int to_device, void* stream);
+
 /* Diagnostic: the raw scores Q K^T (unscaled, unmasked) as fp32 [B, H, Sq, Skv] (contiguous), produced by
  * the same tensor-core instruction sequence the attention kernels use (one fp32-accumulating MMA per 16
  * elements of the head dim, in ascending order). What comes out is NOT the correctly rounded dot

@@ -45,6 +45,7 @@ SYMBOLS = (
     "kfa_cp_bwd_dkdv_step",
     "kfa_cp_bwd_dq_step",
     "kfa_cp_grad_finalize",
+    "kfa_copy_rows",
     "kfa_scores",
     "kfa_selftest",
 )
@@ -139,6 +140,7 @@ def load() -> ctypes.CDLL:
         lib.kfa_cp_bwd_dkdv_step.argtypes = [T, T, T, T, fp, i64, A, A, i32, f32, i32, i32, ip, vp]
         lib.kfa_cp_bwd_dq_step.argtypes = [T, T, T, T, fp, i64, A, i32, f32, i32, i32, ip, vp]
         lib.kfa_cp_grad_finalize.argtypes = [A, T, i32, vp]
+        lib.kfa_copy_rows.argtypes = [vp, i64, vp, i64, i64, i64, i32, vp]
         lib.kfa_scores.argtypes = [T, T, fp, i32, ip, vp]
         lib.kfa_selftest.argtypes = [ctypes.c_char_p, ctypes.c_int]
         for name in SYMBOLS:

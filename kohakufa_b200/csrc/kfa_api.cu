@@ -601,6 +601,17 @@ int kfa_bwd(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const
   return kfa_bwd_dq(q, k, v, dout, stats, dq, scale, block, dtype, dev_status, stream);
 }
 
+int kfa_copy_rows(void* dst, int64_t dst_pitch, const void* src, int64_t src_pitch, int64_t row_bytes, int64_t rows,
+                  int to_device, void* stream) {
+  if (!dst || !src || row_bytes <= 0 || rows <= 0 || dst_pitch < row_bytes || src_pitch < row_bytes)
+    return fail(KFA_ERR_ARG, "kfa_copy_rows: null pointer or pitch shorter than a row");
+  KFA_CUDA(cudaMemcpy2DAsync(dst, static_cast<size_t>(dst_pitch), src, static_cast<size_t>(src_pitch),
+                             static_cast<size_t>(row_bytes), static_cast<size_t>(rows),
+                             to_device ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost,
+                             static_cast<cudaStream_t>(stream)));
+  return KFA_OK;
+}
+
 int64_t kfa_bwd_dq_acc_bytes(int64_t B, int64_t H, int64_t Sq, int64_t D) {
   return B * H * ((Sq + 127) / 128) * 128 * D * 4;
 }

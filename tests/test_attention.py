@@ -356,3 +356,29 @@ def test_host_buffer_entry_point():
     out2 = hostio.attention_fwd_bwd_host(*host, causal=True, pipeline=pipe)[0]
     torch.cuda.synchronize()
     assert torch.equal(out2, want[0].cpu())
+
+
+@pytest.mark.parametrize("storage", ["bshd", "bhsd"])
+def test_host_buffer_head_groups(storage):
+    """Grouped-query heads through the host entry point. With ``[B, S, H, D]`` storage the units are
+    groups of K / V heads with the query heads they serve (pitched copies); with ``[B, H, S, D]``
+    storage they are batch entries."""
+    from kohakufa_b200 import hostio
+
+    gen = torch.Generator().manual_seed(5)
+
+    def make(heads, seq):
+        if storage == "bshd":
+            return torch.randn(2, seq, heads, 128, generator=gen).bfloat16().pin_memory().transpose(1, 2)
+        return torch.randn(2, heads, seq, 128, generator=gen).bfloat16().pin_memory()
+
+    host = [make(8, 260), make(2, 390), make(2, 390), make(8, 260)]
+    pipe = hostio.HostPipeline(*host[:3], "cuda")
+    assert len(pipe.units) == (4 if storage == "bshd" else 2)
+    got = hostio.attention_fwd_bwd_host(*host, block_causal=130, pipeline=pipe)
+    torch.cuda.synchronize()
+    q, k, v = (t.cuda().requires_grad_() for t in host[:3])
+    want = run(q, k, v, host[3].cuda(), block_causal=130)
+    for g, w in zip(got, want):
+        assert oracle.rel_l2(g, w.cpu()) < 1e-3
+    assert torch.equal(got[0], want[0].cpu())
