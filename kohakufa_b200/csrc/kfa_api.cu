@@ -601,6 +601,12 @@ int kfa_bwd(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const
   return kfa_bwd_dq(q, k, v, dout, stats, dq, scale, block, dtype, dev_status, stream);
 }
 
+#ifdef KFA_FWD_TRACE
+int kfa_trace_read(long long* out) {
+  return cudaMemcpyFromSymbol(out, kfa::kfa_trace, sizeof(kfa::kfa_trace)) == cudaSuccess ? 0 : 1;
+}
+#endif
+
 int kfa_copy_rows(void* dst, int64_t dst_pitch, const void* src, int64_t src_pitch, int64_t row_bytes, int64_t rows,
                   int to_device, void* stream) {
   if (!dst || !src || row_bytes <= 0 || rows <= 0 || dst_pitch < row_bytes || src_pitch < row_bytes)

@@ -8,9 +8,10 @@
 //   CTA = 256 query rows of one (batch, head), as two 128-row halves; key tiles of 128. 512 threads:
 //   warps 0-3   softmax of half 0 (thread t <-> query row t): row max, exponentials, P, row sum
 //   warps 4-7   the same for half 1
-//   warps 8-11  correction for both halves: exact rescale of O_h whenever a row's max moved, and the
-//               epilogue (O / l -> 16 bits -> global, statistics); runs beside the exponentials
-//   warp  12    MMA issue (one lane): S_h = Q_h K_j^T, O_h += P_h V_j      (tcgen05, TMEM)
+//   warps 8-11  correction for both halves: exact rescale of O_h whenever a row's max moved; runs beside
+//               the exponentials
+//   (epilogue: each softmax warpgroup writes its own half, O / l -> 16 bits -> global, statistics)
+//   warps 12, 14  MMA issue for half 0 / half 1 (one lane each): S_h = Q_h K_j^T, O_h += P_h V_j  (tcgen05, TMEM)
 //   warp  13    TMA producer (one lane): Q halves once, K_j / V_j through a ring
 //   Register budgets per role (setmaxnreg): the softmax warpgroups take what the others give up.
 //
@@ -88,7 +89,7 @@ constexpr int FWD_REGS_SOFTMAX = 152, FWD_REGS_CORRECTION = 96, FWD_REGS_ISSUE =
 constexpr int FWD_PARTS = KFA_FWD_PARTS;       // pieces a key tile's 128 score columns are produced and consumed in
 constexpr int FWD_PART_KEYS = 128 / FWD_PARTS;
 constexpr int FWD_BAR_BYTES = 512;        // mbarriers + the tensor-memory address
-constexpr int FWD_HANDOVER_BYTES = 4096;  // alpha [half][part][128] and final (m, l) [half][2][128], fp32
+constexpr int FWD_HANDOVER_BYTES = 2048;  // alpha [half][part][128], fp32
 constexpr int TILE_BYTES_64 = 128 * 64 * 2;  // one 128-row x 64-column 16-bit box = 16 KB
 
 template <int D>
@@ -114,6 +115,13 @@ __device__ __forceinline__ int key_limit(int r, int P, int Skv) {
   return lim < Skv ? static_cast<int>(lim) : Skv;
 }
 
+#ifdef KFA_FWD_TRACE
+__device__ long long kfa_trace[6][64][2][8];
+#define TR(role, j, part, ev) do { if (trace_on && (j) < 64) kfa_trace[role][j][part][ev] = clock64(); } while (0)
+#else
+#define TR(role, j, part, ev) do {} while (0)
+#endif
+
 template <int D, bool BF16, bool MASKW>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -135,24 +143,26 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   constexpr int B_SREADY = 2 + 2 * NS;    // 4: [half][part] the 64 score columns of that part are in TMEM
   constexpr int B_PREADY = 6 + 2 * NS;    // 4: [half][part] the 64 keys of P_h of that part are stored (128 arrivals)
   constexpr int B_OFINAL = 10 + 2 * NS;   // 2
-  constexpr int B_DRAIN = 12 + 2 * NS;    // 1
-  constexpr int B_PVDONE = 13 + 2 * NS;   // 4: [half][part] that part of O_h += P V has retired
-  constexpr int B_ALPHA = 17 + 2 * NS;    // 4: [half][part] the rows' rescale factors are in shared memory (128 arrivals)
-  constexpr int B_OREADY = 21 + 2 * NS;   // 4: [half][part] O_h is rescaled for that part (128 arrivals)
-  constexpr int B_LFINAL = 25 + 2 * NS;   // 2: [half] the rows' final m and l are in shared memory (128 arrivals)
-  constexpr int N_BARS = 27 + 2 * NS;
+  constexpr int B_DRAIN = 12 + 2 * NS;    // 2: [half] everything that half's MMA warp issued has retired
+  constexpr int B_PVDONE = 14 + 2 * NS;   // 4: [half][part] that part of O_h += P V has retired
+  constexpr int B_ALPHA = 18 + 2 * NS;    // 4: [half][part] the rows' rescale factors are in shared memory (128 arrivals)
+  constexpr int B_OREADY = 22 + 2 * NS;   // 4: [half][part] O_h is rescaled for that part (128 arrivals)
+  constexpr int N_BARS = 26 + 2 * NS;
   static_assert(N_BARS * 8 + 16 <= FWD_BAR_BYTES, "barrier block too small");
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + N_BARS);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
-  // hand-over between the softmax and the correction warpgroups: alpha [half][part][row], then (m, l) [half][2][row]
+  // hand-over between the softmax and the correction warpgroups: alpha [half][part][row]
   float* s_alpha = reinterpret_cast<float*>(smem + Cfg::SMEM_TILES + FWD_BAR_BYTES);
-  float* s_final = s_alpha + 4 * 128;
   const uint32_t bar0 = smem_u32(bars);
   auto bar = [&](int i) { return bar0 + 8u * i; };
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
+#ifdef KFA_FWD_TRACE
+  const bool trace_on = (blockIdx.x == 0) && (lane == 0);
+  if (warp == 8) TR(2, 0, 0, 4);
+#endif
 
   // ---- tile decode: head-major, heaviest query tile of a head first when causal ----
   const int bh = blockIdx.x / p.n_q_tiles;
@@ -195,7 +205,7 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     mbar_init(bar(B_QREADY + 1), 1);
     for (int i = 0; i < NS; ++i) {
       mbar_init(bar(B_KVREADY + i), 1);
-      mbar_init(bar(B_KVFREE + i), 1);
+      mbar_init(bar(B_KVFREE + i), 2);  // one arrival per MMA warp
     }
     for (int i = 0; i < 4; ++i) {
       mbar_init(bar(B_SREADY + i), 1);
@@ -206,9 +216,8 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(B_OFINAL + i), 1);
-      mbar_init(bar(B_LFINAL + i), 128);
+      mbar_init(bar(B_DRAIN + i), 1);
     }
-    mbar_init(bar(B_DRAIN), 1);
     // An earlier failure (status word already set): allocate, skip the work, free.
     *s_abort = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
     fence_mbar_init();
@@ -241,6 +250,7 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *s_tmem;
+  if (warp == 8) TR(2, 0, 0, 5);
   if (use_list) {
     n_max = static_cast<int>(s_tmem[2]);
     n_tiles[0] = n_tiles[0] > 0 ? n_max : 0;
@@ -253,7 +263,7 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   // Each role sets its register budget first (the kernel starts with 128 per thread).
   if (dead) {
     // nothing to do
-  } else if (warp >= 14) {
+  } else if (warp == 15) {
     reg_budget<FWD_REGS_ISSUE>();
   } else if (warp == 13) {
     // =========================== TMA producer ===========================
@@ -293,35 +303,40 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           if (armed[i] >= 0) mbar_drain(bar(B_KVREADY + i), armed[i] & 1);
       }
     }
-  } else if (warp == 12) {
+  } else if (warp == 12 || warp == 14) {
     // =========================== MMA issue ===========================
-    // The whole warp runs this role converged; one elected lane issues the tcgen05 instructions.
+    // One warp per half (12: half 0, 14: half 1): the two halves' chains are independent, and two issuing
+    // warps keep the tensor core fed while one of them sits in its waits. The whole warp runs this role
+    // converged; one elected lane issues the tcgen05 instructions. A K / V stage is free again once BOTH
+    // warps' instructions that read it have retired (a commit counts only the committing thread's own).
     reg_budget<FWD_REGS_ISSUE>();
     {
+      const int hf = (warp - 12) >> 1;
       const bool lead = elect_one();
       constexpr uint32_t IDESC_S = make_idesc(BF16, false, 128, FWD_PART_KEYS);
       constexpr uint32_t IDESC_O = make_idesc(BF16, true, 128, D);
-      const uint32_t tmS[2] = {tmem + Cfg::TM_S0, tmem + Cfg::TM_S1};
-      const uint32_t tmO[2] = {tmem + Cfg::TM_O0, tmem + Cfg::TM_O1};
-      const uint32_t q_lo[2] = {sdesc_lo(sQ, 16), sdesc_lo(sQ + Cfg::TILE_BYTES, 16)};
+      const uint32_t tmS = tmem + (hf ? Cfg::TM_S1 : Cfg::TM_S0);
+      const uint32_t tmO = tmem + (hf ? Cfg::TM_O1 : Cfg::TM_O0);
+      const uint32_t q_lo = sdesc_lo(sQ + hf * Cfg::TILE_BYTES, 16);
+      const int nt = n_tiles[hf];
       bool ok = true;
 
       // S_h of the 64 keys of one part (rows 64 part .. of the K tile) into columns 64 part .. of S_h
-      auto issue_S = [&](int hf, int stage, int part) {
+      auto issue_S = [&](int stage, int part) {
         const uint32_t k_lo = sdesc_lo(sKV + stage * Cfg::TILE_BYTES + part * (FWD_PART_KEYS * 128), 16);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = ((kk >> 2) * TILE_BYTES_64 + (kk & 3) * 32) >> 4;
-          umma_ss_lead(lead, tmS[hf] + FWD_PART_KEYS * part, q_lo[hf] + off, k_lo + off, IDESC_S, kk > 0 ? 1u : 0u);
+          umma_ss_lead(lead, tmS + FWD_PART_KEYS * part, q_lo + off, k_lo + off, IDESC_S, kk > 0 ? 1u : 0u);
         }
       };
       // O_h += P V over the 64 keys of one part; its 16-bit P sits in the first 32 columns of the part
-      auto issue_PV = [&](int hf, int stage, bool acc, int part) {
+      auto issue_PV = [&](int stage, bool acc, int part) {
         const uint32_t v_lo = sdesc_lo(sKV + stage * Cfg::TILE_BYTES, TILE_BYTES_64);
 #pragma unroll
         for (int k4 = 0; k4 < FWD_PART_KEYS / 16; ++k4) {
           const int kk = part * (FWD_PART_KEYS / 16) + k4;
-          umma_ts_lead(lead, tmO[hf], tmS[hf] + FWD_PART_KEYS * part + k4 * 8, v_lo + ((kk * 2048) >> 4), IDESC_O,
+          umma_ts_lead(lead, tmO, tmS + FWD_PART_KEYS * part + k4 * 8, v_lo + ((kk * 2048) >> 4), IDESC_O,
                        (acc || kk > 0) ? 1u : 0u);
         }
       };
@@ -329,24 +344,23 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         return mbar_wait_warp(bar(B_KVREADY + idx % NS), (idx / NS) & 1, ctl, 2);
       };
 
-      // S(0), both parts, for both halves
+      // S(0), both parts
       ok = kv_wait(0);
-      for (int hf = 0; hf < 2 && ok; ++hf) {
-        if (n_tiles[hf] == 0) continue;
+      if (ok && nt > 0) {
         ok = mbar_wait_warp(bar(B_QREADY + hf), 0, ctl, 3);
-        if (!ok) break;
-        tc_fence_after();
-        for (int part = 0; part < FWD_PARTS; ++part) {
-          issue_S(hf, 0, part);
-          umma_commit_lead(lead, bar(B_SREADY + 2 * hf + part));
+        if (ok) {
+          tc_fence_after();
+          for (int part = 0; part < FWD_PARTS; ++part) {
+            issue_S(0, part);
+            umma_commit_lead(lead, bar(B_SREADY + 2 * hf + part));
+          }
         }
       }
       if (ok) umma_commit_lead(lead, bar(B_KVFREE + 0));
 
-      // Per key tile and 64-key part, for each half: O_h += P V of the part (once its P is stored and O_h
-      // carries the part's rescale), then the next tile's scores of the same part overwrite it. The other
-      // part of S_h is untouched meanwhile, so the softmax of one part runs while the tensor core works on
-      // the other.
+      // Per key tile and 64-key part: O_h += P V of the part (once its P is stored and O_h carries the
+      // part's rescale), then the next tile's scores of the same part overwrite it. The other part of S_h
+      // is untouched meanwhile, so the softmax of one part runs while the tensor core works on the other.
       for (int j = 0; j < n_max && ok; ++j) {
         const int iv = 2 * j + 1;  // V_j
         const int ik = 2 * j + 2;  // K_{j+1}
@@ -358,20 +372,23 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           if (!ok) break;
         }
         for (int part = 0; part < FWD_PARTS && ok; ++part) {
-          for (int hf = 0; hf < 2 && ok; ++hf) {
-            if (j < n_tiles[hf]) {
-              ok = mbar_wait_warp(bar(B_PREADY + 2 * hf + part), j & 1, ctl, 4);
-              if (ok) ok = mbar_wait_warp(bar(B_OREADY + 2 * hf + part), j & 1, ctl, 8);
-              if (!ok) break;
-              tc_fence_after();
-              issue_PV(hf, iv % NS, j > 0, part);
-              umma_commit_lead(lead, bar(B_PVDONE + 2 * hf + part));
-              if (part == FWD_PARTS - 1 && j == n_tiles[hf] - 1) umma_commit_lead(lead, bar(B_OFINAL + hf));
-            }
-            if (more && j + 1 < n_tiles[hf]) {
-              issue_S(hf, ik % NS, part);
-              umma_commit_lead(lead, bar(B_SREADY + 2 * hf + part));
-            }
+          if (j < nt) {
+            TR(3 + 2 * hf, j, part, 0);
+            ok = mbar_wait_warp(bar(B_PREADY + 2 * hf + part), j & 1, ctl, 4);
+            TR(3 + 2 * hf, j, part, 1);
+            if (ok) ok = mbar_wait_warp(bar(B_OREADY + 2 * hf + part), j & 1, ctl, 8);
+            if (!ok) break;
+            TR(3 + 2 * hf, j, part, 2);
+            tc_fence_after();
+            issue_PV(iv % NS, j > 0, part);
+            umma_commit_lead(lead, bar(B_PVDONE + 2 * hf + part));
+            if (part == FWD_PARTS - 1 && j == nt - 1) umma_commit_lead(lead, bar(B_OFINAL + hf));
+            TR(3 + 2 * hf, j, part, 3);
+          }
+          if (more && j + 1 < nt) {
+            issue_S(ik % NS, part);
+            umma_commit_lead(lead, bar(B_SREADY + 2 * hf + part));
+            TR(3 + 2 * hf, j, part, 4);
           }
         }
         if (ok) {
@@ -380,11 +397,11 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
       }
       // Everything issued has to retire before TMEM is freed.
-      umma_commit_lead(lead, bar(B_DRAIN));
-      mbar_drain(bar(B_DRAIN), 0);
+      umma_commit_lead(lead, bar(B_DRAIN + hf));
+      mbar_drain(bar(B_DRAIN + hf), 0);
     }
   } else if (warp >= 8) {
-    // =========================== correction: rescale of O, epilogue ===========================
+    // =========================== correction: rescale of O ===========================
     // Thread t <-> row t of BOTH halves. For every (half, part) in the order the MMA warp consumes them:
     // take the rows' factors alpha = exp2((m_old - m_new) c) from the softmax warpgroup, multiply O_h by
     // them if any row of the warp moved its max (exact; bit-identical to always multiplying), release the
@@ -398,8 +415,10 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       for (int part = 0; part < FWD_PARTS && ok; ++part) {
         for (int hf = 0; hf < 2; ++hf) {
           if (j >= n_tiles[hf]) continue;
+          if (warp == 8) TR(2 + 2 * hf, j, part, 0);
           ok = mbar_wait_warp(bar(B_ALPHA + 2 * hf + part), j & 1, ctl, 9);
           if (!ok) break;
+          if (warp == 8) TR(2 + 2 * hf, j, part, 1);
           const float alpha = s_alpha[(2 * hf + part) * 128 + r_in];
           if ((j > 0 || part > 0) && !__all_sync(0xffffffffu, alpha == 1.0f)) {
             // every part of O_h += P V issued so far has to have retired (the barrier of the previous part
@@ -422,22 +441,124 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           }
           tc_fence_before();
           mbar_arrive(bar(B_OREADY + 2 * hf + part));
+          if (warp == 8) TR(2 + 2 * hf, j, part, 2);
         }
       }
     }
-    // ---- epilogue, one half after the other ----
-    for (int hf = 0; hf < 2 && ok; ++hf) {
-      const int nt = n_tiles[hf];
-      if (nt == 0) continue;
-      ok = mbar_wait_warp(bar(B_LFINAL + hf), 0, ctl, 5);
-      if (ok) ok = mbar_wait_warp(bar(B_OFINAL + hf), 0, ctl, 6);
+  } else {
+    // =========================== softmax ===========================
+    reg_budget<FWD_REGS_SOFTMAX>();
+    const int hf = warp >> 2;
+    const int r_in = tid & 127;
+    const int row = row0 + 128 * hf + r_in;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tS = tmem + (hf ? Cfg::TM_S1 : Cfg::TM_S0) + lane_base;
+    const int nt = n_tiles[hf];
+    const int nu = n_unmasked[hf];
+    const int my_limit = key_limit(min(row, Sq - 1), p.P, Skv);
+    const float c = p.c;
+
+    float m = -INFINITY;
+    float l = 0.f;
+    bool ok = true;
+    // boolean mask: this row's words, one 16-byte load per key tile, fetched a tile ahead
+    const uint4* mrow = nullptr;
+    uint4 mnext = make_uint4(0u, 0u, 0u, 0u);
+    if constexpr (MASKW) {
+      mrow = reinterpret_cast<const uint4*>(p.mw + bc * p.mw_sb + h * p.mw_sh +
+                                            static_cast<long long>(min(row, Sq - 1)) * p.mw_row);
+      if (nt > 0) mnext = __ldg(mrow + tile_of(0));
+    }
+    for (int j = 0; j < nt; ++j) {  // j counts visited tiles (tile_of(j) is the key tile)
+      uint32_t mbits[4] = {mnext.x, mnext.y, mnext.z, mnext.w};
+      bool apply_bits = false;
+      if constexpr (MASKW) {
+        if (j + 1 < nt) mnext = __ldg(mrow + tile_of(j + 1));
+        apply_bits = !__all_sync(0xffffffffu, (mbits[0] & mbits[1] & mbits[2] & mbits[3]) == 0xffffffffu);
+      }
+      const bool masked = (j >= nu);
+      // The tile's 128 keys are handled as two parts of 64 with their own score columns, so that the
+      // tensor core refills one part while this thread works on the other.
+#pragma unroll
+      for (int part = 0; part < FWD_PARTS; ++part) {
+        constexpr int PK = FWD_PART_KEYS;
+        if ((warp & 3) == 0) TR(hf, j, part, 0);
+        ok = mbar_wait_warp(bar(B_SREADY + 2 * hf + part), j & 1, ctl, 5);
+        if (!ok) break;
+        if ((warp & 3) == 0) TR(hf, j, part, 1);
+        tc_fence_after();
+        const uint32_t tSp = tS + PK * part;
+        const int lim = my_limit - j * 128 - PK * part;
+        float s[PK];
+#pragma unroll
+        for (int c0 = 0; c0 < PK; c0 += 32) tmem_ld32(tSp + c0, reinterpret_cast<uint32_t*>(s + c0));
+        tmem_wait_ld();
+        if ((warp & 3) == 0) TR(hf, j, part, 2);
+        if constexpr (MASKW) {
+          if (apply_bits) {
+#pragma unroll
+            for (int i = 0; i < PK; ++i)
+              if (!((mbits[(PK / 32) * part + (i >> 5)] >> (i & 31)) & 1u)) s[i] = -INFINITY;
+          }
+        } else if (masked) {
+#pragma unroll
+          for (int i = 0; i < PK; ++i)
+            if (i >= lim) s[i] = -INFINITY;
+        }
+        float mx0 = fmaxf(s[0], s[1]), mx1 = fmaxf(s[2], s[3]), mx2 = fmaxf(s[4], s[5]), mx3 = fmaxf(s[6], s[7]);
+#pragma unroll
+        for (int i = 8; i < PK; i += 8) {  // pairs of maxima: three-input max instructions
+          mx0 = fmaxf(mx0, fmaxf(s[i], s[i + 1]));
+          mx1 = fmaxf(mx1, fmaxf(s[i + 2], s[i + 3]));
+          mx2 = fmaxf(mx2, fmaxf(s[i + 4], s[i + 5]));
+          mx3 = fmaxf(mx3, fmaxf(s[i + 6], s[i + 7]));
+        }
+        const float m_new = fmaxf(fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)), m);
+        // A row that has seen no key yet (boolean masks only) shifts by 0: its exponents stay -inf, P = 0.
+        const float m_shift = (MASKW && m_new == -INFINITY) ? 0.f : m_new;
+        // Shift first, then scale: the largest exponent of the row is exactly 0.
+        const float alpha = ex2(__fmul_rn(__fsub_rn(m, m_shift), c));
+        m = m_new;
+        // hand the factor to the correction warpgroup: it rescales O_h while the exponentials below run
+        s_alpha[(2 * hf + part) * 128 + r_in] = alpha;
+        mbar_arrive(bar(B_ALPHA + 2 * hf + part));
+        if ((warp & 3) == 0) TR(hf, j, part, 3);
+        // ---- the exponentials, 64 keys at a time (their P goes to tensor memory as soon as it is packed) ----
+        const float2 neg_m = make_float2(-m_shift, -m_shift);
+        const float2 c2 = make_float2(c, c);
+        float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
+        const float2* s2 = reinterpret_cast<const float2*>(s);
+        uint32_t pk[PK / 2];
+        {
+#pragma unroll
+          for (int i = 0; i < PK / 2; i += 2) {
+            const float2 x0 = __fmul2_rn(__fadd2_rn(s2[i], neg_m), c2);
+            const float2 x1 = __fmul2_rn(__fadd2_rn(s2[i + 1], neg_m), c2);
+            const float2 p0 = make_float2(ex2(x0.x), ex2(x0.y));
+            const float2 p1 = make_float2(ex2(x1.x), ex2(x1.y));
+            la = __fadd2_rn(la, p0);
+            lb = __fadd2_rn(lb, p1);
+            pk[i] = pack16<BF16>(p0.x, p0.y);
+            pk[i + 1] = pack16<BF16>(p1.x, p1.y);
+          }
+        }
+#pragma unroll
+        for (int c0 = 0; c0 < PK / 2; c0 += 32) tmem_st32(tSp + c0, pk + c0);  // P over the score columns already in registers
+        if ((warp & 3) == 0) TR(hf, j, part, 4);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar(B_PREADY + 2 * hf + part));
+        if ((warp & 3) == 0) TR(hf, j, part, 5);
+        l = l * alpha + ((la.x + la.y) + (lb.x + lb.y));
+      }
       if (!ok) break;
+    }
+    // ---- epilogue: each softmax warpgroup writes its own half (the rows' m and l are in its registers) ----
+    if (ok && nt > 0) ok = mbar_wait_warp(bar(B_OFINAL + hf), 0, ctl, 6);
+    if (ok && nt > 0) {
+      if ((warp & 3) == 0) TR(2, 0, 1, 4 + hf);
       tc_fence_after();
-      const int row = row0 + 128 * hf + r_in;
-      const uint32_t tO = tOh[hf];
-      float m = s_final[(2 * hf) * 128 + r_in];
-      float l = s_final[(2 * hf + 1) * 128 + r_in];
-      const float c = p.c;
+      const uint32_t tO = tmem + (hf ? Cfg::TM_O1 : Cfg::TM_O0) + lane_base;
       if (p.mode != 0) {
         // Partial result of a context-parallel step: the unnormalised fp32 O with its (m, l) goes to
         // (mode 1), or is merged into (mode 2), the carry in global memory. Merging keeps the two
@@ -514,118 +635,13 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
       }
     }
-  } else {
-    // =========================== softmax ===========================
-    reg_budget<FWD_REGS_SOFTMAX>();
-    const int hf = warp >> 2;
-    const int r_in = tid & 127;
-    const int row = row0 + 128 * hf + r_in;
-    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t tS = tmem + (hf ? Cfg::TM_S1 : Cfg::TM_S0) + lane_base;
-    const int nt = n_tiles[hf];
-    const int nu = n_unmasked[hf];
-    const int my_limit = key_limit(min(row, Sq - 1), p.P, Skv);
-    const float c = p.c;
-
-    float m = -INFINITY;
-    float l = 0.f;
-    bool ok = true;
-    // boolean mask: this row's words, one 16-byte load per key tile, fetched a tile ahead
-    const uint4* mrow = nullptr;
-    uint4 mnext = make_uint4(0u, 0u, 0u, 0u);
-    if constexpr (MASKW) {
-      mrow = reinterpret_cast<const uint4*>(p.mw + bc * p.mw_sb + h * p.mw_sh +
-                                            static_cast<long long>(min(row, Sq - 1)) * p.mw_row);
-      if (nt > 0) mnext = __ldg(mrow + tile_of(0));
-    }
-    for (int j = 0; j < nt; ++j) {  // j counts visited tiles (tile_of(j) is the key tile)
-      uint32_t mbits[4] = {mnext.x, mnext.y, mnext.z, mnext.w};
-      bool apply_bits = false;
-      if constexpr (MASKW) {
-        if (j + 1 < nt) mnext = __ldg(mrow + tile_of(j + 1));
-        apply_bits = !__all_sync(0xffffffffu, (mbits[0] & mbits[1] & mbits[2] & mbits[3]) == 0xffffffffu);
-      }
-      const bool masked = (j >= nu);
-      // The tile's 128 keys are handled as two parts of 64 with their own score columns, so that the
-      // tensor core refills one part while this thread works on the other.
-#pragma unroll
-      for (int part = 0; part < FWD_PARTS; ++part) {
-        constexpr int PK = FWD_PART_KEYS;
-        ok = mbar_wait_warp(bar(B_SREADY + 2 * hf + part), j & 1, ctl, 5);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t tSp = tS + PK * part;
-        const int lim = my_limit - j * 128 - PK * part;
-        float s[PK];
-#pragma unroll
-        for (int c0 = 0; c0 < PK; c0 += 32) tmem_ld32(tSp + c0, reinterpret_cast<uint32_t*>(s + c0));
-        tmem_wait_ld();
-        if constexpr (MASKW) {
-          if (apply_bits) {
-#pragma unroll
-            for (int i = 0; i < PK; ++i)
-              if (!((mbits[(PK / 32) * part + (i >> 5)] >> (i & 31)) & 1u)) s[i] = -INFINITY;
-          }
-        } else if (masked) {
-#pragma unroll
-          for (int i = 0; i < PK; ++i)
-            if (i >= lim) s[i] = -INFINITY;
-        }
-        float mx0 = fmaxf(s[0], s[1]), mx1 = fmaxf(s[2], s[3]), mx2 = fmaxf(s[4], s[5]), mx3 = fmaxf(s[6], s[7]);
-#pragma unroll
-        for (int i = 8; i < PK; i += 8) {  // pairs of maxima: three-input max instructions
-          mx0 = fmaxf(mx0, fmaxf(s[i], s[i + 1]));
-          mx1 = fmaxf(mx1, fmaxf(s[i + 2], s[i + 3]));
-          mx2 = fmaxf(mx2, fmaxf(s[i + 4], s[i + 5]));
-          mx3 = fmaxf(mx3, fmaxf(s[i + 6], s[i + 7]));
-        }
-        const float m_new = fmaxf(fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)), m);
-        // A row that has seen no key yet (boolean masks only) shifts by 0: its exponents stay -inf, P = 0.
-        const float m_shift = (MASKW && m_new == -INFINITY) ? 0.f : m_new;
-        // Shift first, then scale: the largest exponent of the row is exactly 0.
-        const float alpha = ex2(__fmul_rn(__fsub_rn(m, m_shift), c));
-        m = m_new;
-        // hand the factor to the correction warpgroup: it rescales O_h while the exponentials below run
-        s_alpha[(2 * hf + part) * 128 + r_in] = alpha;
-        mbar_arrive(bar(B_ALPHA + 2 * hf + part));
-        // ---- the exponentials, 64 keys at a time (their P goes to tensor memory as soon as it is packed) ----
-        const float2 neg_m = make_float2(-m_shift, -m_shift);
-        const float2 c2 = make_float2(c, c);
-        float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
-        const float2* s2 = reinterpret_cast<const float2*>(s);
-#pragma unroll
-        for (int g = 0; g < PK / 64; ++g) {
-          uint32_t pk[32];
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float2 x0 = __fmul2_rn(__fadd2_rn(s2[32 * g + i], neg_m), c2);
-            const float2 x1 = __fmul2_rn(__fadd2_rn(s2[32 * g + i + 1], neg_m), c2);
-            const float2 p0 = make_float2(ex2(x0.x), ex2(x0.y));
-            const float2 p1 = make_float2(ex2(x1.x), ex2(x1.y));
-            la = __fadd2_rn(la, p0);
-            lb = __fadd2_rn(lb, p1);
-            pk[i] = pack16<BF16>(p0.x, p0.y);
-            pk[i + 1] = pack16<BF16>(p1.x, p1.y);
-          }
-          tmem_st32(tSp + 32 * g, pk);  // P over the score columns already in registers
-        }
-        tmem_wait_st();
-        tc_fence_before();
-        mbar_arrive(bar(B_PREADY + 2 * hf + part));
-        l = l * alpha + ((la.x + la.y) + (lb.x + lb.y));
-      }
-      if (!ok) break;
-    }
-    if (ok && nt > 0) {  // the rows' final statistics, for the epilogue
-      s_final[(2 * hf) * 128 + r_in] = m;
-      s_final[(2 * hf + 1) * 128 + r_in] = l;
-      mbar_arrive(bar(B_LFINAL + hf));
-    }
   }
 
   // ---- teardown (every thread gets here, also after an abort) ----
+  if (warp == 8) TR(2, 1, 0, 4);
   tc_fence_before();
   __syncthreads();
+  if (warp == 8) TR(2, 1, 0, 5);
   if (*s_abort) {  // gave up (or an earlier kernel did): the rows of this CTA read as NaN
     const int r1 = min(row0 + 256, Sq);
     const long long bhl = static_cast<long long>(b) * p.H + h;
