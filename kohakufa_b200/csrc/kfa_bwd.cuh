@@ -411,10 +411,13 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   auto bar = [&](int i) { return bar0 + 8u * i; };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef KFA_FWD_TRACE
+  const bool trace_on = (blockIdx.x == 0) && (lane == 0);
+#endif
 
-  // tile decode: head-major; when causal the first key tiles see the most queries and come first
-  const int bh = blockIdx.x / p.n_k128;  // over batch x K / V heads
-  const int kt = blockIdx.x % p.n_k128;
+  // tile decode (groups of heads, tile-major inside); when causal the first key tiles see the most queries and come first
+  int bh, kt;  // bh over batch x K / V heads
+  decode_tile(blockIdx.x, p.B * p.Hkv, p.n_k128, bh, kt);
   const int b = bh / p.Hkv, hk = bh % p.Hkv;
   const int kv0 = kt * 128;  // relative to the sequence's first key
   int Sq = p.Sq, Skv = p.Skv, q_base = 0, k_base = 0, bc = b;  // bc: batch coordinate in the tensors
@@ -431,6 +434,7 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int n_per = max((Sq + 127) / 128 - first_i, 0);
   int n_steps = n_per * p.group;
   const bool ragged_keys = kv0 + 128 > Skv;
+  const int i_full = (p.P > 0 && !ragged_keys) ? first_full_tile(kv0, p.P) : 0;  // query tiles before it are masked steps
   // boolean masks with a tile table: the (query head, query tile) steps this CTA runs, in shared memory
   uint32_t* s_list = reinterpret_cast<uint32_t*>(smem + Cfg::KV_SMEM_TILES + 256);
   const bool use_list = MASKW && p.mt != nullptr;
@@ -549,12 +553,15 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         // dV += P^T(i) dO_i in two parts (the first 32 queries of each warpgroup's P^T are signalled
         // early, so the tensor core starts while the other exponentials are computed), then S^T(i+1)
         // may overwrite the P^T columns
+        TR(3, s, 0, 0);
         ok = mbar_wait_warp(bar(B_PLO), s & 1, ctl, 14);
         if (!ok) break;
+        TR(3, s, 0, 1);
         tc_fence_after();
         issue_tmemA_k64<D>(lead, tDV, tST, sdesc_lo(do_s, TILE_BYTES_64), IDESC_ACC, s > 0, 0);
         ok = mbar_wait_warp(bar(B_P), s & 1, ctl, 20);
         if (!ok) break;
+        TR(3, s, 0, 2);
         tc_fence_after();
         issue_tmemA_k64<D>(lead, tDV, tST, sdesc_lo(do_s, TILE_BYTES_64), IDESC_ACC, s > 0, 1);
         if (more) {
@@ -563,9 +570,11 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           issue_kmajor_n128<D>(lead, tST, k_lo, sdesc_lo(q_n, 16), IDESC_S);
           umma_commit_lead(lead, bar(B_S));
         }
+        TR(3, s, 0, 3);
         // dK += dS^T(i) Q_i, then dP^T(i+1) may overwrite the dS^T columns
         ok = mbar_wait_warp(bar(B_DS), s & 1, ctl, 16);
         if (!ok) break;
+        TR(3, s, 0, 4);
         tc_fence_after();
         issue_tmemA_k128<D>(lead, tDK, tDP, sdesc_lo(q_s, TILE_BYTES_64), IDESC_ACC, s > 0);
         umma_commit_lead(lead, bar(B_QFREE + slot));
@@ -573,6 +582,7 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           issue_kmajor_n128<D>(lead, tDP, v_lo, sdesc_lo(do_n, 16), IDESC_S);
           umma_commit_lead(lead, bar(B_DP));
         }
+        TR(3, s, 0, 5);
       }
       if (ok) umma_commit_lead(lead, bar(B_ACC));
       umma_commit_lead(lead, bar(B_DRAIN));
@@ -621,7 +631,8 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
       if (n_steps > 0) mask_fetch(0);
     }
-    for (int s = 0; s < n_steps; ++s) {
+    StepWalk walk;
+    for (int s = 0; s < n_steps; ++s, walk.next(n_per)) {
       uint2 wcur[4];
       if constexpr (MASKW) {
 #pragma unroll
@@ -629,13 +640,15 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (s + 1 < n_steps) mask_fetch(s + 1);
       }
       const int slot = s % NSL;
-      const int i = tile_of(s);
+      const int i = use_list ? tile_of(s) : first_i + walk.rel;
       const int q0 = i * 128 + 64 * hq + col0;  // query of this thread's first column
       // masked step: some (key, query) pair of this tile pair is hidden, or keys are padded
-      const bool masked = ragged_keys || (p.P > 0 && key_limit(i * 128, p.P, Skv) < kv0 + 128);
-      ok = mbar_wait_warp(bar(B_QREADY + slot), (s / NSL) & 1, ctl, 17);  // stats of this step
-      if (ok) ok = mbar_wait_warp(bar(B_S), s & 1, ctl, 18);
+      const bool masked = ragged_keys || (p.P > 0 && i < i_full);
+      if ((warp & 3) == 0) TR(hq, s, 0, 0);
+      // (the step's statistics have landed too: S^T(i) was issued after the slot's copies had completed)
+      ok = mbar_wait_warp(bar(B_S), s & 1, ctl, 18);
       if (!ok) break;
+      if ((warp & 3) == 0) TR(hq, s, 0, 1);
       tc_fence_after();
       const float* st =
           reinterpret_cast<const float*>(smem + 2 * Cfg::TILE_BYTES + slot * Cfg::KV_SLOT_BYTES +
@@ -646,6 +659,7 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tmem_ld_16x256b_x8(tS, reinterpret_cast<uint32_t*>(sv));
         tmem_ld_16x256b_x8(tS + HALF, reinterpret_cast<uint32_t*>(sv + 16));
         tmem_wait_ld();
+        if ((warp & 3) == 0) TR(hq, s, 0, 2);
         uint32_t pk[32];
         // 16-bit P^T goes over the first 32 of the 64 columns this warp has just read (all its lanes),
         // in two parts of 32 queries (16 packed columns) each
@@ -655,12 +669,14 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           p_frag<BF16, true, 0>(sv, st, c2, q0, qmin, pr, pk);
         else
           p_frag<BF16, false, 0>(sv, st, c2, q0, qmin, pr, pk);
+        if ((warp & 3) == 0) TR(hq, s, 0, 7);
         tmem_st_16x128b_x4(tS, pk);
         tmem_st_16x128b_x4(tS + HALF, pk + 16);
         if constexpr (D == 128) {  // (at D = 64 the dV MMA is too short for the early start to pay)
           tmem_wait_st();
           tc_fence_before();
           mbar_arrive(bar(B_PLO));
+          if ((warp & 3) == 0) TR(hq, s, 0, 3);
         }
         if constexpr (MASKW)
           p_frag_bits<BF16, 4>(sv, st, c2, wcur, col0, pr, pk);
@@ -675,8 +691,10 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tc_fence_before();
       if constexpr (D != 128) mbar_arrive(bar(B_PLO));
       mbar_arrive(bar(B_P));
+      if ((warp & 3) == 0) TR(hq, s, 0, 4);
       ok = mbar_wait_warp(bar(B_DP), s & 1, ctl, 19);
       if (!ok) break;
+      if ((warp & 3) == 0) TR(hq, s, 0, 5);
       tc_fence_after();
       {
         float2 dp[32];
@@ -691,6 +709,7 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar(B_DS));
+      if ((warp & 3) == 0) TR(hq, s, 0, 6);
     }
     // ---- epilogue: warps 0-3 store dV, warps 4-7 store scale * dK ----
     const bool valid = key < Skv;
@@ -782,8 +801,8 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-  const int bh = blockIdx.x / p.n_q128;
-  const int t = blockIdx.x % p.n_q128;
+  int bh, t;
+  decode_tile(blockIdx.x, p.B * p.H, p.n_q128, bh, t);
   const int qt = (p.P > 0) ? (p.n_q128 - 1 - t) : t;
   const int b = bh / p.H, h = bh % p.H;
   const int row0 = qt * 128;  // relative to the sequence's first row

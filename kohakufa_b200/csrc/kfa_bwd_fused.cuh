@@ -194,9 +194,9 @@ kfa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-  // tile decode: head-major; under a causal mask the first key tiles see the most queries and come first
-  const int bh = blockIdx.x / p.n_k128;  // over batch x K / V heads
-  const int kt = blockIdx.x % p.n_k128;
+  // tile decode (groups of heads, tile-major inside); under a causal mask the first key tiles see the most queries and come first
+  int bh, kt;  // bh over batch x K / V heads
+  decode_tile(blockIdx.x, p.B * p.Hkv, p.n_k128, bh, kt);
   const int b = bh / p.Hkv, hk = bh % p.Hkv;
   const int kv0 = kt * 128;
   const int Sq = p.Sq, Skv = p.Skv;
@@ -204,6 +204,7 @@ kfa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const int n_per = max((Sq + 127) / 128 - first_i, 0);  // query tiles that see these keys
   const int n_steps = n_per * p.group;                   // ... for every query head of the group
   const bool ragged_keys = kv0 + 128 > Skv;
+  const int i_full = (p.P > 0 && !ragged_keys) ? first_full_tile(kv0, p.P) : 0;  // query tiles before it are masked steps
   // step s -> query head, query tile. Key tile kt starts its walk kt tiles in, so that the CTAs of a head
   // that run side by side add their dQ tiles to different places.
   const int rot = (n_per > 0) ? kt % n_per : 0;
@@ -213,6 +214,11 @@ kfa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     return first_i + r;
   };
   auto head_of = [&](int s) { return hk * p.group + s / n_per; };
+  auto tile_at = [&](const StepWalk& w) {  // the same without a division, for the loops that walk step by step
+    int r = w.rel + rot;
+    if (r >= n_per) r -= n_per;
+    return first_i + r;
+  };
 
   if (tid == 0) {
     mbar_init(bar(B_KV), 1);
@@ -414,9 +420,10 @@ kfa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     const int r_in = tid & 127;
     const uint32_t tDQ = tmem + Cfg::TM_DQ + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     bool ok = true;
-    for (int s = 0; s < n_steps; ++s) {
-      const int i = tile_of(s);
-      const int head = head_of(s);
+    StepWalk walk;
+    for (int s = 0; s < n_steps; ++s, walk.next(n_per)) {
+      const int i = tile_at(walk);
+      const int head = hk * p.group + walk.g;
       ok = mbar_wait_warp(bar(B_DQ), s & 1, ctl, 43);
       if (!ok) break;
       tc_fence_after();
@@ -501,11 +508,12 @@ kfa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     const uint32_t s_row0 = sDS + hq * TILE_BYTES_64 + static_cast<uint32_t>((warp & 3) * 32 + (lane >> 2)) * 128u;
     const float2 c2 = make_float2(p.c, p.c);
     bool ok = true;
-    for (int s = 0; s < n_steps; ++s) {
-      const int i = tile_of(s);
+    StepWalk walk;
+    for (int s = 0; s < n_steps; ++s, walk.next(n_per)) {
+      const int i = tile_at(walk);
       const int q0 = i * 128 + 64 * hq + col0;  // query of this thread's first column
       // masked step: some (key, query) pair of this tile pair is hidden, or keys are padded
-      const bool masked = ragged_keys || (p.P > 0 && key_limit(i * 128, p.P, Skv) < kv0 + 128);
+      const bool masked = ragged_keys || (p.P > 0 && i < i_full);
       const float* st = ml_smem + (s & 1) * (Cfg::ML_BYTES / 4) + 64 * hq + col0;  // -m here, -log2 l 128 floats on
       ok = mbar_wait_warp(bar(B_MLREADY + (s & 1)), (s >> 1) & 1, ctl, 50);
       if (ok) ok = mbar_wait_warp(bar(B_S), s & 1, ctl, 44);

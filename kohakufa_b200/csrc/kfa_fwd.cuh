@@ -122,6 +122,41 @@ __device__ long long kfa_trace[6][64][2][8];
 #define TR(role, j, part, ev) do {} while (0)
 #endif
 
+// First 128-row query tile all of whose rows see every key of the 128-key tile at kv0 (block-causal frame
+// P > 0, the key tile complete): tile i is fully visible iff key_limit(128 i) >= kv0 + 128, which is monotone
+// in i. Computed once per CTA, so that the key-major loops do no division per step.
+__device__ __forceinline__ int first_full_tile(int kv0, int P) {
+  const long long t = (static_cast<long long>(kv0) + 128 + P - 1) / P - 1;
+  return static_cast<int>((t * P + 127) / 128);
+}
+
+// Launch order of the main kernels: the (batch, head) pairs in groups of 8; inside a group tile-major. Under a
+// causal mask every head's tiles run from the heaviest to the lightest, so a group's heavy tiles all start
+// before its light ones and the launch ends on light tiles (head after head, the last wave would hold
+// heavy tiles of the last heads: 4 % of the forward's time at 128 heads, 30 % at 16), while the CTAs that
+// run side by side still share the K / V (or Q / dO) of a few heads in L2.
+__device__ __forceinline__ void decode_tile(int idx, int n_bh, int n_tiles, int& bh, int& t) {
+  constexpr int G = 8;
+  const int per_group = G * n_tiles;
+  const int g = idx / per_group;
+  const int r = idx - g * per_group;
+  const int gs = min(G, n_bh - g * G);
+  t = r / gs;
+  bh = g * G + (r - t * gs);
+}
+
+// Walk over the steps of a key-major CTA without a division per step: query tile (relative to the first
+// one that sees the keys) and query head of the K / V head's group.
+struct StepWalk {
+  int rel = 0, g = 0;
+  __device__ __forceinline__ void next(int n_per) {
+    if (++rel == n_per) {
+      rel = 0;
+      ++g;
+    }
+  }
+};
+
 template <int D, bool BF16, bool MASKW>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -164,9 +199,9 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   if (warp == 8) TR(2, 0, 0, 4);
 #endif
 
-  // ---- tile decode: head-major, heaviest query tile of a head first when causal ----
-  const int bh = blockIdx.x / p.n_q_tiles;
-  const int t = blockIdx.x % p.n_q_tiles;
+  // ---- tile decode (groups of heads, tile-major inside), heaviest query tile first when causal ----
+  int bh, t;
+  decode_tile(blockIdx.x, p.B * p.H, p.n_q_tiles, bh, t);
   const int q_tile = (p.P > 0) ? (p.n_q_tiles - 1 - t) : t;
   const int b = bh / p.H;
   const int h = bh % p.H;
