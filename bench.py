@@ -244,6 +244,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=None, help="override the configuration's batch (profiling a small case)")
     ap.add_argument("--heads", type=int, default=None, help="override the configuration's head count")
+    ap.add_argument("--head-dim", type=int, default=None, help="override the configuration's head dim (a multiple of 16 up to 128)")
     ap.add_argument("--backward", default=None, choices=["auto", "fused", "split"],
                     help="backward implementation (default: the package's, 'auto' unless KFA_BACKWARD says otherwise)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -255,10 +256,11 @@ def main():
     from kohakufa_b200 import workloads
 
     cfg = workloads.CONFIGS[args.config]
-    if args.batch or args.heads:
+    if args.batch or args.heads or args.head_dim:
         import dataclasses
 
-        cfg = dataclasses.replace(cfg, batch=args.batch or cfg.batch, heads=args.heads or cfg.heads)
+        cfg = dataclasses.replace(cfg, batch=args.batch or cfg.batch, heads=args.heads or cfg.heads,
+                                  dim=args.head_dim or cfg.dim)
     if args.impl == "reference":
         run_reference(args, cfg)
         return

@@ -9,7 +9,7 @@
  *   - Every tensor is a [B, H, S, D] view described by KfaTensor4: element strides, last
  *     dimension contiguous, every other stride a multiple of 8 elements (16 bytes), base
  *     pointer 16-byte aligned (the reference's rule, src/kohakufa/sm100/op.py:53-55).
- *   - 16-bit data is fp16 (KFA_F16) or bf16 (KFA_BF16). D is 64 or 128. H of q is a multiple of
+ *   - 16-bit data is fp16 (KFA_F16) or bf16 (KFA_BF16). D is a multiple of 16 up to 128 (the fused backward: 64 or 128). H of q is a multiple of
  *     H of k / v (grouped-query attention: query head h uses K / V head h / (H / Hkv)).
  *   - block = 0: dense. block = P > 0: key c is visible to query r iff c / P <= r / P
  *     (top-left aligned; P = 1 is token-causal) (tests/reference.py:6-12).

@@ -66,7 +66,8 @@ int check_tensor(const KfaTensor4* t, const char* name) {
   return KFA_OK;
 }
 
-// 4-D tiled map over a [B, H, S, D] view: dims (D, S, H, B), box (64, 128, 1, 1), 128-byte swizzle,
+// 4-D tiled map over a [B, H, S, D] view: dims (D, S, H, B), box (C, 128, 1, 1) with C the chunk width of the
+// head dim (64, 32 or 16 columns) and the swizzle that spans the box's row (128, 64 or 32 bytes);
 // out-of-range rows read as zeros.
 int make_map(const KfaTensor4* t, int dtype, CUtensorMap* map, const char* name) {
   EncodeFn enc = encode_fn();
@@ -79,10 +80,13 @@ int make_map(const KfaTensor4* t, int dtype, CUtensorMap* map, const char* name)
     return static_cast<cuuint64_t>(s) * 2;
   };
   cuuint64_t strides[3] = {st(2), st(1), st(0)};
-  cuuint32_t box[4] = {64, 128, 1, 1};
+  const int chunk = kfa::chunk_cols(static_cast<int>(D));
+  cuuint32_t box[4] = {static_cast<cuuint32_t>(chunk), 128, 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUtensorMapSwizzle swizzle =
+      chunk == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : (chunk == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
   CUresult r = enc(map, dtype == KFA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
-                   t->ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   t->ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(KFA_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", name, (int)r);
   return KFA_OK;
@@ -93,7 +97,7 @@ int check_qkv(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, int
   if ((rc = check_tensor(q, "q")) || (rc = check_tensor(k, "k")) || (rc = check_tensor(v, "v"))) return rc;
   if (dtype != KFA_F16 && dtype != KFA_BF16) return fail(KFA_ERR_ARG, "dtype %d: KFA_F16 or KFA_BF16", dtype);
   const int64_t D = q->shape[3];
-  if (D != 64 && D != 128) return fail(KFA_ERR_ARG, "head_dim %lld: 64 or 128", (long long)D);
+  if (D < 16 || D > 128 || D % 16) return fail(KFA_ERR_ARG, "head_dim %lld: a multiple of 16 up to 128", (long long)D);
   for (int i = 0; i < 4; ++i)
     if (k->shape[i] != v->shape[i]) return fail(KFA_ERR_ARG, "k and v shapes differ");
   if (k->shape[0] != q->shape[0] || k->shape[3] != D) return fail(KFA_ERR_ARG, "k / v batch or head_dim differ from q");
@@ -188,24 +192,41 @@ int launch_dq(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& m
   return p.mw ? launch_dq_t<D, BF16, true>(mq, mk, mv, mdo, p, s) : launch_dq_t<D, BF16, false>(mq, mk, mv, mdo, p, s);
 }
 
+// Runs `call` with KD = the head dim and KB = (dtype is bf16) as compile-time constants.
+#define KFA_DISPATCH_D(KD_, dtype_, call) \
+  case KD_: {                             \
+    constexpr int KD = KD_;               \
+    if ((dtype_) == KFA_F16) {            \
+      constexpr bool KB = false;          \
+      return call;                        \
+    } else {                              \
+      constexpr bool KB = true;           \
+      return call;                        \
+    }                                     \
+  }
+// The fused backward exists for head dims 64 and 128.
+#define KFA_DISPATCH_FUSED(D_, dtype_, call)               \
+  do {                                                     \
+    switch (D_) {                                          \
+      KFA_DISPATCH_D(64, dtype_, call)                     \
+      KFA_DISPATCH_D(128, dtype_, call)                    \
+      default:                                             \
+        return fail(KFA_ERR_ARG, "fused backward: head_dim %d: 64 or 128", (int)(D_)); \
+    }                                                      \
+  } while (0)
 #define KFA_DISPATCH(D_, dtype_, call)                     \
   do {                                                     \
-    if ((D_) == 64 && (dtype_) == KFA_F16) {               \
-      constexpr int KD = 64;                               \
-      constexpr bool KB = false;                           \
-      return call;                                         \
-    } else if ((D_) == 64) {                               \
-      constexpr int KD = 64;                               \
-      constexpr bool KB = true;                            \
-      return call;                                         \
-    } else if ((dtype_) == KFA_F16) {                      \
-      constexpr int KD = 128;                              \
-      constexpr bool KB = false;                           \
-      return call;                                         \
-    } else {                                               \
-      constexpr int KD = 128;                              \
-      constexpr bool KB = true;                            \
-      return call;                                         \
+    switch (D_) {                                          \
+      KFA_DISPATCH_D(16, dtype_, call)                     \
+      KFA_DISPATCH_D(32, dtype_, call)                     \
+      KFA_DISPATCH_D(48, dtype_, call)                     \
+      KFA_DISPATCH_D(64, dtype_, call)                     \
+      KFA_DISPATCH_D(80, dtype_, call)                     \
+      KFA_DISPATCH_D(96, dtype_, call)                     \
+      KFA_DISPATCH_D(112, dtype_, call)                    \
+      KFA_DISPATCH_D(128, dtype_, call)                    \
+      default:                                             \
+        return fail(KFA_ERR_ARG, "head_dim %d: a multiple of 16 up to 128", (int)(D_)); \
     }                                                      \
   } while (0)
 
@@ -363,7 +384,8 @@ int prepare_impl(const KfaTensor4* out, const KfaTensor4* dout, const float* lse
   if (!lse || !stats) return fail(KFA_ERR_ARG, "lse / stats: null pointer");
   if (dtype != KFA_F16 && dtype != KFA_BF16) return fail(KFA_ERR_ARG, "dtype %d", dtype);
   const int64_t D = out->shape[3];
-  if (D != 64 && D != 128) return fail(KFA_ERR_ARG, "head_dim %lld: 64 or 128", (long long)D);
+  if (D < 16 || D > 128 || D % 16) return fail(KFA_ERR_ARG, "head_dim %lld: a multiple of 16 up to 128", (long long)D);
+  if (dq_acc && D != 64 && D != 128) return fail(KFA_ERR_ARG, "fused backward: head_dim %lld: 64 or 128", (long long)D);
   kfa::PrepParams p;
   std::memset(&p, 0, sizeof(p));
   p.o = out->ptr;
@@ -478,7 +500,7 @@ int convert_impl(const float* dq_acc, const KfaTensor4* dq, float scale, int dty
   if (D != 64 && D != 128) return fail(KFA_ERR_ARG, "head_dim %lld: 64 or 128", (long long)D);
   if (dq->shape[0] * dq->shape[1] > 65535) return fail(KFA_ERR_ARG, "B * H > 65535");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  KFA_DISPATCH(D, dtype, (launch_dq_convert<KD, KB>(dq_acc, dq, scale, dev_status, s)));
+  KFA_DISPATCH_FUSED(D, dtype, (launch_dq_convert<KD, KB>(dq_acc, dq, scale, dev_status, s)));
 }
 
 int fused_impl(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const KfaTensor4* dout,
@@ -505,7 +527,7 @@ int fused_impl(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, co
   p.dv_sh = dv->stride[1];
   p.dv_ss = dv->stride[2];
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  KFA_DISPATCH(q->shape[3], dtype, (launch_fused<KD, KB>(mq, mk, mv, mdo, p, dq_acc, s)));
+  KFA_DISPATCH_FUSED(q->shape[3], dtype, (launch_fused<KD, KB>(mq, mk, mv, mdo, p, dq_acc, s)));
 }
 
 }  // namespace

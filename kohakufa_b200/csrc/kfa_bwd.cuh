@@ -101,12 +101,13 @@ struct PrepParams {
 };
 
 // ---------------------------------------------------------------------------------------
-// prepare: HBM-bound; D / 8 lanes per row, 16-byte loads.
+// prepare: HBM-bound; D / 8 lanes per row (rounded up to a power of two), 16-byte loads.
 // ---------------------------------------------------------------------------------------
 template <int D, bool BF16>
 __global__ void __launch_bounds__(128) kfa_bwd_prepare_kernel(const PrepParams p) {
-  constexpr int LPR = D / 8;       // lanes per row
-  constexpr int RPW = 32 / LPR;    // rows per warp pass
+  constexpr int VECS = D / 8;                                                      // 16-byte pieces of a row
+  constexpr int LPR = VECS <= 2 ? 2 : (VECS <= 4 ? 4 : (VECS <= 8 ? 8 : 16));      // lanes per row (a power of two)
+  constexpr int RPW = 32 / LPR;                                                    // rows per warp pass
   const int tile = blockIdx.x;
   const int bh = blockIdx.y;
   const int b = bh / p.H, h = bh % p.H;
@@ -132,7 +133,7 @@ __global__ void __launch_bounds__(128) kfa_bwd_prepare_kernel(const PrepParams p
     const int r_in = r0 + sub;
     const int row = tile * 128 + r_in;
     float acc = 0.f;
-    if (row < Sq) {
+    if (row < Sq && vec < VECS) {
       const uint4 ov = *reinterpret_cast<const uint4*>(ob + 2 * (row * p.o_ss + vec * 8));
       const uint4 gv = *reinterpret_cast<const uint4*>(gb + 2 * (row * p.do_ss + vec * 8));
       const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w};
@@ -165,12 +166,14 @@ constexpr int STATS_BYTES = 3 * 128 * 4;
 
 template <int D>
 struct BwdCfg {
-  static constexpr int CHUNKS = D / 64;
-  static constexpr int TILE_BYTES = CHUNKS * TILE_BYTES_64;
+  static constexpr int CHUNK_COLS = chunk_cols(D);
+  static constexpr int CHUNKS = D / CHUNK_COLS;
+  static constexpr int CHUNK_BYTES = chunk_bytes(D);
+  static constexpr int TILE_BYTES = CHUNKS * CHUNK_BYTES;  // 128 rows x D columns
   static constexpr uint32_t TMEM_COLS = 512;
   static constexpr uint32_t TM_S = 0, TM_DP = 128, TM_ACC0 = 256, TM_ACC1 = 256 + D;
   // dK/dV kernel: K, V resident; ring of (Q_i, dO_i, stats_i) slots.
-  static constexpr int KV_SLOTS = (D == 128) ? 2 : 3;
+  static constexpr int KV_SLOTS = (D > 96) ? 2 : 3;
   static constexpr int KV_SLOT_BYTES = 2 * TILE_BYTES + 2048;  // stats padded to keep 1 KB alignment
   static constexpr int KV_SMEM_TILES = 2 * TILE_BYTES + KV_SLOTS * KV_SLOT_BYTES;
   static constexpr int KV_SMEM_BYTES = KV_SMEM_TILES + 1024 + 256;
@@ -180,25 +183,25 @@ struct BwdCfg {
   // later, by dQ(j); V_j only by dP(j): three K buffers and two V buffers let the copy of tile j + 2
   // start a whole step before it is needed (with K and V sharing two slots it could start only when
   // dQ(j) had retired, and the tensor core waited for the copy at every step).
-  static constexpr int NK = (D == 128) ? 3 : 4;
-  static constexpr int NV = (D == 128) ? 2 : 3;
+  static constexpr int NK = (D > 96) ? 3 : 4;
+  static constexpr int NV = (D > 96) ? 2 : 3;
   static constexpr int Q_SMEM_TILES = (2 + NK + NV) * TILE_BYTES;
   static constexpr int Q_SMEM_BYTES = Q_SMEM_TILES + 1024 + 256;
-  static constexpr int Q_LIST_CAP = (D == 128) ? 768 : 1024;  // key tiles a masked CTA can list (what fits)
+  static constexpr int Q_LIST_CAP = (D > 96) ? 768 : 1024;  // key tiles a masked CTA can list (what fits)
   static constexpr int Q_SMEM_BYTES_LIST = Q_SMEM_BYTES + 2 * Q_LIST_CAP;
 };
 
 // Issue helpers for the MMA warp (converged; `lead` is true in the one lane that issues). Operand
-// tiles are 128B-swizzled [rows][64] boxes, D / 64 of them 16 KB apart; descriptors are passed as
-// their low words (see sdesc_lo).
+// tiles are swizzled [128 rows][C] boxes, D / C of them one after the other (C = chunk_cols(D));
+// descriptors are passed as their low words (see sdesc_lo).
 // acc[128 x 128] = A[128 rows, D] * B[128 rows, D]^T, contraction over D.
 template <int D>
 __device__ __forceinline__ void issue_kmajor_n128(bool lead, uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo,
                                                   uint32_t idesc) {
 #pragma unroll
   for (int kk = 0; kk < D / 16; ++kk) {
-    const uint32_t off = ((kk >> 2) * TILE_BYTES_64 + (kk & 3) * 32) >> 4;
-    umma_ss_lead(lead, d_tmem, a_lo + off, b_lo + off, idesc, kk > 0 ? 1u : 0u);
+    const uint32_t off = kstep_bytes(D, kk) >> 4;
+    umma_ss_lead(lead, d_tmem, a_lo + off, b_lo + off, idesc, kk > 0 ? 1u : 0u, sdesc_hi_for(D));
   }
 }
 // acc[128 x D] (+)= A16[128 x 128] * B[128 rows, D], contraction over B's rows (MN-major B, leading
@@ -209,8 +212,8 @@ __device__ __forceinline__ void issue_tmemA_k128(bool lead, uint32_t d_tmem, uin
                                                  uint32_t idesc, bool acc) {
 #pragma unroll
   for (int kk = 0; kk < 8; ++kk)
-    umma_ts_lead(lead, d_tmem, a_tmem + (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8), b_lo + ((kk * 16 * 128) >> 4), idesc,
-                 (acc || kk > 0) ? 1u : 0u);
+    umma_ts_lead(lead, d_tmem, a_tmem + (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8), b_lo + (kstep_rows_bytes(D, kk) >> 4), idesc,
+                 (acc || kk > 0) ? 1u : 0u, sdesc_hi_for(D));
 }
 
 // The same for half of the contraction: k-steps 2 * part, 2 * part + 1 of each warpgroup's piece
@@ -221,21 +224,22 @@ __device__ __forceinline__ void issue_tmemA_k64(bool lead, uint32_t d_tmem, uint
 #pragma unroll
   for (int x = 0; x < 4; ++x) {
     const int kk = (x >> 1) * 4 + 2 * part + (x & 1);
-    umma_ts_lead(lead, d_tmem, a_tmem + (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8), b_lo + ((kk * 16 * 128) >> 4), idesc,
-                 (acc || x > 0 || part > 0) ? 1u : 0u);
+    umma_ts_lead(lead, d_tmem, a_tmem + (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8), b_lo + (kstep_rows_bytes(D, kk) >> 4), idesc,
+                 (acc || x > 0 || part > 0) ? 1u : 0u, sdesc_hi_for(D));
   }
 }
 
 // Stores (add = false) or adds (add = true) a row of an fp32 accumulator times mul to fp32 memory.
+template <int W = 32>
 __device__ __forceinline__ void store_acc_row_f32(uint32_t taddr, int col0, int ncols, float mul, float* grow,
                                                   bool valid, bool add) {
-  for (int cc = col0; cc < col0 + ncols; cc += 32) {
-    float o[32];
-    tmem_ld32(taddr + cc, reinterpret_cast<uint32_t*>(o));
+  for (int cc = col0; cc < col0 + ncols; cc += W) {
+    float o[W];
+    tmem_ldw<W>(taddr + cc, reinterpret_cast<uint32_t*>(o));
     tmem_wait_ld();
     if (valid) {
 #pragma unroll
-      for (int i = 0; i < 32; i += 4) {
+      for (int i = 0; i < W; i += 4) {
         float4 w = make_float4(o[i] * mul, o[i + 1] * mul, o[i + 2] * mul, o[i + 3] * mul);
         if (add) {
           const float4 old = *reinterpret_cast<const float4*>(grow + cc + i);
@@ -251,16 +255,16 @@ __device__ __forceinline__ void store_acc_row_f32(uint32_t taddr, int col0, int 
 }
 
 // Writes a row of an fp32 accumulator (TMEM columns [col0, col0 + ncols)) times mul as 16-bit.
-template <bool BF16>
+template <bool BF16, int W = 32>
 __device__ __forceinline__ void store_acc_row(uint32_t taddr, int col0, int ncols, float mul, uint8_t* grow,
                                               bool valid) {
-  for (int cc = col0; cc < col0 + ncols; cc += 32) {
-    float o[32];
-    tmem_ld32(taddr + cc, reinterpret_cast<uint32_t*>(o));
+  for (int cc = col0; cc < col0 + ncols; cc += W) {
+    float o[W];
+    tmem_ldw<W>(taddr + cc, reinterpret_cast<uint32_t*>(o));
     tmem_wait_ld();
     if (valid) {
 #pragma unroll
-      for (int i = 0; i < 32; i += 8) {
+      for (int i = 0; i < W; i += 8) {
         uint4 w;
         w.x = pack16<BF16>(o[i] * mul, o[i + 1] * mul);
         w.y = pack16<BF16>(o[i + 2] * mul, o[i + 3] * mul);
@@ -496,8 +500,8 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       prefetch_tensormap(&tmDO);
       mbar_expect_tx(bar(B_KV), 2 * Cfg::TILE_BYTES);
       for (int ch = 0; ch < CH; ++ch) {
-        tma_load_4d(sK + ch * TILE_BYTES_64, &tmK, bar(B_KV), ch * 64, k_base + kv0, hk, bc);
-        tma_load_4d(sV + ch * TILE_BYTES_64, &tmV, bar(B_KV), ch * 64, k_base + kv0, hk, bc);
+        tma_load_4d(sK + ch * Cfg::CHUNK_BYTES, &tmK, bar(B_KV), ch * Cfg::CHUNK_COLS, k_base + kv0, hk, bc);
+        tma_load_4d(sV + ch * Cfg::CHUNK_BYTES, &tmV, bar(B_KV), ch * Cfg::CHUNK_COLS, k_base + kv0, hk, bc);
       }
       bool ok = true;
       int issued = 0;
@@ -510,8 +514,8 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const uint32_t base = sSlot + slot * Cfg::KV_SLOT_BYTES;
         mbar_expect_tx(bar(B_QREADY + slot), 2 * Cfg::TILE_BYTES + STATS_BYTES);
         for (int ch = 0; ch < CH; ++ch) {
-          tma_load_4d(base + ch * TILE_BYTES_64, &tmQ, bar(B_QREADY + slot), ch * 64, q_base + i * 128, head, bc);
-          tma_load_4d(base + Cfg::TILE_BYTES + ch * TILE_BYTES_64, &tmDO, bar(B_QREADY + slot), ch * 64,
+          tma_load_4d(base + ch * Cfg::CHUNK_BYTES, &tmQ, bar(B_QREADY + slot), ch * Cfg::CHUNK_COLS, q_base + i * 128, head, bc);
+          tma_load_4d(base + Cfg::TILE_BYTES + ch * Cfg::CHUNK_BYTES, &tmDO, bar(B_QREADY + slot), ch * Cfg::CHUNK_COLS,
                       q_base + i * 128, head, bc);
         }
         bulk_load(base + 2 * Cfg::TILE_BYTES,
@@ -558,12 +562,12 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (!ok) break;
         TR(3, s, 0, 1);
         tc_fence_after();
-        issue_tmemA_k64<D>(lead, tDV, tST, sdesc_lo(do_s, TILE_BYTES_64), IDESC_ACC, s > 0, 0);
+        issue_tmemA_k64<D>(lead, tDV, tST, sdesc_lo(do_s, Cfg::CHUNK_BYTES), IDESC_ACC, s > 0, 0);
         ok = mbar_wait_warp(bar(B_P), s & 1, ctl, 20);
         if (!ok) break;
         TR(3, s, 0, 2);
         tc_fence_after();
-        issue_tmemA_k64<D>(lead, tDV, tST, sdesc_lo(do_s, TILE_BYTES_64), IDESC_ACC, s > 0, 1);
+        issue_tmemA_k64<D>(lead, tDV, tST, sdesc_lo(do_s, Cfg::CHUNK_BYTES), IDESC_ACC, s > 0, 1);
         if (more) {
           ok = mbar_wait_warp(bar(B_QREADY + nslot), ((s + 1) / NSL) & 1, ctl, 15);
           if (!ok) break;
@@ -576,7 +580,7 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (!ok) break;
         TR(3, s, 0, 4);
         tc_fence_after();
-        issue_tmemA_k128<D>(lead, tDK, tDP, sdesc_lo(q_s, TILE_BYTES_64), IDESC_ACC, s > 0);
+        issue_tmemA_k128<D>(lead, tDK, tDP, sdesc_lo(q_s, Cfg::CHUNK_BYTES), IDESC_ACC, s > 0);
         umma_commit_lead(lead, bar(B_QFREE + slot));
         if (more) {
           issue_kmajor_n128<D>(lead, tDP, v_lo, sdesc_lo(do_n, 16), IDESC_S);
@@ -672,7 +676,7 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if ((warp & 3) == 0) TR(hq, s, 0, 7);
         tmem_st_16x128b_x4(tS, pk);
         tmem_st_16x128b_x4(tS + HALF, pk + 16);
-        if constexpr (D == 128) {  // (at D = 64 the dV MMA is too short for the early start to pay)
+        if constexpr (D > 64) {  // (at D <= 64 the dV MMA is too short for the early start to pay)
           tmem_wait_st();
           tc_fence_before();
           mbar_arrive(bar(B_PLO));
@@ -689,7 +693,7 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
       tmem_wait_st();
       tc_fence_before();
-      if constexpr (D != 128) mbar_arrive(bar(B_PLO));
+      if constexpr (D <= 64) mbar_arrive(bar(B_PLO));
       mbar_arrive(bar(B_P));
       if ((warp & 3) == 0) TR(hq, s, 0, 4);
       ok = mbar_wait_warp(bar(B_DP), s & 1, ctl, 19);
@@ -735,9 +739,9 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tc_fence_after();
         const uint32_t tacc = tmem + (hq ? Cfg::TM_ACC1 : Cfg::TM_ACC0) + lane_base;
         if (p.acc_mode == 0)
-          store_acc_row<BF16>(tacc, 0, D, hq ? p.scale : 1.0f, grow, valid);
+          store_acc_row<BF16, col_step(D)>(tacc, 0, D, hq ? p.scale : 1.0f, grow, valid);
         else
-          store_acc_row_f32(tacc, 0, D, hq ? p.scale : 1.0f, grow32, valid, p.acc_mode == 2);
+          store_acc_row_f32<col_step(D)>(tacc, 0, D, hq ? p.scale : 1.0f, grow32, valid, p.acc_mode == 2);
       }
     }
   }
@@ -881,8 +885,8 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       prefetch_tensormap(&tmDO);
       mbar_expect_tx(bar(B_Q), 2 * Cfg::TILE_BYTES);
       for (int ch = 0; ch < CH; ++ch) {
-        tma_load_4d(sQ + ch * TILE_BYTES_64, &tmQ, bar(B_Q), ch * 64, q_base + row0, h, bc);
-        tma_load_4d(sDO + ch * TILE_BYTES_64, &tmDO, bar(B_Q), ch * 64, q_base + row0, h, bc);
+        tma_load_4d(sQ + ch * Cfg::CHUNK_BYTES, &tmQ, bar(B_Q), ch * Cfg::CHUNK_COLS, q_base + row0, h, bc);
+        tma_load_4d(sDO + ch * Cfg::CHUNK_BYTES, &tmDO, bar(B_Q), ch * Cfg::CHUNK_COLS, q_base + row0, h, bc);
       }
       bool ok = true;
       int issued_k = 0, issued_v = 0;
@@ -892,14 +896,14 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         if (!ok) break;
         mbar_expect_tx(bar(B_KREADY + ks), Cfg::TILE_BYTES);
         for (int ch = 0; ch < CH; ++ch)
-          tma_load_4d(sKr + ks * Cfg::TILE_BYTES + ch * TILE_BYTES_64, &tmK, bar(B_KREADY + ks), ch * 64,
+          tma_load_4d(sKr + ks * Cfg::TILE_BYTES + ch * Cfg::CHUNK_BYTES, &tmK, bar(B_KREADY + ks), ch * Cfg::CHUNK_COLS,
                       k_base + tile_of(j) * 128, h / p.group, bc);
         issued_k = j + 1;
         if (j >= NV) ok = mbar_wait(bar(B_VFREE + vs), (j / NV - 1) & 1, ctl, 52);
         if (!ok) break;
         mbar_expect_tx(bar(B_VREADY + vs), Cfg::TILE_BYTES);
         for (int ch = 0; ch < CH; ++ch)
-          tma_load_4d(sVr + vs * Cfg::TILE_BYTES + ch * TILE_BYTES_64, &tmV, bar(B_VREADY + vs), ch * 64,
+          tma_load_4d(sVr + vs * Cfg::TILE_BYTES + ch * Cfg::CHUNK_BYTES, &tmV, bar(B_VREADY + vs), ch * Cfg::CHUNK_COLS,
                       k_base + tile_of(j) * 128, h / p.group, bc);
         issued_v = j + 1;
       }
@@ -947,7 +951,7 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         ok = mbar_wait_warp(bar(B_DS), j & 1, ctl, 58);
         if (!ok) break;
         tc_fence_after();
-        issue_tmemA_k128<D>(lead, tDQ, tDP, sdesc_lo(k_s, TILE_BYTES_64), IDESC_ACC, j > 0);
+        issue_tmemA_k128<D>(lead, tDQ, tDP, sdesc_lo(k_s, Cfg::CHUNK_BYTES), IDESC_ACC, j > 0);
         umma_commit_lead(lead, bar(B_KFREE + j % NK));
         if (more) {
           ok = mbar_wait_warp(bar(B_VREADY + nv), ((j + 1) / NV) & 1, ctl, 59);
@@ -1033,14 +1037,17 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     ok = mbar_wait_warp(bar(B_ACC), 0, ctl, 62) && ok;
     if (ok) {
       tc_fence_after();
+      // the two warpgroups share the row's D columns, split at a multiple of 16
+      constexpr int SPLIT = ((D / 2 + 15) / 16) * 16;
+      constexpr int W = (SPLIT % 32 == 0 && (D - SPLIT) % 32 == 0) ? 32 : 16;
+      const int c0 = hk ? SPLIT : 0, nc = hk ? D - SPLIT : SPLIT;
       if (p.acc_mode == 0) {
         uint8_t* grow = reinterpret_cast<uint8_t*>(p.dq) +
                         2 * (bc * p.dq_sb + h * p.dq_sh + static_cast<long long>(q_base + row) * p.dq_ss);
-        store_acc_row<BF16>(tmem + Cfg::TM_ACC0 + lane_base, hk * (D / 2), D / 2, p.scale, grow, row < Sq);
+        store_acc_row<BF16, W>(tmem + Cfg::TM_ACC0 + lane_base, c0, nc, p.scale, grow, row < Sq);
       } else {
         float* grow32 = p.dq32 + (static_cast<long long>(b) * p.H + h) * p.dq32_sh + static_cast<long long>(row) * D;
-        store_acc_row_f32(tmem + Cfg::TM_ACC0 + lane_base, hk * (D / 2), D / 2, p.scale, grow32, row < Sq,
-                          p.acc_mode == 2);
+        store_acc_row_f32<W>(tmem + Cfg::TM_ACC0 + lane_base, c0, nc, p.scale, grow32, row < Sq, p.acc_mode == 2);
       }
     }
   }

@@ -94,12 +94,14 @@ constexpr int TILE_BYTES_64 = 128 * 64 * 2;  // one 128-row x 64-column 16-bit b
 
 template <int D>
 struct FwdCfg {
-  static constexpr int CHUNKS = D / 64;
-  static constexpr int TILE_BYTES = CHUNKS * TILE_BYTES_64;
+  static constexpr int CHUNK_COLS = chunk_cols(D);
+  static constexpr int CHUNKS = D / CHUNK_COLS;
+  static constexpr int CHUNK_BYTES = chunk_bytes(D);
+  static constexpr int TILE_BYTES = CHUNKS * CHUNK_BYTES;  // 128 rows x D columns
 #ifdef KFA_FWD_STAGES_128
-  static constexpr int STAGES = (D == 128) ? KFA_FWD_STAGES_128 : 6;
+  static constexpr int STAGES = (D > 96) ? KFA_FWD_STAGES_128 : 6;
 #else
-  static constexpr int STAGES = (D == 128) ? 4 : 6;
+  static constexpr int STAGES = (D > 96) ? 4 : 6;  // (96: 2 x 24 + 6 x 24 KB)
 #endif
   static constexpr int SMEM_TILES = 2 * TILE_BYTES + STAGES * TILE_BYTES;
   static constexpr int SMEM_BYTES = SMEM_TILES + 1024 /*alignment slack*/ + FWD_BAR_BYTES + FWD_HANDOVER_BYTES;
@@ -311,7 +313,7 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         if (n_tiles[hf] == 0) continue;
         mbar_expect_tx(bar(B_QREADY + hf), Cfg::TILE_BYTES);
         for (int ch = 0; ch < CH; ++ch)
-          tma_load_4d(sQ + (hf * CH + ch) * TILE_BYTES_64, &tmQ, bar(B_QREADY + hf), ch * 64,
+          tma_load_4d(sQ + (hf * CH + ch) * Cfg::CHUNK_BYTES, &tmQ, bar(B_QREADY + hf), ch * Cfg::CHUNK_COLS,
                       q_base + row0 + 128 * hf, h, bc);
       }
       int armed[NS];  // last use index armed per stage (for the drain on abort)
@@ -326,7 +328,7 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         mbar_expect_tx(bar(B_KVREADY + stage), Cfg::TILE_BYTES);
         const CUtensorMap* map = (idx & 1) ? &tmV : &tmK;
         for (int ch = 0; ch < CH; ++ch)
-          tma_load_4d(sKV + (stage * CH + ch) * TILE_BYTES_64, map, bar(B_KVREADY + stage), ch * 64,
+          tma_load_4d(sKV + (stage * CH + ch) * Cfg::CHUNK_BYTES, map, bar(B_KVREADY + stage), ch * Cfg::CHUNK_COLS,
                       k_base + j * 128, h / p.group, bc);
         armed[stage] = use;
       }
@@ -350,6 +352,7 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       const bool lead = elect_one();
       constexpr uint32_t IDESC_S = make_idesc(BF16, false, 128, FWD_PART_KEYS);
       constexpr uint32_t IDESC_O = make_idesc(BF16, true, 128, D);
+      constexpr uint32_t HI = sdesc_hi_for(D);
       const uint32_t tmS = tmem + (hf ? Cfg::TM_S1 : Cfg::TM_S0);
       const uint32_t tmO = tmem + (hf ? Cfg::TM_O1 : Cfg::TM_O0);
       const uint32_t q_lo = sdesc_lo(sQ + hf * Cfg::TILE_BYTES, 16);
@@ -358,21 +361,21 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 
       // S_h of the 64 keys of one part (rows 64 part .. of the K tile) into columns 64 part .. of S_h
       auto issue_S = [&](int stage, int part) {
-        const uint32_t k_lo = sdesc_lo(sKV + stage * Cfg::TILE_BYTES + part * (FWD_PART_KEYS * 128), 16);
+        const uint32_t k_lo = sdesc_lo(sKV + stage * Cfg::TILE_BYTES + part * (FWD_PART_KEYS * 2 * Cfg::CHUNK_COLS), 16);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = ((kk >> 2) * TILE_BYTES_64 + (kk & 3) * 32) >> 4;
-          umma_ss_lead(lead, tmS + FWD_PART_KEYS * part, q_lo + off, k_lo + off, IDESC_S, kk > 0 ? 1u : 0u);
+          const uint32_t off = kstep_bytes(D, kk) >> 4;
+          umma_ss_lead(lead, tmS + FWD_PART_KEYS * part, q_lo + off, k_lo + off, IDESC_S, kk > 0 ? 1u : 0u, HI);
         }
       };
       // O_h += P V over the 64 keys of one part; its 16-bit P sits in the first 32 columns of the part
       auto issue_PV = [&](int stage, bool acc, int part) {
-        const uint32_t v_lo = sdesc_lo(sKV + stage * Cfg::TILE_BYTES, TILE_BYTES_64);
+        const uint32_t v_lo = sdesc_lo(sKV + stage * Cfg::TILE_BYTES, Cfg::CHUNK_BYTES);
 #pragma unroll
         for (int k4 = 0; k4 < FWD_PART_KEYS / 16; ++k4) {
           const int kk = part * (FWD_PART_KEYS / 16) + k4;
-          umma_ts_lead(lead, tmO, tmS + FWD_PART_KEYS * part + k4 * 8, v_lo + ((kk * 2048) >> 4), IDESC_O,
-                       (acc || kk > 0) ? 1u : 0u);
+          umma_ts_lead(lead, tmO, tmS + FWD_PART_KEYS * part + k4 * 8, v_lo + (kstep_rows_bytes(D, kk) >> 4), IDESC_O,
+                       (acc || kk > 0) ? 1u : 0u, HI);
         }
       };
       auto kv_wait = [&](int idx) {
@@ -463,14 +466,15 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             if (!ok) break;
             tc_fence_after();
             const float2 a2 = make_float2(alpha, alpha);
+            constexpr int W = col_step(D);
 #pragma unroll
-            for (int c0 = 0; c0 < D; c0 += 32) {
-              float2 o[16];
-              tmem_ld32(tOh[hf] + c0, reinterpret_cast<uint32_t*>(o));
+            for (int c0 = 0; c0 < D; c0 += W) {
+              float2 o[W / 2];
+              tmem_ldw<W>(tOh[hf] + c0, reinterpret_cast<uint32_t*>(o));
               tmem_wait_ld();
 #pragma unroll
-              for (int i = 0; i < 16; ++i) o[i] = __fmul2_rn(o[i], a2);
-              tmem_st32(tOh[hf] + c0, reinterpret_cast<const uint32_t*>(o));
+              for (int i = 0; i < W / 2; ++i) o[i] = __fmul2_rn(o[i], a2);
+              tmem_stw<W>(tOh[hf] + c0, reinterpret_cast<const uint32_t*>(o));
             }
             tmem_wait_st();
           }
@@ -611,14 +615,15 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           l = l * a_new + l_old * a_old;
           m = m_tot;
         }
+        constexpr int W = col_step(D);
 #pragma unroll
-        for (int cc = 0; cc < D; cc += 32) {
-          float o[32];
-          tmem_ld32(tO + cc, reinterpret_cast<uint32_t*>(o));
+        for (int cc = 0; cc < D; cc += W) {
+          float o[W];
+          tmem_ldw<W>(tO + cc, reinterpret_cast<uint32_t*>(o));
           tmem_wait_ld();
           if (valid) {
 #pragma unroll
-            for (int i = 0; i < 32; i += 4) {
+            for (int i = 0; i < W; i += 4) {
               float4 w = make_float4(o[i] * a_new, o[i + 1] * a_new, o[i + 2] * a_new, o[i + 3] * a_new);
               if (p.mode == 2) {
                 const float4 old = *reinterpret_cast<const float4*>(arow + cc + i);
@@ -646,14 +651,15 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const bool valid = row < Sq;
         uint8_t* orow = reinterpret_cast<uint8_t*>(p.o) +
                         2 * (bc * p.o_sb + h * p.o_sh + static_cast<long long>(q_base + row) * p.o_ss);
+        constexpr int W = col_step(D);
 #pragma unroll
-        for (int cc = 0; cc < D; cc += 32) {
-          float o[32];
-          tmem_ld32(tO + cc, reinterpret_cast<uint32_t*>(o));
+        for (int cc = 0; cc < D; cc += W) {
+          float o[W];
+          tmem_ldw<W>(tO + cc, reinterpret_cast<uint32_t*>(o));
           tmem_wait_ld();
           if (valid) {
 #pragma unroll
-            for (int i = 0; i < 32; i += 8) {
+            for (int i = 0; i < W; i += 8) {
               uint4 w;
               w.x = pack16<BF16>(o[i] * inv, o[i + 1] * inv);
               w.y = pack16<BF16>(o[i + 2] * inv, o[i + 3] * inv);

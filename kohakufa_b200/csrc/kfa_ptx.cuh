@@ -251,6 +251,31 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
 // (the address field cannot carry: shared memory addresses >> 4 fit in its 14 bits).
 constexpr uint32_t SDESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
 
+// Head dims are handled as chunks of C columns, C the widest of 64, 32, 16 that divides the head dim: one TMA
+// box of 128 rows x C columns per chunk, written with the swizzle whose span is the box's row (128, 64 or 32
+// bytes), so that a tile of any head dim that is a multiple of 16 is loaded and multiplied without padding
+// (the reference's chunking: src/kohakufa/sm100/config.py:15, 76-80).
+__host__ __device__ constexpr int chunk_cols(int D) { return D % 64 == 0 ? 64 : (D % 32 == 0 ? 32 : 16); }
+__host__ __device__ constexpr int chunk_bytes(int D) { return 128 * chunk_cols(D) * 2; }
+// High descriptor word for a tile of such chunks: stride offset = eight rows of 2 C bytes; swizzle field
+// 2 / 4 / 6 = 128 / 64 / 32 bytes. (K-major: the leading offset is unused. MN-major: rows are K, C contiguous
+// MN elements per row, leading offset = distance between chunks.)
+__host__ __device__ constexpr uint32_t sdesc_hi_for(int D) {
+  return (static_cast<uint32_t>(16 * chunk_cols(D)) >> 4) | (1u << 14) |
+         ((chunk_cols(D) == 64 ? 2u : (chunk_cols(D) == 32 ? 4u : 6u)) << 29);
+}
+// Byte offset of k-step kk (16 contraction elements) of a K-major tile made of such chunks.
+__host__ __device__ constexpr uint32_t kstep_bytes(int D, int kk) {
+  return static_cast<uint32_t>((kk / (chunk_cols(D) / 16)) * chunk_bytes(D) + (kk % (chunk_cols(D) / 16)) * 32);
+}
+// Byte offset of k-step kk (16 rows) of an MN-major tile made of such chunks.
+__host__ __device__ constexpr uint32_t kstep_rows_bytes(int D, int kk) {
+  return static_cast<uint32_t>(kk * 16 * chunk_cols(D) * 2);
+}
+// Columns of an fp32 accumulator moved per tensor-memory access in the row loops: 32, or 16 where the head
+// dim is an odd multiple of 16.
+__host__ __device__ constexpr int col_step(int D) { return D % 32 == 0 ? 32 : 16; }
+
 __device__ __forceinline__ uint32_t sdesc_lo(uint32_t saddr, uint32_t lbo) {
   return ((saddr & 0x3FFFFu) >> 4) | ((lbo >> 4) << 16);
 }
@@ -267,7 +292,7 @@ __device__ __forceinline__ bool elect_one() {
 }
 
 __device__ __forceinline__ void umma_ss_lead(bool lead, uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo,
-                                             uint32_t idesc, uint32_t accumulate) {
+                                             uint32_t idesc, uint32_t accumulate, uint32_t hi = SDESC_HI) {
   asm volatile(
       "{\n\t.reg .pred p, q;\n\t.reg .b64 da, db;\n\t"
       "mov.b64 da, {%1, %5};\n\t"
@@ -275,20 +300,20 @@ __device__ __forceinline__ void umma_ss_lead(bool lead, uint32_t d_tmem, uint32_
       "setp.ne.b32 p, %4, 0;\n\t"
       "setp.ne.b32 q, %6, 0;\n\t"
       "@q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(SDESC_HI),
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(hi),
       "r"(static_cast<uint32_t>(lead))
       : "memory");
 }
 
 __device__ __forceinline__ void umma_ts_lead(bool lead, uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
-                                             uint32_t idesc, uint32_t accumulate) {
+                                             uint32_t idesc, uint32_t accumulate, uint32_t hi = SDESC_HI) {
   asm volatile(
       "{\n\t.reg .pred p, q;\n\t.reg .b64 db;\n\t"
       "mov.b64 db, {%2, %5};\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "setp.ne.b32 q, %6, 0;\n\t"
       "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %3, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(SDESC_HI),
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(hi),
       "r"(static_cast<uint32_t>(lead))
       : "memory");
 }
@@ -423,6 +448,17 @@ __device__ __forceinline__ void fill_rows_nan16(void* base, long long row_stride
 }
 __device__ __forceinline__ void fill_nan32(float* base, long long count) {
   for (long long i = threadIdx.x; i < count; i += blockDim.x) base[i] = __int_as_float(0x7fc00000);
+}
+
+template <int W>
+__device__ __forceinline__ void tmem_ldw(uint32_t taddr, uint32_t* r) {
+  if constexpr (W == 32) tmem_ld32(taddr, r);
+  else tmem_ld16(taddr, r);
+}
+template <int W>
+__device__ __forceinline__ void tmem_stw(uint32_t taddr, const uint32_t* r) {
+  if constexpr (W == 32) tmem_st32(taddr, r);
+  else tmem_st16(taddr, r);
 }
 
 // ----------------------------------------------------------------------------------

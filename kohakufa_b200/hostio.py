@@ -154,7 +154,7 @@ def attention_fwd_bwd_host(q, k, v, dout, *, causal=False, block_causal=0, scale
                            pipeline=None):
     """out, dq, dk, dv (pinned host tensors) of ``attention(q, k, v, ...)`` and its backward for ``dout``.
     All four inputs: pinned host ``[B, H, S, D]`` views with a contiguous last dim (e.g. ``[B, S, H, D]``
-    storage), fp16 or bf16, head dim 64 or 128. ``pipeline``: a ``HostPipeline`` to reuse buffers and
+    storage), fp16 or bf16, head dim a multiple of 16 up to 128. ``pipeline``: a ``HostPipeline`` to reuse buffers and
     streams across calls. The returned host tensors are valid once the current stream has caught up
     (``torch.cuda.current_stream().synchronize()``)."""
     if causal and block_causal not in (0, 1):

@@ -3,7 +3,7 @@
 Mirrors the operator boundary of the reference (KohakuFA ``src/kohakufa/sm100/op.py:41-175``):
 
     q [B, H, Sq, D], k / v [B, H, Skv, D], fp16 or bf16 (views of [B, S, H, D] projections are
-    fine: any strides with a contiguous last dim and 16-byte aligned strides), D = 64 or 128.
+    fine: any strides with a contiguous last dim and 16-byte aligned strides), D a multiple of 16 up to 128.
     scale: softmax scale (None -> D ** -0.5). block_causal: frame size P (query i sees key j iff
     j // P <= i // P), 0 for dense attention.
     Returns out [B, H, Sq, D], a view of [B, Sq, H, D] storage.
@@ -27,7 +27,8 @@ from kohakufa_b200 import _lib
 
 import os
 
-KERNEL_DIMS = (64, 128)  # head dims the kernels are built for; the API zero-pads up to one
+KERNEL_DIMS = tuple(range(16, 129, 16))  # head dims the kernels are built for (the reference's multiples of 16: api.py:18-29); the API zero-pads up to one
+FUSED_DIMS = (64, 128)  # ... and those the fused backward is built for
 MAX_KERNEL_DIM = 128
 
 
@@ -78,6 +79,8 @@ def is_deterministic() -> bool:
 def use_fused_backward(dim: int, batch_heads: int) -> bool:
     """Whether the fused kernel runs for this head dim under the current mode."""
     if _backward_mode == "split" or batch_heads > 65535:
+        return False
+    if dim not in FUSED_DIMS:
         return False
     return _backward_mode == "fused" or FUSED_IS_FASTER[dim]
 

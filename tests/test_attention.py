@@ -135,8 +135,23 @@ def test_head_dims(dim, causal):
     check(run(q, k, v, dout, causal=causal), want_for(q, k, v, dout, block=int(causal)))
 
 
+@pytest.mark.parametrize("dim", [16, 32, 48, 80, 96, 112])
+@pytest.mark.parametrize("dtype,tol", [(torch.float16, TOL), (torch.bfloat16, BF16_TOL)])
+def test_native_head_dims(dim, dtype, tol):
+    """Every multiple of 16 has kernels of its own (chunks of 64 / 32 / 16 columns under the 128 / 64 / 32
+    byte swizzle): ragged lengths, a block-causal frame, several key tiles, both dtypes; and the library is
+    given the head dim itself, not a padded one."""
+    from kohakufa_b200 import op
+
+    assert op.kernel_dim_for(dim) == dim and op.kernel_dim_for(dim - 3) == dim
+    q, k, v, dout = inputs(2, 3, 300, 517, dim=dim, seed=dim, dtype=dtype)
+    check(run(q, k, v, dout, block_causal=130), want_for(q, k, v, dout, block=130), tol=tol)
+    q, k, v, dout = inputs(1, 2, 700, 700, dim=dim, seed=dim + 1, dtype=dtype)
+    check(run(q, k, v, dout, causal=True), want_for(q, k, v, dout, block=1), tol=tol)
+
+
 @pytest.mark.parametrize("heads,kv_heads,mode", [(4, 2, {"causal": True}), (6, 1, {}), (8, 2, {"block_causal": 100})])
-@pytest.mark.parametrize("dim,dtype,tol", [(64, torch.float16, TOL), (128, torch.bfloat16, BF16_TOL)])
+@pytest.mark.parametrize("dim,dtype,tol", [(64, torch.float16, TOL), (128, torch.bfloat16, BF16_TOL), (96, torch.bfloat16, BF16_TOL), (48, torch.float16, TOL)])
 def test_gqa(heads, kv_heads, mode, dim, dtype, tol):
     """Grouped-query / multi-query attention: query head h uses K / V head h // (H / Hkv); dK / dV sum
     over the group (reference test: tests/test_attention.py:189-211)."""

@@ -127,7 +127,8 @@ def test_mask(shape, mask_shape, density):
     check(run(q, k, v, dout, mask=mask), oracle.attention_fp64(q, k, v, dout, 64**-0.5, mask=mask))
 
 
-@pytest.mark.parametrize("dim,dtype,tol", [(128, torch.bfloat16, BF16_TOL), (128, torch.float16, TOL), (64, torch.bfloat16, BF16_TOL)])
+@pytest.mark.parametrize("dim,dtype,tol", [(128, torch.bfloat16, BF16_TOL), (128, torch.float16, TOL), (64, torch.bfloat16, BF16_TOL),
+                                           (32, torch.float16, TOL), (112, torch.bfloat16, BF16_TOL)])
 def test_mask_dims_and_dtypes(dim, dtype, tol):
     q, k, v, dout = inputs(1, 2, 300, 389, dim=dim, dtype=dtype)
     mask = random_mask((1, 2, 300, 389), 0.5)

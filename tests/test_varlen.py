@@ -93,6 +93,11 @@ def test_varlen_bf16():
     check_varlen([300, 129, 700], [300, 129, 700], 4, 2, 1, dtype=torch.bfloat16, tol=BF16_TOL)
 
 
+@pytest.mark.parametrize("dim", [32, 80])
+def test_varlen_native_head_dims(dim):
+    check_varlen([700, 130, 256], [700, 130, 256], 4, 2, 1, dtype=torch.bfloat16, tol=BF16_TOL, dim=dim)
+
+
 def test_varlen_dim128_bf16():
     check_varlen([700, 130, 256], [700, 130, 256], 2, 2, 1, dtype=torch.bfloat16, tol=BF16_TOL, dim=128)
 
