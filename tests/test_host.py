@@ -105,11 +105,13 @@ def test_stride_rule():
 def test_pad_head_dim():
     q, k, v = qkv(d=40)
     pq, pk, pv = api._fit_head_dim(q, k, v)
-    assert pq.shape[-1] == pk.shape[-1] == pv.shape[-1] == 64
+    assert pq.shape[-1] == pk.shape[-1] == pv.shape[-1] == 48  # the next multiple of 16 (reference api.py:18-29)
+    assert torch.equal(pq[..., :40], q) and float(pq[..., 40:].abs().max()) == 0.0
     q, k, v = qkv(d=72)
-    assert api._fit_head_dim(q, k, v)[0].shape[-1] == 128
-    q, k, v = qkv(d=128)
-    assert api._fit_head_dim(q, k, v)[0] is q
+    assert api._fit_head_dim(q, k, v)[0].shape[-1] == 80
+    for d in (16, 96, 128):
+        q, k, v = qkv(d=d)
+        assert api._fit_head_dim(q, k, v)[0] is q
 
 
 def test_center_keys_is_a_pure_shift():
