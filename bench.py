@@ -457,11 +457,11 @@ def main():
 # small case of the configuration's shape: (kernel, S, D, block) -> (bytes, (batch, head) pairs of the
 # captured launch). A launch's traffic grows in proportion to the pairs, so a full launch is scaled by them.
 NCU_DRAM_BYTES = {
-    ("dkdv", 8192, 128, 1): (175.1e6, 16),
-    ("dq", 8192, 128, 1): (155.5e6, 16),
-    ("fwd", 8192, 128, 1): (119.1e6, 16),
+    ("dkdv", 8192, 128, 1): (173.8e6, 16),
+    ("dq", 8192, 128, 1): (155.8e6, 16),
+    ("fwd", 8192, 128, 1): (114.8e6, 16),
     ("fused", 8192, 128, 1): (299.9e6, 16),
-    ("fused", 4096, 64, 256): (296.4e6, 64),
+    ("fused", 4096, 64, 256): (294.7e6, 64),
     ("fwd", 4096, 64, 256): (118.5e6, 64),
 }
 
