@@ -658,6 +658,8 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           reinterpret_cast<const float*>(smem + 2 * Cfg::TILE_BYTES + slot * Cfg::KV_SLOT_BYTES +
                                          2 * Cfg::TILE_BYTES) + 64 * hq + col0;
       float2 pr[32];  // fp32 P of this thread's 64 elements, kept for the dS phase
+      // dP^T(i) is usually there already: tested now, settled after the exponentials
+      const bool dp_probe = mbar_test(bar(B_DP), s & 1);
       {
         float2 sv[32];
         tmem_ld_16x256b_x8(tS, reinterpret_cast<uint32_t*>(sv));
@@ -696,7 +698,7 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       if constexpr (D <= 64) mbar_arrive(bar(B_PLO));
       mbar_arrive(bar(B_P));
       if ((warp & 3) == 0) TR(hq, s, 0, 4);
-      ok = mbar_wait_warp(bar(B_DP), s & 1, ctl, 19);
+      ok = mbar_wait_warp_probed(dp_probe, bar(B_DP), s & 1, ctl, 19);
       if (!ok) break;
       if ((warp & 3) == 0) TR(hq, s, 0, 5);
       tc_fence_after();
@@ -998,6 +1000,7 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       tc_fence_after();
       const int lim = my_limit - j * 128 - 64 * hk;  // visible columns of this warpgroup (masked tiles)
       float2 pr[32];
+      bool dp_probe;
       {
         float2 sv[32];
         tmem_ld32(tS, reinterpret_cast<uint32_t*>(sv));
@@ -1005,6 +1008,7 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         tmem_wait_ld();
         tc_fence_before();
         mbar_arrive(bar(B_SREAD));  // S(j) is in registers: the tensor core may write S(j+1)
+        dp_probe = mbar_test(bar(B_DP), j & 1);  // dP(j) is usually there already: settled after the exponentials
 #pragma unroll
         for (int g = 0; g < 2; ++g) {
           if constexpr (MASKW)
@@ -1015,7 +1019,7 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             p_cols_by_key<false>(sv + 16 * g, nm, c2, nl, 32, pr + 16 * g);
         }
       }
-      ok = mbar_wait_warp(bar(B_DP), j & 1, ctl, 61);
+      ok = mbar_wait_warp_probed(dp_probe, bar(B_DP), j & 1, ctl, 61);
       if (!ok) break;
       tc_fence_after();
       {

@@ -515,11 +515,16 @@ kfa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       // masked step: some (key, query) pair of this tile pair is hidden, or keys are padded
       const bool masked = ragged_keys || (p.P > 0 && i < i_full);
       const float* st = ml_smem + (s & 1) * (Cfg::ML_BYTES / 4) + 64 * hq + col0;  // -m here, -log2 l 128 floats on
-      ok = mbar_wait_warp(bar(B_MLREADY + (s & 1)), (s >> 1) & 1, ctl, 50);
-      if (ok) ok = mbar_wait_warp(bar(B_S), s & 1, ctl, 44);
+      {  // both tests in flight together (the statistics have usually landed long before the scores)
+        const bool ml_probe = mbar_test(bar(B_MLREADY + (s & 1)), (s >> 1) & 1);
+        const bool s_probe = mbar_test(bar(B_S), s & 1);
+        ok = mbar_wait_warp_probed(ml_probe, bar(B_MLREADY + (s & 1)), (s >> 1) & 1, ctl, 50);
+        if (ok) ok = mbar_wait_warp_probed(s_probe, bar(B_S), s & 1, ctl, 44);
+      }
       if (!ok) break;
       tc_fence_after();
       float2 pr[32];  // fp32 P of this thread's 64 elements, kept for the dS phase
+      bool dp_probe, dsfree_probe, dl_probe;
       {
         float2 sv[32];
         tmem_ld_16x256b_x8(tS, reinterpret_cast<uint32_t*>(sv));
@@ -539,6 +544,10 @@ kfa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           tc_fence_before();
           mbar_arrive(bar(B_PLO));
         }
+        // what the dS phase waits for is usually there by now: tested here, settled after the second half of P
+        dp_probe = mbar_test(bar(B_DP), s & 1);
+        dsfree_probe = (s == 0) || mbar_test(bar(B_DSFREE), (s - 1) & 1);
+        dl_probe = mbar_test(bar(B_DLREADY), s & 1);
         if (masked)
           p_frag<BF16, true, 4>(sv, st, c2, q0, qmin, pr, pk);
         else
@@ -551,9 +560,11 @@ kfa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       if constexpr (D != 128) mbar_arrive(bar(B_PLO));
       mbar_arrive(bar(B_P));
       mbar_arrive(bar(B_MLFREE + (s & 1)));
-      ok = mbar_wait_warp(bar(B_DP), s & 1, ctl, 45);
-      if (ok && s > 0) ok = mbar_wait_warp(bar(B_DSFREE), (s - 1) & 1, ctl, 46);
-      if (ok) ok = mbar_wait_warp(bar(B_DLREADY), s & 1, ctl, 30);
+      if (!__all_sync(0xffffffffu, dp_probe && dsfree_probe && dl_probe)) {
+        ok = mbar_wait_warp(bar(B_DP), s & 1, ctl, 45);
+        if (ok && s > 0) ok = mbar_wait_warp(bar(B_DSFREE), (s - 1) & 1, ctl, 46);
+        if (ok) ok = mbar_wait_warp(bar(B_DLREADY), s & 1, ctl, 30);
+      }
       if (!ok) break;
       tc_fence_after();
       {

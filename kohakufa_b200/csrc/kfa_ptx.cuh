@@ -91,6 +91,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking test of a phase (try_wait may suspend the thread for a while when the phase is incomplete;
+// this never does): for the early tests of mbar_wait_warp_probed.
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Per-CTA control block: abort flag in shared memory, status word in global memory.
 struct Ctl {
   volatile int* s_abort;
@@ -99,25 +113,32 @@ struct Ctl {
 
 // Bounded wait for the phase with the given parity to complete. Returns false when the
 // CTA is aborting (this wait or another ran out of time, or another CTA reported a failure).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const Ctl& ctl, int site) {
-  if (mbar_try_wait(bar, parity)) return true;
+// The first test stands apart from the polling loop: a wait whose phase has already completed (most of them,
+// in a pipeline that runs ahead) costs one try_wait and, for a warp, one vote.
+__device__ __forceinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity, volatile int* s_abort, int* g_status,
+                                            int site) {
   const long long t0 = clock64();
   uint32_t spins = 0;
   for (;;) {
     if (mbar_try_wait(bar, parity)) return true;
     if (KFA_SHORT_WAITS || (++spins & 31u) == 0u) {
-      if (*ctl.s_abort) return false;
-      if ((spins & 1023u) == 0u && *reinterpret_cast<volatile int*>(ctl.g_status) != 0) {
-        *ctl.s_abort = 1;
+      if (*s_abort) return false;
+      if ((spins & 1023u) == 0u && *reinterpret_cast<volatile int*>(g_status) != 0) {
+        *s_abort = 1;
         return false;
       }
       if (clock64() - t0 > KFA_WAIT_CYCLES) {
-        *ctl.s_abort = 1;
-        atomicCAS(ctl.g_status, 0, KFA_DEV_TIMEOUT_BASE + site);
+        *s_abort = 1;
+        atomicCAS(g_status, 0, KFA_DEV_TIMEOUT_BASE + site);
         return false;
       }
     }
   }
+}
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const Ctl& ctl, int site) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_poll(bar, parity, ctl.s_abort, ctl.g_status, site);
 }
 
 // For a thread that gives up while copies it has started may still be in flight: waits (bounded, without
@@ -132,16 +153,20 @@ __device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity) {
 // The same for a full warp about to run warp-aligned tcgen05 instructions: the warp reconverges
 // and every lane gets the same answer (false if any lane gave up).
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, const Ctl& ctl, int site) {
-#ifdef KFA_WAIT_ONE_LANE
-  // one lane polls, the warp-wide shuffle hands its answer (and, being a warp barrier, the ordering of what
-  // it observed) to the others: 32 times fewer polls on the shared-memory pipe
-  bool ok = true;
-  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, ctl, site);
-  return __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-#else
-  const bool ok = mbar_wait(bar, parity, ctl, site);
+  bool ok = mbar_try_wait(bar, parity);
+  if (__all_sync(0xffffffffu, ok)) return true;  // the phase had completed: about 25 clk
+  if (!ok) ok = mbar_wait_poll(bar, parity, ctl.s_abort, ctl.g_status, site);
   return __all_sync(0xffffffffu, ok);
-#endif
+}
+
+// A test costs the thread its round trip to the barrier, about 50 clk, even when the phase completed long
+// ago. Where the phase is usually complete well before it is needed, a warp tests it EARLY (`probed =
+// mbar_test(...)`, issued ahead of independent work) and settles here when it needs the data: the
+// round trip is hidden, and the data was complete when the early test saw it.
+__device__ __forceinline__ bool mbar_wait_warp_probed(bool probed, uint32_t bar, uint32_t parity, const Ctl& ctl,
+                                                      int site) {
+  if (__all_sync(0xffffffffu, probed)) return true;
+  return mbar_wait_warp(bar, parity, ctl, site);
 }
 
 // ----------------------------------------------------------------------------------
