@@ -623,7 +623,7 @@ int kfa_bwd(const KfaTensor4* q, const KfaTensor4* k, const KfaTensor4* v, const
   return kfa_bwd_dq(q, k, v, dout, stats, dq, scale, block, dtype, dev_status, stream);
 }
 
-#ifdef KFA_FWD_TRACE
+#ifdef KFA_TRACE
 int kfa_trace_read(long long* out) {
   return cudaMemcpyFromSymbol(out, kfa::kfa_trace, sizeof(kfa::kfa_trace)) == cudaSuccess ? 0 : 1;
 }

@@ -415,7 +415,7 @@ kfa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   auto bar = [&](int i) { return bar0 + 8u * i; };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-#ifdef KFA_FWD_TRACE
+#ifdef KFA_TRACE
   const bool trace_on = (blockIdx.x == 0) && (lane == 0);
 #endif
 

@@ -117,7 +117,9 @@ __device__ __forceinline__ int key_limit(int r, int P, int Skv) {
   return lim < Skv ? static_cast<int>(lim) : Skv;
 }
 
-#ifdef KFA_FWD_TRACE
+// Debug build only (-DKFA_TRACE): CTA 0 of the forward and of the dK / dV kernel records clock64() at its
+// hand-offs, per role, key-tile step, part and event; `kfa_trace_read` copies the table to the host.
+#ifdef KFA_TRACE
 __device__ long long kfa_trace[6][64][2][8];
 #define TR(role, j, part, ev) do { if (trace_on && (j) < 64) kfa_trace[role][j][part][ev] = clock64(); } while (0)
 #else
@@ -196,7 +198,7 @@ kfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-#ifdef KFA_FWD_TRACE
+#ifdef KFA_TRACE
   const bool trace_on = (blockIdx.x == 0) && (lane == 0);
   if (warp == 8) TR(2, 0, 0, 4);
 #endif
