@@ -43,6 +43,8 @@ constexpr int FUSED_THREADS = 512;
 // file); the dQ warpgroup and the MMA + TMA warpgroup then hand registers to the P / dS warpgroups:
 // 2 x 128 x 144 + 128 x 152 + 128 x 72 = 65536 (the dQ warpgroup holds a whole 128 x 128 fp32 tile).
 constexpr int FUSED_REGS_COMPUTE = 144, FUSED_REGS_REDUCE = 152, FUSED_REGS_ISSUE = 72;
+static_assert(2 * 128 * FUSED_REGS_COMPUTE + 128 * FUSED_REGS_REDUCE + 128 * FUSED_REGS_ISSUE <= 512 * 128,
+              "register budgets exceed the CTA's allocation (512 threads x 128): a setmaxnreg.inc would wait for ever");
 
 template <int D>
 struct FusedCfg {

@@ -83,6 +83,10 @@ constexpr int FWD_REGS_SOFTMAX = 176, FWD_REGS_CORRECTION = 72, FWD_REGS_ISSUE =
 #else
 constexpr int FWD_REGS_SOFTMAX = 152, FWD_REGS_CORRECTION = 96, FWD_REGS_ISSUE = 96;
 #endif
+// (A CTA owns the registers it was launched with, 512 x 128 here: budgets beyond that would make a
+// setmaxnreg.inc wait for ever.)
+static_assert(2 * 128 * FWD_REGS_SOFTMAX + 128 * FWD_REGS_CORRECTION + 128 * FWD_REGS_ISSUE <= FWD_THREADS * 128,
+              "register budgets exceed the CTA's allocation");
 #ifndef KFA_FWD_PARTS
 #define KFA_FWD_PARTS 2
 #endif

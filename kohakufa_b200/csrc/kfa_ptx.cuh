@@ -448,13 +448,14 @@ __device__ __forceinline__ void tmem_st_16x128b_x4(uint32_t taddr, const uint32_
 }
 
 // Sets the calling warpgroup's registers per thread (all four warps must call it). The kernel starts
-// with 128 per thread: a budget above that waits until other warpgroups have released enough.
-template <int N>
+// with LAUNCH per thread (what its thread count leaves of the 64 K registers, in eights): a budget above
+// that waits until other warpgroups have released enough.
+template <int N, int LAUNCH = 128>
 __device__ __forceinline__ void reg_budget() {
   static_assert(N % 8 == 0 && N >= 24 && N <= 256, "register budget");
-  if constexpr (N > 128) {
+  if constexpr (N > LAUNCH) {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
-  } else if constexpr (N < 128) {
+  } else if constexpr (N < LAUNCH) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
   }
 }
