@@ -93,7 +93,7 @@ def _strides_ok(t: Tensor) -> bool:
 
 def _check(q: Tensor, k: Tensor, v: Tensor) -> None:
     """Same conditions and exception types as the reference's ``_check`` (op.py:41-55), with the
-    head dims and head counts this build supports."""
+    head dims and head counts this library supports."""
     if q.dtype not in (torch.float16, torch.bfloat16) or k.dtype != q.dtype or v.dtype != q.dtype:
         raise TypeError("attention: q, k, v must be fp16 or bf16 (all the same)")
     if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
