@@ -280,7 +280,9 @@ def main():
     dev = torch.device("cuda", local)
     affinity = bind_to_gpu_cpus(local)  # before any pinned allocation: first touch places the pages
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        from kohakufa_b200.ring import nccl_options
+
+        dist.init_process_group("nccl", device_id=dev, pg_options=nccl_options())  # (the C5 ring record uses it)
 
     # ---- inputs: this rank's batch shard, generated on the CPU, resident in HBM ----
     # C5 (one 131072-token sequence): context-parallel ring over the N GPUs, strong scaling.

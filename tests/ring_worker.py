@@ -28,7 +28,7 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    dist.init_process_group("nccl", device_id=dev)
+    dist.init_process_group("nccl", device_id=dev, pg_options=ring.nccl_options())
     rank, world = dist.get_rank(), dist.get_world_size()
     dtype = torch.bfloat16
     gen = torch.Generator().manual_seed(7)
