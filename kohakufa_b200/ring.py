@@ -209,7 +209,7 @@ def nccl_options():
     nearly all of an SM's shared memory, so a send / receive CTA can only start on an SM that an attention
     CTA has just left; at the default priority the block scheduler hands that SM to the next attention CTA of
     the running grid, the transfer of step t+1 starts when step t's grid has drained, and nothing overlaps
-    (measured at 8 GPUs: the forward waited 6.4 of its 22.6 ms for K / V). Pass the result as
+    (measured at 8 GPUs: the compute stream waited 10.2 of 80 ms for transfers; with the priority 1.1 of 73). Pass the result as
     ``pg_options`` to ``init_process_group`` / ``new_group``."""
     opts = dist.ProcessGroupNCCL.Options()
     opts.is_high_priority_stream = True
