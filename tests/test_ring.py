@@ -115,3 +115,11 @@ def test_emulated_ring_matches_single_call_and_oracle(world, dim, dtype):
         err_single = oracle.metrics(single, w)["rel_err"]
         assert err < tol, (name, err)
         assert err <= 1.25 * err_single + 1e-5, (name, err, err_single)  # no worse than one call
+
+
+def test_nccl_options_ask_for_a_high_priority_stream():
+    """The ring's transfers only overlap the attention grids when NCCL's kernels run at high priority."""
+    if not hasattr(torch.distributed, "ProcessGroupNCCL"):
+        pytest.skip("torch built without NCCL")
+    assert ring.nccl_options().is_high_priority_stream
+
