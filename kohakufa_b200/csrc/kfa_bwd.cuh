@@ -172,6 +172,12 @@ struct BwdCfg {
   static constexpr int TILE_BYTES = CHUNKS * CHUNK_BYTES;  // 128 rows x D columns
   static constexpr uint32_t TMEM_COLS = 512;
   static constexpr uint32_t TM_S = 0, TM_DP = 128, TM_ACC0 = 256, TM_ACC1 = 256 + D;
+  // dQ kernel at D > 64: the 16-bit dS gets two buffers of 64 columns of its own (dQ ends at 256 + D <= 384), so
+  // that dP(j+1) is issued as soon as the warpgroups hold dP(j) instead of after dQ(j): the step is no longer
+  // the loop dS(j-1) -> dQ(j-1), dP(j) -> dS(j) through the tensor core (C3: 2.67 -> 2.57 ms). At D <= 64, where
+  // the two products are short, dS stays over the dP columns (own columns: 0.564 -> 0.582 ms at C4's shape).
+  static constexpr bool DS_OWN = (D > 64);
+  static constexpr uint32_t TM_DS = 384;
   // dK/dV kernel: K, V resident; ring of (Q_i, dO_i, stats_i) slots.
   static constexpr int KV_SLOTS = (D > 96) ? 2 : 3;
   static constexpr int KV_SLOT_BYTES = 2 * TILE_BYTES + 2048;  // stats padded to keep 1 KB alignment
@@ -214,6 +220,16 @@ __device__ __forceinline__ void issue_tmemA_k128(bool lead, uint32_t d_tmem, uin
   for (int kk = 0; kk < 8; ++kk)
     umma_ts_lead(lead, d_tmem, a_tmem + (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8), b_lo + (kstep_rows_bytes(D, kk) >> 4), idesc,
                  (acc || kk > 0) ? 1u : 0u, sdesc_hi_for(D));
+}
+
+// The same with the 16-bit A operand as ONE piece of 64 columns (contraction indices 0-127 at a_tmem .. + 63).
+template <int D>
+__device__ __forceinline__ void issue_tmemA_k128_packed(bool lead, uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
+                                                        uint32_t idesc, bool acc) {
+#pragma unroll
+  for (int kk = 0; kk < 8; ++kk)
+    umma_ts_lead(lead, d_tmem, a_tmem + kk * 8, b_lo + (kstep_rows_bytes(D, kk) >> 4), idesc, (acc || kk > 0) ? 1u : 0u,
+                 sdesc_hi_for(D));
 }
 
 // The same for half of the contraction: k-steps 2 * part, 2 * part + 1 of each warpgroup's piece
@@ -798,7 +814,9 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   constexpr int B_DS = B_S + 3;                // dS(j) stored by both warpgroups
   constexpr int B_ACC = B_S + 4;
   constexpr int B_DRAIN = B_S + 5;
-  constexpr int N_BARS = B_S + 6;
+  constexpr int B_DPREAD = B_S + 6;            // both warpgroups hold dP(j) in registers (256 arrivals)
+  constexpr int B_DSFREE = B_S + 7;            // 2: dQ(j), which read dS buffer j % 2, has retired
+  constexpr int N_BARS = B_S + 9;
   static_assert(N_BARS * 8 + 16 <= 256, "barrier block too small");
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + N_BARS);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
@@ -844,6 +862,9 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     mbar_init(bar(B_DS), 256);
     mbar_init(bar(B_ACC), 1);
     mbar_init(bar(B_DRAIN), 1);
+    mbar_init(bar(B_DPREAD), 256);
+    mbar_init(bar(B_DSFREE + 0), 1);
+    mbar_init(bar(B_DSFREE + 1), 1);
     *s_abort = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
     fence_mbar_init();
   }
@@ -949,20 +970,33 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           issue_kmajor_n128<D>(lead, tS, q_lo, sdesc_lo(sKr + nk * Cfg::TILE_BYTES, 16), IDESC_S);
           umma_commit_lead(lead, bar(B_S));
         }
-        // dQ += dS(j) K_j, then dP(j+1) may overwrite the dS columns
-        ok = mbar_wait_warp(bar(B_DS), j & 1, ctl, 58);
-        if (!ok) break;
-        tc_fence_after();
-        issue_tmemA_k128<D>(lead, tDQ, tDP, sdesc_lo(k_s, Cfg::CHUNK_BYTES), IDESC_ACC, j > 0);
-        umma_commit_lead(lead, bar(B_KFREE + j % NK));
-        if (more) {
+        auto issue_dP_next = [&]() {
           ok = mbar_wait_warp(bar(B_VREADY + nv), ((j + 1) / NV) & 1, ctl, 59);
-          if (!ok) break;
+          if (ok && Cfg::DS_OWN) ok = mbar_wait_warp(bar(B_DPREAD), j & 1, ctl, 63);
+          if (!ok) return;
           tc_fence_after();
           issue_kmajor_n128<D>(lead, tDP, do_lo, sdesc_lo(sVr + nv * Cfg::TILE_BYTES, 16), IDESC_S);
           umma_commit_lead(lead, bar(B_DP));
           umma_commit_lead(lead, bar(B_VFREE + nv));
+        };
+        // own dS columns: dP(j+1) as soon as the warpgroups hold dP(j) in registers
+        if (Cfg::DS_OWN && more) issue_dP_next();
+        if (!ok) break;
+        // dQ += dS(j) K_j
+        ok = mbar_wait_warp(bar(B_DS), j & 1, ctl, 58);
+        if (!ok) break;
+        tc_fence_after();
+        if constexpr (Cfg::DS_OWN) {
+          issue_tmemA_k128_packed<D>(lead, tDQ, tmem + Cfg::TM_DS + 64 * (j & 1), sdesc_lo(k_s, Cfg::CHUNK_BYTES), IDESC_ACC, j > 0);
+          umma_commit_lead(lead, bar(B_KFREE + j % NK));
+          umma_commit_lead(lead, bar(B_DSFREE + (j & 1)));
+        } else {
+          issue_tmemA_k128<D>(lead, tDQ, tDP, sdesc_lo(k_s, Cfg::CHUNK_BYTES), IDESC_ACC, j > 0);
+          umma_commit_lead(lead, bar(B_KFREE + j % NK));
         }
+        // dS over the dP columns: dP(j+1) may overwrite them once dQ(j) is issued
+        if (!Cfg::DS_OWN && more) issue_dP_next();
+        if (!ok) break;
       }
       if (ok) umma_commit_lead(lead, bar(B_ACC));
       umma_commit_lead(lead, bar(B_DRAIN));
@@ -975,6 +1009,7 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tS = tmem + Cfg::TM_S + 64 * hk + lane_base;
     const uint32_t tDP = tmem + Cfg::TM_DP + 64 * hk + lane_base;
+    const uint32_t tDS = tmem + Cfg::TM_DS + 32 * hk + lane_base;  // this warpgroup's 32 packed columns of buffer 0
     const float* st = p.stats + static_cast<long long>(bh) * p.stats_sh + qt * 384ll;
     const float2 nm = make_float2(st[r_in], st[r_in]);                // -m
     const float2 nl = make_float2(st[128 + r_in], st[128 + r_in]);    // -log2 l
@@ -1026,12 +1061,23 @@ kfa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         float2 dp[32];
         tmem_ld32(tDP, reinterpret_cast<uint32_t*>(dp));
         tmem_ld32(tDP + 32, reinterpret_cast<uint32_t*>(dp + 16));
+        // own dS columns: the buffer of this step was last read by dQ(j-2), retired long ago: tested while the loads fly
+        const bool free_probe = !Cfg::DS_OWN || (j < 2) || mbar_test(bar(B_DSFREE + (j & 1)), ((j >> 1) - 1) & 1);
         tmem_wait_ld();
+        if constexpr (Cfg::DS_OWN) {
+          tc_fence_before();
+          mbar_arrive(bar(B_DPREAD));  // dP(j) is in registers: the tensor core may write dP(j+1)
+          if (j >= 2) {
+            ok = mbar_wait_warp_probed(free_probe, bar(B_DSFREE + (j & 1)), ((j >> 1) - 1) & 1, ctl, 64);
+            if (!ok) break;
+          }
+        }
 #pragma unroll
         for (int g = 0; g < 2; ++g) {
           uint32_t dk[16];
           ds_cols_by_key<BF16>(dp + 16 * g, pr + 16 * g, nd, dk);
-          tmem_st16(tDP + 16 * g, dk);  // 16-bit dS over dP columns this thread has already read
+          // 16-bit dS into its own columns, or over dP columns this thread has already read
+          tmem_st16(Cfg::DS_OWN ? tDS + 64 * (j & 1) + 16 * g : tDP + 16 * g, dk);
         }
       }
       tmem_wait_st();
