@@ -22,7 +22,8 @@
 // kernel). A step has two compute phases, P from S and then dS from dP, each followed by an MMA that
 // consumes the 16-bit result straight from TMEM (P^T / dS^T overwrite the S^T / dP^T columns they
 // came from). The MMA warp interleaves the four (three) MMAs of consecutive steps,
-//   dK/dV:  dV(i)  S^T(i+1)  dK(i)  dP^T(i+1)          dQ:  S(j+1)  dQ(j)  dP(j+1)
+//   dK/dV:  dV(i)  S^T(i+1)  dK(i)  dP^T(i+1)          dQ:  S(j+1)  dQ(j)  dP(j+1)   (D > 64: S(j+1)  dP(j+1)  dQ(j),
+//                                                          with dS in columns of its own: see BwdCfg::DS_OWN)
 // so that while the warpgroups compute one phase the tensor core always has another MMA to run, and
 // every smem x smem MMA is a full 128-column one (64-column ones run at 2/3 rate on this part).
 //
