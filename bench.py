@@ -460,7 +460,7 @@ def main():
 # captured launch). A launch's traffic grows in proportion to the pairs, so a full launch is scaled by them.
 NCU_DRAM_BYTES = {
     ("dkdv", 8192, 128, 1): (173.8e6, 16),
-    ("dq", 8192, 128, 1): (155.8e6, 16),
+    ("dq", 8192, 128, 1): (157.1e6, 16),
     ("fwd", 8192, 128, 1): (114.8e6, 16),
     ("fused", 8192, 128, 1): (299.9e6, 16),
     ("fused", 4096, 64, 256): (294.7e6, 64),
